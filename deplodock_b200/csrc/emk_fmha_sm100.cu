@@ -1,0 +1,416 @@
+// Causal grouped-query flash attention on tcgen05 tensor cores, bf16 operands, head_dim 128, fp32 online softmax.
+//
+// Reference behaviour: SdpaOp (emmy/compiler/ir/frontend/ir.py:241-275) decomposed by
+// emmy/compiler/pipeline/passes/frontend/decomposition/010_sdpa.py:52-141 (Kᵀ, GQA head h -> h / group, scale
+// 1/sqrt(D), causal mask, softmax, PV) and lowered as a one-warp-per-16-rows mma.sync flash kernel
+// (emmy/compiler/pipeline/passes/lowering/kernel/_twist.py:229) that re-reads Q and K fragments from global memory
+// every 16 keys, never skips masked tiles and does not share K/V between the query heads of a group.
+//
+// Here one CTA owns 128 query rows of TWO query heads that share a KV head (two 128x128 tiles, "ping-pong"):
+//   warps 0..3  softmax of tile 0 (thread = query row: no shuffles for row max / row sum)
+//   warps 4..7  softmax of tile 1
+//   warp 8      TMA producer: Q once, then a 2-slot ring of K tiles and a 2-slot ring of V tiles
+//   warp 9      MMA issuer: S = Q·Kᵀ (both operands from shared memory) and O += P·V (P from tensor memory,
+//               V from shared memory as an MN-major operand)
+// Tensor memory (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each; the bf16 probabilities P overwrite the
+// first 64 columns of their S tile. While the tensor core works on one tile the softmax warps work on the other.
+// Only KV blocks at or below the diagonal are visited, heavy query blocks are scheduled first, and O is rescaled
+// lazily (only when the running max grows by more than 2^8), so most iterations never touch O.
+// Every mbarrier wait is bounded; after an expiry all roles fall through to the common teardown.
+#include "emk_common.cuh"
+
+#include <math_constants.h>
+
+namespace {
+
+using namespace emk;
+
+constexpr int FM = 128;   // query rows per tile
+constexpr int FN = 128;   // keys per KV block
+constexpr int HD = 128;   // head dim
+constexpr int FMHA_THREADS = 320;
+constexpr int TILE_BYTES = FM * HD * 2;   // 32 KB: two 64-column halves of 16 KB
+constexpr int HALF_BYTES = FM * 64 * 2;   // 16 KB
+constexpr int KV_STAGES = 2;
+constexpr uint32_t IDESC_S = make_idesc_bf16(FM, FN, 0, 0);
+constexpr uint32_t IDESC_PV = make_idesc_bf16(FM, HD, 0, 1);
+constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
+
+struct FmhaArgs {
+  __nv_bfloat16* o;
+  int B, Hq, Hkv, S, group, pairs;
+  int nqblk;
+  // coordinates: x = h * cs + 64 * half, y = b * rb + h * rh + s  (q side indexed by query head, kv side by KV head)
+  int q_cs, q_rb, q_rh;
+  int kv_cs, kv_rb, kv_rh;
+  int o_cs, o_rb, o_rh;
+  int64_t ld_o;
+  float scale_log2;
+  int* status;
+  unsigned long long limit_ns;
+};
+
+struct __align__(8) FmhaBarriers {
+  uint64_t q_full;
+  uint64_t k_full[KV_STAGES], k_empty[KV_STAGES];
+  uint64_t v_full[KV_STAGES], v_empty[KV_STAGES];
+  uint64_t s_full[2], p_full[2], o_done[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__global__ void __launch_bounds__(FMHA_THREADS, 1)
+fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
+                   const __grid_constant__ CUtensorMap tma_v, const FmhaArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* sQ = smem;                               // 2 tiles
+  uint8_t* sK = sQ + 2 * TILE_BYTES;                // KV_STAGES tiles
+  uint8_t* sV = sK + KV_STAGES * TILE_BYTES;        // KV_STAGES tiles
+  FmhaBarriers* bars = reinterpret_cast<FmhaBarriers*>(sV + KV_STAGES * TILE_BYTES);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // Work decode: heaviest query blocks first.
+  const int per_qblk = a.B * a.Hkv * a.pairs;
+  const int qblk = a.nqblk - 1 - (int)(blockIdx.x / per_qblk);
+  int rem = (int)(blockIdx.x % per_qblk);
+  const int pair = rem % a.pairs;
+  rem /= a.pairs;
+  const int hkv = rem % a.Hkv;
+  const int b = rem / a.Hkv;
+  const int hq0 = hkv * a.group + 2 * pair;
+  const bool two = (2 * pair + 1) < a.group;
+  const int q0 = qblk * FM;
+  const int nblk = qblk + 1;  // KV blocks 0..qblk (FM == FN)
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->q_full, 1);
+    for (int i = 0; i < KV_STAGES; ++i) {
+      mbar_init(&bars->k_full[i], 1);
+      mbar_init(&bars->k_empty[i], 1);
+      mbar_init(&bars->v_full[i], 1);
+      mbar_init(&bars->v_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->s_full[i], 1);
+      mbar_init(&bars->p_full[i], 128);
+      mbar_init(&bars->o_done[i], 1);
+    }
+    bars->abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 8 && lane == 0) {
+    tma_prefetch_desc(&tma_q);
+    tma_prefetch_desc(&tma_k);
+    tma_prefetch_desc(&tma_v);
+  }
+  if (warp == 0) {
+    tmem_alloc(&bars->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+  const WaitCtx wc{&bars->abort_flag, a.status, a.limit_ns};
+
+  if (warp == 8) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      const int ntile = two ? 2 : 1;
+      mbar_arrive_expect_tx(&bars->q_full, (uint32_t)(ntile * TILE_BYTES));
+      for (int t = 0; t < ntile; ++t) {
+        const int hq = hq0 + t;
+        const int y = b * a.q_rb + hq * a.q_rh + q0;
+        tma_load_2d(sQ + t * TILE_BYTES, &tma_q, &bars->q_full, hq * a.q_cs, y);
+        tma_load_2d(sQ + t * TILE_BYTES + HALF_BYTES, &tma_q, &bars->q_full, hq * a.q_cs + 64, y);
+      }
+      const int ykv = b * a.kv_rb + hkv * a.kv_rh;
+      const int xkv = hkv * a.kv_cs;
+      for (int j = 0; j < nblk; ++j) {
+        const int st = j % KV_STAGES;
+        const uint32_t ph = (uint32_t)(j / KV_STAGES) & 1u;
+        if (!mbar_wait(&bars->k_empty[st], ph ^ 1u, wc, EMK_DEV_TIMEOUT_PRODUCER)) break;
+        mbar_arrive_expect_tx(&bars->k_full[st], TILE_BYTES);
+        tma_load_2d(sK + st * TILE_BYTES, &tma_k, &bars->k_full[st], xkv, ykv + j * FN);
+        tma_load_2d(sK + st * TILE_BYTES + HALF_BYTES, &tma_k, &bars->k_full[st], xkv + 64, ykv + j * FN);
+        if (!mbar_wait(&bars->v_empty[st], ph ^ 1u, wc, EMK_DEV_TIMEOUT_PRODUCER)) break;
+        mbar_arrive_expect_tx(&bars->v_full[st], TILE_BYTES);
+        tma_load_2d(sV + st * TILE_BYTES, &tma_v, &bars->v_full[st], xkv, ykv + j * FN);
+        tma_load_2d(sV + st * TILE_BYTES + HALF_BYTES, &tma_v, &bars->v_full[st], xkv + 64, ykv + j * FN);
+      }
+    }
+  } else if (warp == 9) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      const int ntile = two ? 2 : 1;
+      const uint32_t sq_addr = smem_u32(sQ);
+      const uint32_t sk_addr = smem_u32(sK);
+      const uint32_t sv_addr = smem_u32(sV);
+      auto issue_s = [&](int t, int st) {
+        const uint32_t qa = sq_addr + t * TILE_BYTES;
+        const uint32_t ka = sk_addr + st * TILE_BYTES;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+          const uint32_t off = (uint32_t)((ks >> 2) * HALF_BYTES + (ks & 3) * 32);
+          umma_ss(tmem_base + (uint32_t)(t * FN), make_smem_desc(qa + off, 0, 1024), make_smem_desc(ka + off, 0, 1024),
+                  IDESC_S, (uint32_t)(ks != 0));
+        }
+      };
+      auto issue_pv = [&](int t, int st, bool accumulate) {
+        const uint32_t va = sv_addr + st * TILE_BYTES;
+#pragma unroll
+        for (int ks = 0; ks < FN / 16; ++ks) {
+          umma_ts(tmem_base + 256u + (uint32_t)(t * HD), tmem_base + (uint32_t)(t * FN) + (uint32_t)(ks * 8),
+                  make_smem_desc(va + ks * 16 * 128, HALF_BYTES, 1024), IDESC_PV,
+                  (uint32_t)(accumulate || ks != 0));
+        }
+      };
+      bool ok = mbar_wait(&bars->q_full, 0, wc, EMK_DEV_TIMEOUT_MMA);
+      if (ok) ok = mbar_wait(&bars->k_full[0], 0, wc, EMK_DEV_TIMEOUT_MMA);
+      if (ok) {
+        tc_fence_after();
+        for (int t = 0; t < ntile; ++t) {
+          issue_s(t, 0);
+          tc_commit(&bars->s_full[t]);
+        }
+        tc_commit(&bars->k_empty[0]);
+      }
+      for (int j = 0; j < nblk && ok; ++j) {
+        const int st = j % KV_STAGES;
+        const uint32_t ph = (uint32_t)(j / KV_STAGES) & 1u;
+        const int stn = (j + 1) % KV_STAGES;
+        const uint32_t phn = (uint32_t)((j + 1) / KV_STAGES) & 1u;
+        const bool has_next = (j + 1) < nblk;
+        for (int t = 0; t < ntile && ok; ++t) {
+          ok = mbar_wait(&bars->p_full[t], (uint32_t)j & 1u, wc, EMK_DEV_TIMEOUT_MMA);
+          if (ok && t == 0) ok = mbar_wait(&bars->v_full[st], ph, wc, EMK_DEV_TIMEOUT_MMA);
+          if (!ok) break;
+          tc_fence_after();
+          issue_pv(t, st, j > 0);
+          tc_commit(&bars->o_done[t]);
+          if (t == ntile - 1) tc_commit(&bars->v_empty[st]);
+          if (has_next) {
+            if (t == 0) {
+              ok = mbar_wait(&bars->k_full[stn], phn, wc, EMK_DEV_TIMEOUT_MMA);
+              if (!ok) break;
+              tc_fence_after();
+            }
+            issue_s(t, stn);
+            tc_commit(&bars->s_full[t]);
+            if (t == ntile - 1) tc_commit(&bars->k_empty[stn]);
+          }
+        }
+      }
+    }
+  } else {
+    // ---------------- softmax / correction / epilogue: warps 0..3 tile 0, warps 4..7 tile 1 ----------------
+    const int t = warp >> 2;
+    if (t == 0 || two) {
+      const int quarter = warp & 3;
+      const int r_in_tile = quarter * 32 + lane;
+      const int q_row = q0 + r_in_tile;  // position in the sequence
+      const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+      const uint32_t tS = tmem_base + lane_base + (uint32_t)(t * FN);
+      const uint32_t tO = tmem_base + lane_base + 256u + (uint32_t)(t * HD);
+      float m_used = -CUDART_INF_F;
+      float l = 0.f;
+      bool ok = true;
+      for (int j = 0; j < nblk; ++j) {
+        if (!mbar_wait_warp(&bars->s_full[t], (uint32_t)j & 1u, wc, EMK_DEV_TIMEOUT_SOFTMAX)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        uint32_t s[FN];
+#pragma unroll
+        for (int c = 0; c < FN / 32; ++c) tmem_ld_x32(tS + (uint32_t)(c * 32), s + c * 32);
+        tmem_ld_wait();
+        float mx = -CUDART_INF_F;
+        if (j == nblk - 1) {
+          // diagonal block: key index k0 + i is visible to query q_row iff k0 + i <= q_row, k0 == q0 here
+#pragma unroll
+          for (int i = 0; i < FN; ++i) {
+            const float v = (i <= r_in_tile) ? __uint_as_float(s[i]) : -CUDART_INF_F;
+            s[i] = __float_as_uint(v);
+            mx = fmaxf(mx, v);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < FN; ++i) mx = fmaxf(mx, __uint_as_float(s[i]));
+        }
+        const float m_new = fmaxf(m_used, mx * a.scale_log2);
+        const bool need = (m_new - m_used) > RESCALE_THRESHOLD;  // true on the first block (m_used = -inf)
+        if (__any_sync(0xffffffffu, need)) {
+          if (j > 0) {
+            if (!mbar_wait_warp(&bars->o_done[t], (uint32_t)(j - 1) & 1u, wc, EMK_DEV_TIMEOUT_SOFTMAX)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const float alpha = ex2_approx(m_used - m_new);
+            l *= alpha;
+#pragma unroll 1
+            for (int c = 0; c < HD / 32; ++c) {
+              uint32_t o[32];
+              tmem_ld_x32(tO + (uint32_t)(c * 32), o);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              tmem_st_x32(tO + (uint32_t)(c * 32), o);
+            }
+            tmem_st_wait();
+          }
+          m_used = m_new;
+        }
+        const float neg_m = -m_used;
+        float sum = 0.f;
+        uint32_t p[FN / 2];
+#pragma unroll
+        for (int i = 0; i < FN / 2; ++i) {
+          const float p0 = ex2_approx(fmaf(__uint_as_float(s[2 * i]), a.scale_log2, neg_m));
+          const float p1 = ex2_approx(fmaf(__uint_as_float(s[2 * i + 1]), a.scale_log2, neg_m));
+          sum += p0 + p1;
+          p[i] = pack_bf16x2(p0, p1);
+        }
+        l += sum;
+        tmem_st_x32(tS, p);
+        tmem_st_x32(tS + 32u, p + 32);
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(&bars->p_full[t]);
+      }
+      if (ok && mbar_wait_warp(&bars->o_done[t], (uint32_t)(nblk - 1) & 1u, wc, EMK_DEV_TIMEOUT_SOFTMAX)) {
+        tc_fence_after();
+        const float inv = 1.0f / l;
+        const int hq = hq0 + t;
+        __nv_bfloat16* orow =
+            a.o + ((int64_t)b * a.o_rb + (int64_t)hq * a.o_rh + q_row) * a.ld_o + (int64_t)hq * a.o_cs;
+#pragma unroll 1
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld_x32(tO + (uint32_t)(c * 32), o);
+          tmem_ld_wait();
+          if (q_row < a.S) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 v;
+              v.x = pack_bf16x2(__uint_as_float(o[q * 8 + 0]) * inv, __uint_as_float(o[q * 8 + 1]) * inv);
+              v.y = pack_bf16x2(__uint_as_float(o[q * 8 + 2]) * inv, __uint_as_float(o[q * 8 + 3]) * inv);
+              v.z = pack_bf16x2(__uint_as_float(o[q * 8 + 4]) * inv, __uint_as_float(o[q * 8 + 5]) * inv);
+              v.w = pack_bf16x2(__uint_as_float(o[q * 8 + 6]) * inv, __uint_as_float(o[q * 8 + 7]) * inv);
+              *reinterpret_cast<uint4*>(orow + c * 32 + q * 8) = v;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (bars->abort_flag) abort_drain();
+  if (warp == 0) tmem_dealloc(tmem_base, 512);
+}
+
+constexpr int FMHA_SMEM = (2 + 2 * KV_STAGES) * TILE_BYTES + 1024 + (int)sizeof(FmhaBarriers);
+
+int fmha_launch(emk_handle_t h, const void* q, const void* k, const void* v, void* o, int64_t B, int64_t Hq,
+                int64_t Hkv, int64_t S, int64_t D, bool token_major, int64_t ld_q, int64_t ld_k, int64_t ld_v,
+                int64_t ld_o, float scale, cudaStream_t s) {
+  if (!h || !q || !k || !v || !o) return EMK_ERR_ARG;
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || S <= 0) return EMK_ERR_SHAPE;
+  if (D != HD) {
+    EMK_SET_ERR(h, "emk_sdpa_causal_gqa_bf16: head_dim must be 128, got %lld", (long long)D);
+    return EMK_ERR_SHAPE;
+  }
+  if (Hq % Hkv != 0) {
+    EMK_SET_ERR(h, "emk_sdpa_causal_gqa_bf16: Hq (%lld) must be a multiple of Hkv (%lld)", (long long)Hq,
+                (long long)Hkv);
+    return EMK_ERR_SHAPE;
+  }
+  if (B * Hq * S > 0x7fffffffLL || B * S > 0x7fffffffLL) return EMK_ERR_SHAPE;
+  if ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)o) & 15u) != 0) return EMK_ERR_ALIGN;
+  if (token_major && ((ld_q | ld_k | ld_v | ld_o) % 8) != 0) return EMK_ERR_ALIGN;
+
+  FmhaArgs a;
+  a.o = (__nv_bfloat16*)o;
+  a.B = (int)B;
+  a.Hq = (int)Hq;
+  a.Hkv = (int)Hkv;
+  a.S = (int)S;
+  a.group = (int)(Hq / Hkv);
+  a.pairs = (a.group + 1) / 2;
+  a.nqblk = (int)((S + FM - 1) / FM);
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.status = h->status_dev;
+  a.limit_ns = h->wait_limit_ns;
+
+  CUtensorMap tq, tk, tv;
+  int rc;
+  if (!token_major) {
+    a.q_cs = 0; a.q_rb = (int)(Hq * S); a.q_rh = (int)S;
+    a.kv_cs = 0; a.kv_rb = (int)(Hkv * S); a.kv_rh = (int)S;
+    a.o_cs = 0; a.o_rb = (int)(Hq * S); a.o_rh = (int)S;
+    a.ld_o = HD;
+    rc = emk_make_tmap_2d(h, &tq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, q, HD, (uint64_t)(B * Hq * S), HD * 2, 64, FM,
+                          CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    rc = emk_make_tmap_2d(h, &tk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, k, HD, (uint64_t)(B * Hkv * S), HD * 2, 64, FN,
+                          CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    rc = emk_make_tmap_2d(h, &tv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, v, HD, (uint64_t)(B * Hkv * S), HD * 2, 64, FN,
+                          CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+  } else {
+    a.q_cs = HD; a.q_rb = (int)S; a.q_rh = 0;
+    a.kv_cs = HD; a.kv_rb = (int)S; a.kv_rh = 0;
+    a.o_cs = HD; a.o_rb = (int)S; a.o_rh = 0;
+    a.ld_o = ld_o;
+    if (ld_q < Hq * HD || ld_k < Hkv * HD || ld_v < Hkv * HD || ld_o < Hq * HD) return EMK_ERR_SHAPE;
+    rc = emk_make_tmap_2d(h, &tq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, q, (uint64_t)(Hq * HD), (uint64_t)(B * S),
+                          (uint64_t)ld_q * 2, 64, FM, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    rc = emk_make_tmap_2d(h, &tk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, k, (uint64_t)(Hkv * HD), (uint64_t)(B * S),
+                          (uint64_t)ld_k * 2, 64, FN, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    rc = emk_make_tmap_2d(h, &tv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, v, (uint64_t)(Hkv * HD), (uint64_t)(B * S),
+                          (uint64_t)ld_v * 2, 64, FN, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+  }
+
+  static bool configured[64] = {false};
+  if (h->device < 64 && !configured[h->device]) {
+    EMK_CUDA_TRY(h, cudaFuncSetAttribute(fmha_causal_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FMHA_SMEM));
+    configured[h->device] = true;
+  }
+  const int64_t grid = (int64_t)a.nqblk * B * Hkv * a.pairs;
+  if (grid > 0x7fffffffLL) return EMK_ERR_SHAPE;
+  fmha_causal_kernel<<<(unsigned)grid, FMHA_THREADS, FMHA_SMEM, s>>>(tq, tk, tv, a);
+  EMK_LAUNCH_CHECK(h);
+  return EMK_OK;
+}
+
+}  // namespace
+
+extern "C" int emk_sdpa_causal_gqa_bf16(emk_handle_t h, const void* q, const void* k, const void* v, void* o,
+                                        int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, float scale,
+                                        emk_stream_t stream) {
+  return fmha_launch(h, q, k, v, o, B, Hq, Hkv, S, D, false, 0, 0, 0, 0, scale, (cudaStream_t)stream);
+}
+
+extern "C" int emk_sdpa_causal_gqa_bf16_tok(emk_handle_t h, const void* q, const void* k, const void* v, void* o,
+                                            int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int64_t ld_q,
+                                            int64_t ld_k, int64_t ld_v, int64_t ld_o, float scale,
+                                            emk_stream_t stream) {
+  return fmha_launch(h, q, k, v, o, B, Hq, Hkv, S, D, true, ld_q, ld_k, ld_v, ld_o, scale, (cudaStream_t)stream);
+}

@@ -1,0 +1,157 @@
+// CUDA-core GEMM with the same arguments and epilogues as the tensor-core path. Two uses: operand shapes the TMA
+// path cannot take (K or N not a multiple of 8), and an independent device-side check of the tcgen05 kernels in the
+// tests (the reference keeps the same triangulation idea: staged paths are asserted equal to the direct path,
+// tests/compiler/e2e/test_matmul_coverage.py:300,938-1068).
+#include "emk_common.cuh"
+
+namespace {
+
+using namespace emk;
+
+__device__ __forceinline__ float simt_dot(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                                          int64_t m, int64_t n, int64_t N, int64_t K, int wl) {
+  float acc = 0.f;
+  const __nv_bfloat16* xr = x + m * K;
+  if (wl == EMK_W_NK) {
+    const __nv_bfloat16* wr = w + n * K;
+    for (int64_t k = 0; k < K; ++k) acc = fmaf(__bfloat162float(xr[k]), __bfloat162float(wr[k]), acc);
+  } else {
+    for (int64_t k = 0; k < K; ++k) acc = fmaf(__bfloat162float(xr[k]), __bfloat162float(w[k * N + n]), acc);
+  }
+  return acc;
+}
+
+__global__ void __launch_bounds__(256) gemm_simt_kernel(const __nv_bfloat16* __restrict__ x,
+                                                        const __nv_bfloat16* __restrict__ w,
+                                                        const __nv_bfloat16* __restrict__ residual,
+                                                        __nv_bfloat16* __restrict__ y, int64_t M, int64_t N,
+                                                        int64_t K, int wl, int epi) {
+  const int64_t ncols_out = (epi == EMK_EPI_SWIGLU) ? N / 2 : N;
+  const int64_t total = M * ncols_out;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t m = i / ncols_out, j = i % ncols_out;
+    float out;
+    if (epi == EMK_EPI_SWIGLU) {
+      const float gate = bf16_round(simt_dot(x, w, m, 2 * j, N, K, wl));
+      const float up = bf16_round(simt_dot(x, w, m, 2 * j + 1, N, K, wl));
+      out = bf16_round(gate / (1.0f + __expf(-gate))) * up;
+    } else {
+      const float acc = simt_dot(x, w, m, j, N, K, wl);
+      if (epi == EMK_EPI_RESIDUAL) out = bf16_round(acc) + __bfloat162float(residual[m * N + j]);
+      else if (epi == EMK_EPI_BIAS) out = acc + __bfloat162float(residual[j]);
+      else out = acc;
+    }
+    y[i] = __float2bfloat16_rn(out);
+  }
+}
+
+
+// Generic attention on CUDA cores: one warp per (batch, query head, query row), online softmax in fp32, any head_dim
+// up to 256, causal or full, fp32 or bf16 operands. Covers SdpaOp shapes the tensor-core kernel does not take and
+// serves the tests as an independent device-side check of it.
+template <typename T>
+__device__ __forceinline__ float ld_as_float(const T* p);
+template <>
+__device__ __forceinline__ float ld_as_float<float>(const float* p) { return *p; }
+template <>
+__device__ __forceinline__ float ld_as_float<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <typename T>
+__device__ __forceinline__ void st_from_float(T* p, float v);
+template <>
+__device__ __forceinline__ void st_from_float<float>(float* p, float v) { *p = v; }
+template <>
+__device__ __forceinline__ void st_from_float<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+template <typename T>
+__global__ void __launch_bounds__(256) sdpa_simt_kernel(const T* __restrict__ q, const T* __restrict__ k,
+                                                        const T* __restrict__ v, T* __restrict__ o, int64_t B,
+                                                        int64_t Hq, int64_t Hkv, int64_t Sq, int64_t Skv, int D,
+                                                        float scale, int causal) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row_id = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row_id >= B * Hq * Sq) return;
+  const int64_t i = row_id % Sq;
+  const int64_t hq = (row_id / Sq) % Hq;
+  const int64_t b = row_id / (Sq * Hq);
+  const int64_t hkv = hq / (Hq / Hkv);
+  const T* qr = q + row_id * D;
+  const T* kb = k + (b * Hkv + hkv) * Skv * D;
+  const T* vb = v + (b * Hkv + hkv) * Skv * D;
+  float qv[8], acc[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const int d = lane + 32 * e;
+    qv[e] = d < D ? ld_as_float<T>(qr + d) : 0.f;
+    acc[e] = 0.f;
+  }
+  float m = -INFINITY, l = 0.f;
+  // causal: torch aligns the mask to the top-left corner (key j visible to query i iff j <= i)
+  const int64_t jend = causal ? (i + 1 < Skv ? i + 1 : Skv) : Skv;
+  for (int64_t j = 0; j < jend; ++j) {
+    float dot = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int d = lane + 32 * e;
+      if (d < D) dot = fmaf(qv[e], ld_as_float<T>(kb + j * D + d), dot);
+    }
+    dot = warp_sum(dot) * scale;
+    const float m_new = fmaxf(m, dot);
+    const float alpha = expf(m - m_new);
+    const float p = expf(dot - m_new);
+    l = l * alpha + p;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int d = lane + 32 * e;
+      if (d < D) acc[e] = acc[e] * alpha + p * ld_as_float<T>(vb + j * D + d);
+    }
+    m = m_new;
+  }
+  const float inv = 1.0f / l;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const int d = lane + 32 * e;
+    if (d < D) st_from_float<T>(o + row_id * D + d, acc[e] * inv);
+  }
+}
+
+}  // namespace
+
+extern "C" int emk_linear_bf16_simt(emk_handle_t h, const void* x, const void* w, const void* residual, void* y,
+                                    int64_t M, int64_t N, int64_t K, int wlayout, int epilogue, emk_stream_t stream) {
+  if (!h || !x || !w || !y) return EMK_ERR_ARG;
+  if (M <= 0 || N <= 0 || K <= 0) return EMK_ERR_SHAPE;
+  if (wlayout != EMK_W_NK && wlayout != EMK_W_KN) return EMK_ERR_ARG;
+  if (epilogue < EMK_EPI_NONE || epilogue > EMK_EPI_BIAS) return EMK_ERR_ARG;
+  if ((epilogue == EMK_EPI_RESIDUAL || epilogue == EMK_EPI_BIAS) && !residual) return EMK_ERR_ARG;
+  if (epilogue == EMK_EPI_SWIGLU && (N % 2) != 0) return EMK_ERR_SHAPE;
+  const int64_t total = M * ((epilogue == EMK_EPI_SWIGLU) ? N / 2 : N);
+  int64_t blocks = (total + 255) / 256;
+  if (blocks > (int64_t)h->sm_count * 32) blocks = (int64_t)h->sm_count * 32;
+  gemm_simt_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)residual, (__nv_bfloat16*)y, M, N, K,
+      wlayout, epilogue);
+  EMK_LAUNCH_CHECK(h);
+  return EMK_OK;
+}
+
+extern "C" int emk_sdpa_simt(emk_handle_t h, const void* q, const void* k, const void* v, void* o, int64_t B,
+                             int64_t Hq, int64_t Hkv, int64_t Sq, int64_t Skv, int64_t D, float scale, int causal,
+                             int dtype, emk_stream_t stream) {
+  if (!h || !q || !k || !v || !o) return EMK_ERR_ARG;
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || Sq <= 0 || Skv <= 0 || D <= 0 || D > 256 || Hq % Hkv != 0) return EMK_ERR_SHAPE;
+  const int64_t rows = B * Hq * Sq;
+  const int64_t blocks = (rows + 7) / 8;
+  if (blocks > 0x7fffffffLL) return EMK_ERR_SHAPE;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == EMK_F32)
+    sdpa_simt_kernel<float><<<(unsigned)blocks, 256, 0, s>>>((const float*)q, (const float*)k, (const float*)v,
+                                                             (float*)o, B, Hq, Hkv, Sq, Skv, (int)D, scale, causal);
+  else if (dtype == EMK_BF16)
+    sdpa_simt_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, s>>>(
+        (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (__nv_bfloat16*)o, B, Hq, Hkv, Sq,
+        Skv, (int)D, scale, causal);
+  else
+    return EMK_ERR_DTYPE;
+  EMK_LAUNCH_CHECK(h);
+  return EMK_OK;
+}

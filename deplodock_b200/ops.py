@@ -1,0 +1,250 @@
+"""Torch-tensor front end of the C-ABI kernels: validates tensors, passes raw device pointers and the current CUDA
+stream to ``libemk.so``. PyTorch is used only for device memory and streams; every computation below is one call into
+the library (no eager fallback).
+
+Each function names the reference Torch-IR op it stands for (``emmy/compiler/ir/frontend/ir.py``).
+"""
+
+from __future__ import annotations
+
+import math
+from ctypes import c_void_p
+
+import torch
+
+from deplodock_b200 import cabi
+
+_handles: dict[int, cabi.Handle] = {}
+
+
+def handle(device: int | None = None) -> cabi.Handle:
+    """The library handle of ``device`` (default: torch's current CUDA device), created on first use."""
+    if not torch.cuda.is_available():
+        raise RuntimeError("deplodock_b200 kernels need a CUDA device (sm_100a); there is no CPU fallback")
+    if device is None:
+        device = torch.cuda.current_device()
+    h = _handles.get(device)
+    if h is None:
+        with torch.cuda.device(device):
+            h = cabi.Handle(device)
+        _handles[device] = h
+    return h
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: torch.Tensor | None) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _check_cuda_contig(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise ValueError("expected CUDA tensors")
+        if not t.is_contiguous():
+            raise ValueError("expected contiguous tensors")
+
+
+_DTYPES = {torch.float32: cabi.EMK_F32, torch.bfloat16: cabi.EMK_BF16}
+
+
+def _dtype_token(t: torch.Tensor) -> int:
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise TypeError(f"unsupported dtype {t.dtype}; the kernels take float32 and bfloat16") from None
+
+
+def device_status() -> None:
+    """Synchronise the current stream and raise if a kernel recorded an expired wait or a launch error."""
+    handle().device_status(torch.cuda.current_stream().cuda_stream)
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, out: torch.Tensor | None = None) -> torch.Tensor:
+    """RmsNormOp (``ir/frontend/ir.py:296-312``) over the last axis."""
+    _check_cuda_contig(x, weight, out)
+    if weight.dtype != x.dtype or weight.numel() != x.shape[-1]:
+        raise ValueError("weight must be a vector of the row length with the dtype of x")
+    y = torch.empty_like(x) if out is None else out
+    cols = x.shape[-1]
+    rows = x.numel() // cols
+    h = handle()
+    h.check(h.lib.emk_rmsnorm(h.ptr, _ptr(x), _ptr(weight), _ptr(y), rows, cols, float(eps), _dtype_token(x),
+                              _stream()), "emk_rmsnorm")
+    return y
+
+
+def softmax_lastdim(x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """SoftmaxOp(axis=-1) (``ir/frontend/ir.py:343-358``)."""
+    _check_cuda_contig(x, out)
+    y = torch.empty_like(x) if out is None else out
+    cols = x.shape[-1]
+    rows = x.numel() // cols
+    h = handle()
+    h.check(h.lib.emk_softmax_lastdim(h.ptr, _ptr(x), _ptr(y), rows, cols, _dtype_token(x), _stream()),
+            "emk_softmax_lastdim")
+    return y
+
+
+def _linear_common(fn_name: str, x, w, *, residual, bias, swiglu, w_is_kn, out):
+    _check_cuda_contig(x, w, residual, bias, out)
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise TypeError("linear expects bfloat16 operands")
+    K = x.shape[-1]
+    M = x.numel() // K
+    if w_is_kn:
+        if w.shape[0] != K:
+            raise ValueError("weight [K,N] does not match x")
+        N = w.shape[1]
+    else:
+        if w.shape[1] != K:
+            raise ValueError("weight [N,K] does not match x")
+        N = w.shape[0]
+    if sum(v is not None and v is not False for v in (residual, bias, swiglu or None)) > 1:
+        raise ValueError("choose at most one of residual / bias / swiglu")
+    epi, extra = cabi.EMK_EPI_NONE, None
+    n_out = N
+    if residual is not None:
+        epi, extra = cabi.EMK_EPI_RESIDUAL, residual
+    elif bias is not None:
+        epi, extra = cabi.EMK_EPI_BIAS, bias
+    elif swiglu:
+        epi, n_out = cabi.EMK_EPI_SWIGLU, N // 2
+    y = torch.empty(*x.shape[:-1], n_out, dtype=torch.bfloat16, device=x.device) if out is None else out
+    h = handle()
+    fn = getattr(h.lib, fn_name)
+    h.check(fn(h.ptr, _ptr(x), _ptr(w), _ptr(extra), _ptr(y), M, N, K,
+               cabi.EMK_W_KN if w_is_kn else cabi.EMK_W_NK, epi, _stream()), fn_name)
+    return y
+
+
+def linear(x, w, *, residual=None, bias=None, swiglu=False, w_is_kn=False, out=None) -> torch.Tensor:
+    """LinearOp ``x @ w.T`` (``ir/frontend/ir.py:202-217``) or, with ``w_is_kn``, MatmulOp ``x @ w`` (``:221-237``), on
+    the tcgen05 tensor cores, with an optional fused epilogue."""
+    return _linear_common("emk_linear_bf16", x, w, residual=residual, bias=bias, swiglu=swiglu, w_is_kn=w_is_kn,
+                          out=out)
+
+
+def linear_simt(x, w, *, residual=None, bias=None, swiglu=False, w_is_kn=False, out=None) -> torch.Tensor:
+    """Same contract on CUDA cores: for K or N not a multiple of 8, and as a cross-check in the tests."""
+    return _linear_common("emk_linear_bf16_simt", x, w, residual=residual, bias=bias, swiglu=swiglu, w_is_kn=w_is_kn,
+                          out=out)
+
+
+def linear_w8(x: torch.Tensor, w_e4m3: torch.Tensor, scale: torch.Tensor, out=None) -> torch.Tensor:
+    """bf16 activations times e4m3 weights ``[N,K]`` with one fp32 scale per output channel."""
+    _check_cuda_contig(x, w_e4m3, scale, out)
+    if x.dtype != torch.bfloat16 or w_e4m3.dtype != torch.float8_e4m3fn or scale.dtype != torch.float32:
+        raise TypeError("linear_w8 expects bfloat16 x, float8_e4m3fn weights and float32 scales")
+    K = x.shape[-1]
+    M = x.numel() // K
+    N = w_e4m3.shape[0]
+    if w_e4m3.shape[1] != K or scale.numel() != N:
+        raise ValueError("weight/scale shapes do not match x")
+    y = torch.empty(*x.shape[:-1], N, dtype=torch.bfloat16, device=x.device) if out is None else out
+    h = handle()
+    h.check(h.lib.emk_linear_bf16_w8(h.ptr, _ptr(x), _ptr(w_e4m3), _ptr(scale), _ptr(y), M, N, K, _stream()),
+            "emk_linear_bf16_w8")
+    return y
+
+
+def sdpa_causal_gqa(q, k, v, scale: float | None = None, out=None) -> torch.Tensor:
+    """SdpaOp(is_causal=True) with grouped KV heads (``ir/frontend/ir.py:241-275``); q ``[B,Hq,S,128]``, k/v
+    ``[B,Hkv,S,128]`` bf16, on the tcgen05 flash kernel."""
+    _check_cuda_contig(q, k, v, out)
+    if not (q.dtype == k.dtype == v.dtype == torch.bfloat16):
+        raise TypeError("sdpa_causal_gqa expects bfloat16 operands")
+    B, Hq, S, D = q.shape
+    Hkv = k.shape[1]
+    if k.shape != (B, Hkv, S, D) or v.shape != (B, Hkv, S, D):
+        raise ValueError("k/v shapes do not match q")
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    o = torch.empty_like(q) if out is None else out
+    h = handle()
+    h.check(h.lib.emk_sdpa_causal_gqa_bf16(h.ptr, _ptr(q), _ptr(k), _ptr(v), _ptr(o), B, Hq, Hkv, S, D, float(scale),
+                                           _stream()), "emk_sdpa_causal_gqa_bf16")
+    return o
+
+
+def sdpa_causal_gqa_tok(qkv: torch.Tensor, B: int, S: int, Hq: int, Hkv: int, out: torch.Tensor,
+                        scale: float | None = None) -> torch.Tensor:
+    """Same attention reading the fused token-major projection ``qkv [B*S, (Hq+2*Hkv)*128]`` in place and writing
+    ``out [B*S, Hq*128]`` — the layout of the traced layer before its transposes."""
+    _check_cuda_contig(qkv, out)
+    D = 128
+    ld = qkv.shape[-1]
+    if ld != (Hq + 2 * Hkv) * D or qkv.numel() != B * S * ld or out.numel() != B * S * Hq * D:
+        raise ValueError("qkv/out shapes do not match B, S, Hq, Hkv")
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    esz = qkv.element_size()
+    h = handle()
+    qp = qkv.data_ptr()
+    h.check(h.lib.emk_sdpa_causal_gqa_bf16_tok(
+        h.ptr, c_void_p(qp), c_void_p(qp + Hq * D * esz), c_void_p(qp + (Hq + Hkv) * D * esz), _ptr(out), B, Hq, Hkv,
+        S, D, ld, ld, ld, Hq * D, float(scale), _stream()), "emk_sdpa_causal_gqa_bf16_tok")
+    return out
+
+
+def sdpa_simt(q, k, v, causal: bool, scale: float | None = None) -> torch.Tensor:
+    """SdpaOp on CUDA cores: fp32 or bf16, head_dim <= 256, causal or full."""
+    _check_cuda_contig(q, k, v)
+    B, Hq, Sq, D = q.shape
+    Hkv, Skv = k.shape[1], k.shape[2]
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    o = torch.empty_like(q)
+    h = handle()
+    h.check(h.lib.emk_sdpa_simt(h.ptr, _ptr(q), _ptr(k), _ptr(v), _ptr(o), B, Hq, Hkv, Sq, Skv, D, float(scale),
+                                int(bool(causal)), _dtype_token(q), _stream()), "emk_sdpa_simt")
+    return o
+
+
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, out=None) -> torch.Tensor:
+    """GatherOp of the embedding table (bf16 rows) by int64 token ids."""
+    _check_cuda_contig(table, ids, out)
+    if table.dtype != torch.bfloat16 or ids.dtype != torch.int64:
+        raise TypeError("embed_gather expects a bfloat16 table and int64 ids")
+    vocab, hidden = table.shape
+    tokens = ids.numel()
+    y = torch.empty(tokens, hidden, dtype=table.dtype, device=table.device) if out is None else out
+    h = handle()
+    h.check(h.lib.emk_embed_gather(h.ptr, _ptr(table), _ptr(ids), _ptr(y), tokens, hidden, vocab, _stream()),
+            "emk_embed_gather")
+    return y
+
+
+def qknorm_rope_(qkv, q_weight, k_weight, cos, sin, S: int, Hq: int, Hkv: int, eps: float = 1e-6) -> torch.Tensor:
+    """In place on the fused projection ``[T,(Hq+2Hkv)*128]``: per-head RMSNorm of q and k, then rotate-half RoPE."""
+    _check_cuda_contig(qkv, q_weight, k_weight, cos, sin)
+    if qkv.dtype != torch.bfloat16 or cos.dtype != torch.float32 or sin.dtype != torch.float32:
+        raise TypeError("qknorm_rope_ expects bfloat16 qkv and float32 cos/sin tables")
+    tokens = qkv.numel() // qkv.shape[-1]
+    if qkv.shape[-1] != (Hq + 2 * Hkv) * 128 or cos.shape[-2:] != (S, 128) or tokens % S != 0:
+        raise ValueError("qkv/cos shapes do not match S, Hq, Hkv")
+    h = handle()
+    h.check(h.lib.emk_qknorm_rope(h.ptr, _ptr(qkv), _ptr(q_weight), _ptr(k_weight), _ptr(cos), _ptr(sin), tokens, S,
+                                  Hq, Hkv, float(eps), _stream()), "emk_qknorm_rope")
+    return qkv
+
+
+def pool_norm_l2(hidden_states, weight, B: int, S: int, eps: float = 1e-6, out=None) -> torch.Tensor:
+    """Last-token pooling, final RMSNorm and L2 normalisation: ``[B*S, hidden]`` bf16 -> ``[B, hidden]`` fp32."""
+    _check_cuda_contig(hidden_states, weight, out)
+    hidden = hidden_states.shape[-1]
+    y = torch.empty(B, hidden, dtype=torch.float32, device=hidden_states.device) if out is None else out
+    h = handle()
+    h.check(h.lib.emk_pool_norm_l2(h.ptr, _ptr(hidden_states), _ptr(weight), _ptr(y), B, S, hidden, float(eps),
+                                   _stream()), "emk_pool_norm_l2")
+    return y
+
+
+def selftest_wait_expiry(limit_ms: int = 20) -> None:
+    """Launch the bounded-wait self test; the following :func:`device_status` raises ``HungKernelError``."""
+    h = handle()
+    h.check(h.lib.emk_selftest_wait_expiry(h.ptr, int(limit_ms), _stream()), "emk_selftest_wait_expiry")

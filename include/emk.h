@@ -1,0 +1,164 @@
+/*
+ * emk.h — C ABI of the B200 (sm_100a) kernel backend for emmy's compiler hot path.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream; none of them allocates,
+ * frees or synchronises (except where stated), so every compute call can be captured in a CUDA graph.
+ * All calls return an emk_status_t (0 = success). Paths in the comments are relative to the root of the
+ * reference project (cloudrift-ai/deplodock, Python package "emmy").
+ *
+ * What this interface replaces: the reference lowers each fused Torch-IR op to generated CUDA text
+ * (emmy/compiler/ir/kernel/render.py:407-515, emmy/compiler/pipeline/passes/lowering/cuda/010_lower_kernelop.py:63-112),
+ * compiles it with nvcc at run time (emmy/compiler/backend/cuda/nvcc.py:118-177) and launches it through cupy
+ * (emmy/compiler/backend/cuda/program.py:394-424, :960-1035). Here each op is one hand-written kernel behind one
+ * export; the Python Backend shim (deplodock_b200/backend.py) binds them with ctypes.
+ */
+#ifndef EMK_H_
+#define EMK_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define EMK_VERSION 100
+
+/* Status codes. The Python shim maps them onto the exception types the reference raises
+ * (emmy/compiler/backend/cuda/program.py:379-384 ValueError, :525 HungKernelError, :1027-1031 RuntimeError). */
+typedef enum {
+  EMK_OK = 0,
+  EMK_ERR_SHAPE = 1,     /* a dimension is zero/negative or unsupported by the kernel          */
+  EMK_ERR_DTYPE = 2,     /* unknown dtype token                                                 */
+  EMK_ERR_ALIGN = 3,     /* pointer or leading dimension not aligned as the kernel requires     */
+  EMK_ERR_WORKSPACE = 4, /* caller-provided workspace too small                                 */
+  EMK_ERR_CUDA = 5,      /* a CUDA runtime/driver call failed; see emk_last_error               */
+  EMK_ERR_TIMEOUT = 6,   /* a bounded device-side wait ran out (read back by emk_device_status) */
+  EMK_ERR_ARG = 7,       /* null pointer / bad enum                                             */
+  EMK_ERR_LIMIT = 8      /* size beyond a stated fixed maximum of the entry point               */
+} emk_status_t;
+
+/* dtype tokens: same names as the reference's graph dtypes (emmy/compiler/dtype.py:61-69). */
+typedef enum { EMK_F32 = 0, EMK_BF16 = 1, EMK_F16 = 2 } emk_dtype_t;
+
+/* Layout of the second GEMM operand.
+ *   EMK_W_NK: W is [N,K] row-major, y = x·Wᵀ   — LinearOp (emmy/compiler/ir/frontend/ir.py:202-217).
+ *   EMK_W_KN: W is [K,N] row-major, y = x·W    — MatmulOp (emmy/compiler/ir/frontend/ir.py:221-237). */
+typedef enum { EMK_W_NK = 0, EMK_W_KN = 1 } emk_wlayout_t;
+
+/* Fused GEMM epilogues (the reference folds these as fragment epilogues, emmy/compiler/ir/kernel/ir.py:1266-1288).
+ *   EMK_EPI_NONE     y = bf16(acc)
+ *   EMK_EPI_RESIDUAL y = bf16(bf16(acc) + residual)          residual is [M,N] bf16
+ *   EMK_EPI_SWIGLU   W rows interleaved (gate_j, up_j); y[M,N/2] = bf16(bf16(silu(g)) * u), g,u = bf16(acc)
+ *   EMK_EPI_BIAS     y = bf16(acc + bias[n])                  bias is [N] bf16 passed as `residual` */
+typedef enum { EMK_EPI_NONE = 0, EMK_EPI_RESIDUAL = 1, EMK_EPI_SWIGLU = 2, EMK_EPI_BIAS = 3 } emk_epilogue_t;
+
+typedef struct emk_handle_s* emk_handle_t;
+typedef void* emk_stream_t; /* a cudaStream_t */
+
+/* Library identity and error text. Replaces nothing in the reference (bookkeeping for the binding). */
+int emk_version(void);
+const char* emk_status_string(int status);
+
+/* Per-device handle: holds the device id, SM count, the driver entry point used to encode TMA tensor maps
+ * (the reference calls cuTensorMapEncodeTiled through ctypes, emmy/compiler/backend/cuda/_tma.py:91-170) and a
+ * host-mapped status word that kernels write when a bounded wait runs out. */
+int emk_create(int device, emk_handle_t* out);
+int emk_destroy(emk_handle_t h);
+const char* emk_last_error(emk_handle_t h);
+
+/* Synchronises `stream`, then returns EMK_ERR_TIMEOUT if any kernel since the last call recorded an expired wait
+ * (and clears the word), EMK_ERR_CUDA on a launch/runtime error, else EMK_OK. Same role as the reference's per-launch
+ * polling watchdog `_wait_for_event` (emmy/compiler/backend/cuda/program.py:574-605). */
+int emk_device_status(emk_handle_t h, emk_stream_t stream);
+
+/* Limit, in milliseconds, of every device-side mbarrier wait (default 2000). */
+int emk_set_wait_limit_ms(emk_handle_t h, int ms);
+
+/* RMSNorm over the last axis: y = x * rsqrt(mean(x^2) + eps) * w, statistics in fp32.
+ * Replaces the emitted k_rms_norm_<hash> kernel (RmsNormOp, emmy/compiler/ir/frontend/ir.py:296-312;
+ * decomposition emmy/compiler/pipeline/passes/frontend/decomposition/080_rms_norm.py:17-60).
+ * x,y: [rows, cols] of `dtype` (EMK_F32 or EMK_BF16), row-major; w: [cols] of `dtype`. */
+int emk_rmsnorm(emk_handle_t h, const void* x, const void* w, void* y, int64_t rows, int64_t cols, float eps,
+                int dtype, emk_stream_t stream);
+
+/* Softmax over the last axis, fp32 statistics, one read and one write of the tensor.
+ * Replaces the emitted k_softmax_<hash> kernel (SoftmaxOp, emmy/compiler/ir/frontend/ir.py:343-358;
+ * emmy/compiler/pipeline/passes/lowering/tile/_softmax.py:123). -inf entries give 0; a fully -inf row gives NaN
+ * exactly as torch does. dtype EMK_F32 or EMK_BF16. */
+int emk_softmax_lastdim(emk_handle_t h, const void* x, void* y, int64_t rows, int64_t cols, int dtype,
+                        emk_stream_t stream);
+
+/* y[M,N] = x[M,K] · W (+ epilogue), bf16 operands, fp32 accumulation in tensor memory, bf16 output.
+ * Replaces the emitted k_linear_<hash> kernels (LinearOp/MatmulOp above; TMA ring + mma.sync lowering in
+ * emmy/compiler/pipeline/passes/lowering/kernel/_stage.py:345-450 and _atom.py:598-715).
+ * K and N must be multiples of 8 (16-byte rows for TMA and vector stores); otherwise EMK_ERR_ALIGN.
+ * `residual` is the [M,N] bf16 addend (EMK_EPI_RESIDUAL), the [N] bias (EMK_EPI_BIAS) or NULL.
+ * For EMK_EPI_SWIGLU, y is [M,N/2]. */
+int emk_linear_bf16(emk_handle_t h, const void* x, const void* w, const void* residual, void* y, int64_t M,
+                    int64_t N, int64_t K, int wlayout, int epilogue, emk_stream_t stream);
+
+/* Same contraction with e4m3 weights [N,K] and one fp32 scale per output channel:
+ * y[m,n] = bf16( scale[n] * sum_k x[m,k] * float(Wq[n,k]) ). The weight tile is converted to bf16 inside the
+ * tensor-core main loop. No counterpart kernel exists in the reference (it has no fp8 path). */
+int emk_linear_bf16_w8(emk_handle_t h, const void* x, const void* w_e4m3, const float* scale, void* y, int64_t M,
+                       int64_t N, int64_t K, emk_stream_t stream);
+
+/* Causal grouped-query attention, bf16, head_dim 128: O = softmax(Q·Kᵀ·scale + causal)·V with fp32 online softmax.
+ * Replaces the emitted k_scaled_dot_product_attention kernel (SdpaOp, emmy/compiler/ir/frontend/ir.py:241-275;
+ * decomposition .../decomposition/010_sdpa.py:52-141; flash lowering .../lowering/kernel/_twist.py:229).
+ * q,o: [B,Hq,S,128]; k,v: [B,Hkv,S,128]; all contiguous bf16. Hq must be a multiple of Hkv. */
+int emk_sdpa_causal_gqa_bf16(emk_handle_t h, const void* q, const void* k, const void* v, void* o, int64_t B,
+                             int64_t Hq, int64_t Hkv, int64_t S, int64_t D, float scale, emk_stream_t stream);
+
+/* Embedding row gather: out[t,:] = table[ids[t],:] (bf16 rows of `hidden` elements, hidden*2 a multiple of 16).
+ * Replaces the GatherOp kernel of the traced trunk (emmy/compiler/trace/huggingface.py:17-186). ids are int64. */
+int emk_embed_gather(emk_handle_t h, const void* table, const int64_t* ids, void* out, int64_t tokens,
+                     int64_t hidden, int64_t vocab, emk_stream_t stream);
+
+/* Same attention over token-major operands, so the fused QKV projection output can be consumed without a transpose:
+ * q[(b*S+s)*ld_q + h*128 + d], likewise k, v (head index over Hkv) and o; ld_* are row pitches in elements
+ * (multiples of 8). This is the layout of the traced layer before its transpose(1,2) nodes. */
+int emk_sdpa_causal_gqa_bf16_tok(emk_handle_t h, const void* q, const void* k, const void* v, void* o, int64_t B,
+                                 int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int64_t ld_q, int64_t ld_k,
+                                 int64_t ld_v, int64_t ld_o, float scale, emk_stream_t stream);
+
+/* In place on the fused QKV projection output [T, (Hq+2*Hkv)*128] (T tokens, bf16, position of token t = t % S):
+ * per-head RMSNorm (weights qw, kw [128] bf16, eps) on the Hq query heads and Hkv key heads, then rotate-half RoPE
+ * with cos/sin tables [S,128] fp32; the value heads are left untouched. Replaces the k_mean_linear_reduce_* q/k-norm
+ * kernels and the k_cat_slice_transpose_unsqueeze_pointwise_* RoPE kernel of the reference's lowering of the traced
+ * layer (traced pattern: emmy/compiler/trace/huggingface.py:17-186). */
+int emk_qknorm_rope(emk_handle_t h, void* qkv, const void* qw, const void* kw, const float* cos_table,
+                    const float* sin_table, int64_t tokens, int64_t S, int64_t Hq, int64_t Hkv, float eps,
+                    emk_stream_t stream);
+
+/* Last-token pooling + final RMSNorm + L2 normalisation: for each sequence b, takes row (b*S + S-1) of hidden
+ * [B*S, hidden] (bf16), applies RMSNorm(w, eps) rounding to bf16 as the eager module does, then divides by its L2
+ * norm; writes fp32 [B, hidden]. Stands for the final norm of the trunk plus the pooler the reference leaves to
+ * vLLM (emmy/serving/vllm_model.py:50-58). */
+int emk_pool_norm_l2(emk_handle_t h, const void* hidden_states, const void* w, float* out, int64_t B, int64_t S,
+                     int64_t hidden, float eps, emk_stream_t stream);
+
+/* Plain CUDA-core GEMM used for operand shapes the tensor-core path rejects (K or N not a multiple of 8) and by
+ * the tests as an independent check of the tcgen05 kernels. Same arguments and epilogues as emk_linear_bf16. */
+int emk_linear_bf16_simt(emk_handle_t h, const void* x, const void* w, const void* residual, void* y, int64_t M,
+                         int64_t N, int64_t K, int wlayout, int epilogue, emk_stream_t stream);
+
+/* Generic attention on CUDA cores (one warp per query row, fp32 online softmax): any head_dim <= 256, causal or
+ * full, EMK_F32 or EMK_BF16, q/o [B,Hq,Sq,D], k/v [B,Hkv,Skv,D] contiguous. Takes the SdpaOp shapes the tensor-core
+ * kernel rejects (fp32 inputs, head_dim != 128, non-causal: the reference's scalar flash tier,
+ * emmy/compiler/pipeline/passes/lowering/kernel/_factor.py) and is the device-side cross-check in the tests. */
+int emk_sdpa_simt(emk_handle_t h, const void* q, const void* k, const void* v, void* o, int64_t B, int64_t Hq,
+                  int64_t Hkv, int64_t Sq, int64_t Skv, int64_t D, float scale, int causal, int dtype,
+                  emk_stream_t stream);
+
+/* Launches a one-warp kernel that waits on an mbarrier nobody arrives at, with the given limit; the kernel returns
+ * by itself and records the expiry, so the next emk_device_status returns EMK_ERR_TIMEOUT. Exercises the same
+ * bounded-wait code the GEMM and attention kernels use (the reference's counterpart is the host watchdog test
+ * tests/compiler/backend/test_hung_kernel_watchdog.py, which needs a kernel that never ends; this one always ends). */
+int emk_selftest_wait_expiry(emk_handle_t h, int limit_ms, emk_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EMK_H_ */
