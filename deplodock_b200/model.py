@@ -1,0 +1,183 @@
+"""Qwen3-Embedding-shaped forward on the emk kernels: token ids -> pooled, L2-normalised embeddings.
+
+The reference serves this model one sequence per forward: ``EmmyForwardRunner`` traces the HF trunk with
+``build_full_model_wrapper`` (``emmy/compiler/trace/huggingface.py:17-186``), compiles it into one program and replays
+a captured CUDA graph per sequence (``emmy/serving/runner.py:204-236``); vLLM then pools the last token and normalises
+(``emmy/serving/vllm_model.py:50-58``). The traced layer is GatherOp, five RMSNorm chains, seven LinearOps, a RoPE
+chain, repeat_kv, SdpaOp with an additive causal mask, and a SwiGLU — 18 generated kernels per layer.
+
+Here the same dataflow is a fixed plan of eight launches per layer over a whole batch of sequences:
+
+    rmsnorm -> GEMM(Wqkv) -> q/k-norm + RoPE (in place) -> causal GQA flash attention (token-major, no transposes)
+            -> GEMM(Wo) + residual -> rmsnorm -> GEMM(Wgate|Wup interleaved) + SwiGLU -> GEMM(Wdown) + residual
+
+and a last-token RMSNorm + L2 kernel. The whole forward is captured once in a CUDA graph and replayed. Sequences are
+independent, so a batch can be processed in chunks (``chunk_seqs``) whose activations stay resident in the 126 MB L2.
+Weights are prepared once: q/k/v projections concatenated, gate/up rows interleaved, cos/sin tables rounded to bf16
+as the eager module does.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from deplodock_b200 import ops
+
+
+@dataclass(frozen=True)
+class EmbedConfig:
+    """Trunk shape; defaults are Qwen3-Embedding-0.6B."""
+
+    vocab_size: int = 151669
+    hidden_size: int = 1024
+    intermediate_size: int = 3072
+    num_hidden_layers: int = 28
+    num_attention_heads: int = 16
+    num_key_value_heads: int = 8
+    head_dim: int = 128
+    rms_norm_eps: float = 1e-6
+    rope_theta: float = 1e6
+
+    @classmethod
+    def from_any(cls, cfg) -> "EmbedConfig":
+        """Accepts any object with these attribute names (an HF ``Qwen3Config`` included)."""
+        return cls(**{f: getattr(cfg, f) for f in cls.__dataclass_fields__})  # type: ignore[attr-defined]
+
+    def linear_flops_per_token(self) -> int:
+        H, I, D = self.hidden_size, self.intermediate_size, self.head_dim
+        nq, nkv = self.num_attention_heads, self.num_key_value_heads
+        per_layer = H * (nq + 2 * nkv) * D + nq * D * H + 3 * H * I
+        return 2 * per_layer * self.num_hidden_layers
+
+    def attention_flops(self, batch: int, seq: int) -> int:
+        """Causal-useful flops: 4 * B * Hq * D * S(S+1)/2 per layer."""
+        return self.num_hidden_layers * 4 * batch * self.num_attention_heads * self.head_dim * (seq * (seq + 1) // 2)
+
+
+def rope_tables(seq: int, head_dim: int, theta: float, device) -> tuple[torch.Tensor, torch.Tensor]:
+    """cos/sin ``[seq, head_dim]`` as HF builds them (``cat(freqs, freqs)``), rounded to bf16 like the eager bf16
+    module and stored as fp32 for the kernel."""
+    inv_freq = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.int64).float() / head_dim))
+    freqs = torch.outer(torch.arange(seq, dtype=torch.float32), inv_freq)
+    emb = torch.cat([freqs, freqs], dim=-1)
+    cos = emb.cos().to(torch.bfloat16).float().contiguous().to(device)
+    sin = emb.sin().to(torch.bfloat16).float().contiguous().to(device)
+    return cos, sin
+
+
+class _LayerWeights:
+    __slots__ = ("ln1", "wqkv", "qn", "kn", "wo", "ln2", "wgu", "wdown")
+
+
+class EmbedForward:
+    """Batch forward of the trunk on one GPU. ``state_dict`` uses the HF ``Qwen3Model`` parameter names."""
+
+    #: kernel launches per layer / outside the layers, for launch accounting in the bench
+    LAUNCHES_PER_LAYER = 8
+    LAUNCHES_FIXED = 2
+
+    def __init__(self, cfg, state_dict: dict[str, torch.Tensor], *, batch: int, seq: int, device=None,
+                 chunk_seqs: int | None = None) -> None:
+        self.cfg = EmbedConfig.from_any(cfg)
+        c = self.cfg
+        if c.head_dim != 128:
+            raise ValueError("the attention kernel is built for head_dim 128")
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.batch, self.seq = int(batch), int(seq)
+        self.chunk_seqs = self.batch if not chunk_seqs else min(int(chunk_seqs), self.batch)
+        if self.batch % self.chunk_seqs != 0:
+            raise ValueError("chunk_seqs must divide the batch")
+        dev, bf = self.device, torch.bfloat16
+
+        def w(name: str) -> torch.Tensor:
+            t = state_dict[name]
+            return t.to(device=dev, dtype=bf).contiguous()
+
+        self.embed = w("embed_tokens.weight")
+        self.final_norm = w("norm.weight")
+        self.layers: list[_LayerWeights] = []
+        for i in range(c.num_hidden_layers):
+            p = f"layers.{i}."
+            lw = _LayerWeights()
+            lw.ln1 = w(p + "input_layernorm.weight")
+            lw.wqkv = torch.cat([w(p + "self_attn.q_proj.weight"), w(p + "self_attn.k_proj.weight"),
+                                 w(p + "self_attn.v_proj.weight")], dim=0).contiguous()
+            lw.qn = w(p + "self_attn.q_norm.weight")
+            lw.kn = w(p + "self_attn.k_norm.weight")
+            lw.wo = w(p + "self_attn.o_proj.weight")
+            lw.ln2 = w(p + "post_attention_layernorm.weight")
+            gate, up = w(p + "mlp.gate_proj.weight"), w(p + "mlp.up_proj.weight")
+            # rows interleaved (gate_0, up_0, gate_1, up_1, ...) so one accumulator row holds both halves of a pair
+            lw.wgu = torch.stack([gate, up], dim=1).reshape(2 * c.intermediate_size, c.hidden_size).contiguous()
+            lw.wdown = w(p + "mlp.down_proj.weight")
+            self.layers.append(lw)
+        self.cos, self.sin = rope_tables(self.seq, c.head_dim, c.rope_theta, dev)
+
+        T = self.chunk_seqs * self.seq
+        nq, nkv, D = c.num_attention_heads, c.num_key_value_heads, c.head_dim
+        self.ids = torch.zeros(self.batch, self.seq, dtype=torch.int64, device=dev)
+        self.h = torch.empty(T, c.hidden_size, dtype=bf, device=dev)
+        self.x = torch.empty(T, c.hidden_size, dtype=bf, device=dev)
+        self.qkv = torch.empty(T, (nq + 2 * nkv) * D, dtype=bf, device=dev)
+        self.attn = torch.empty(T, nq * D, dtype=bf, device=dev)
+        self.mlp = torch.empty(T, c.intermediate_size, dtype=bf, device=dev)
+        self.out = torch.empty(self.batch, c.hidden_size, dtype=torch.float32, device=dev)
+        self._graph: torch.cuda.CUDAGraph | None = None
+
+    # -----------------------------------------------------------------------------------------------------------
+    @property
+    def num_launches(self) -> int:
+        chunks = self.batch // self.chunk_seqs
+        return chunks * (self.LAUNCHES_PER_LAYER * self.cfg.num_hidden_layers + self.LAUNCHES_FIXED)
+
+    def flops(self) -> int:
+        return self.cfg.linear_flops_per_token() * self.batch * self.seq + self.cfg.attention_flops(self.batch,
+                                                                                                     self.seq)
+
+    def _forward_chunk(self, ids: torch.Tensor, out: torch.Tensor) -> None:
+        c = self.cfg
+        B, S = ids.shape
+        nq, nkv = c.num_attention_heads, c.num_key_value_heads
+        eps = c.rms_norm_eps
+        ops.embed_gather(self.embed, ids, out=self.h)
+        for lw in self.layers:
+            ops.rmsnorm(self.h, lw.ln1, eps, out=self.x)
+            ops.linear(self.x, lw.wqkv, out=self.qkv)
+            ops.qknorm_rope_(self.qkv, lw.qn, lw.kn, self.cos, self.sin, S, nq, nkv, eps)
+            ops.sdpa_causal_gqa_tok(self.qkv, B, S, nq, nkv, self.attn)
+            ops.linear(self.attn, lw.wo, residual=self.h, out=self.h)
+            ops.rmsnorm(self.h, lw.ln2, eps, out=self.x)
+            ops.linear(self.x, lw.wgu, swiglu=True, out=self.mlp)
+            ops.linear(self.mlp, lw.wdown, residual=self.h, out=self.h)
+        ops.pool_norm_l2(self.h, self.final_norm, B, S, eps, out=out)
+
+    def forward_eager(self) -> torch.Tensor:
+        """Launch the plan on the current stream from ``self.ids``; returns ``self.out`` ``[batch, hidden]`` fp32."""
+        cs = self.chunk_seqs
+        for b0 in range(0, self.batch, cs):
+            self._forward_chunk(self.ids[b0:b0 + cs], self.out[b0:b0 + cs])
+        return self.out
+
+    def capture(self) -> None:
+        """Capture the whole forward in one CUDA graph (after one eager warm-up run)."""
+        self.forward_eager()
+        torch.cuda.synchronize(self.device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self.forward_eager()
+        self._graph = g
+
+    def replay(self) -> torch.Tensor:
+        if self._graph is None:
+            self.capture()
+        self._graph.replay()
+        return self.out
+
+    def __call__(self, ids: torch.Tensor) -> torch.Tensor:
+        """Copy ``ids`` (host or device, ``[batch, seq]`` int64) into the static input buffer and run the graph."""
+        if tuple(ids.shape) != (self.batch, self.seq):
+            raise ValueError(f"expected ids of shape {(self.batch, self.seq)}, got {tuple(ids.shape)}")
+        self.ids.copy_(ids, non_blocking=True)
+        return self.replay()

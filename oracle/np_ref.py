@@ -80,9 +80,10 @@ def swiglu_mlp(x, w_gate, w_up, w_down):
     return linear(silu(linear(x, w_gate)) * linear(x, w_up), w_down)
 
 
-def embed_forward(ids, sd, cfg):
+def trunk_hidden(ids, sd, cfg):
     """fp32 numpy forward of the Qwen3-shaped trunk as the traced graph computes it (GatherOp, RMSNorm chains,
-    LinearOps, RoPE chain, SdpaOp with the additive causal mask, SwiGLU), then last-token pooling and L2 normalise.
+    LinearOps, RoPE chain, SdpaOp with the additive causal mask, SwiGLU): the final-norm hidden states ``[B,S,H]``,
+    the output of the graph ``build_full_model_wrapper`` traces (``emmy/compiler/trace/huggingface.py:17-186``).
     ``sd`` maps HF parameter names to float32 arrays. Small configurations only (pure numpy)."""
     B, S = ids.shape
     D, nq, nkv = cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads
@@ -106,6 +107,11 @@ def embed_forward(ids, sd, cfg):
         x = rms_norm(h, sd[p + "post_attention_layernorm.weight"], cfg.rms_norm_eps)
         h = h + swiglu_mlp(x, sd[p + "mlp.gate_proj.weight"], sd[p + "mlp.up_proj.weight"],
                            sd[p + "mlp.down_proj.weight"])
-    h = rms_norm(h, sd["norm.weight"], cfg.rms_norm_eps)
-    last = h[:, -1]
+    return rms_norm(h, sd["norm.weight"], cfg.rms_norm_eps)
+
+
+def embed_forward(ids, sd, cfg):
+    """Trunk, then last-token pooling and L2 normalise (the pooler the reference leaves to vLLM,
+    ``emmy/serving/vllm_model.py:50-58``)."""
+    last = trunk_hidden(ids, sd, cfg)[:, -1]
     return last / np.maximum(np.linalg.norm(last, axis=-1, keepdims=True), 1e-12)
