@@ -1,0 +1,447 @@
+"""Benchmark of the hot path on B200: the Qwen3-Embedding-0.6B-shaped forward (64 sequences x 512 tokens, bf16,
+random-init weights, uniform-random token ids), batch-sharded over N GPUs, plus the four per-kernel configurations.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--no-kernels]
+
+Prints ONE JSON line on rank 0. A step is one forward of the whole 64-sequence batch: every rank replays its captured
+CUDA graph on its shard (64/N sequences) and the pooled embeddings are all-gathered. ``value`` is sequences/s with the
+ids already resident on the device; ``e2e`` repeats the measurement through the public call with pinned host ids
+(host->device copy of the ids and device->host copy of the gathered embeddings inside the timed region).
+``roofline`` describes the dominant kernel of the step (the tcgen05 GEMM), timed with CUDA events around every
+launch of it in an extra eager pass of the same plan; ``kernels`` lists the four named kernel configurations with
+their own roofline fractions. ``cpu_baseline`` times the CPU oracle (the PyTorch-eager trunk) on a bounded sample.
+``--impl reference`` runs only that CPU arm, with all host threads.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+BATCH, SEQ = 64, 512
+METRIC, UNIT = "embed_forward_seqs_per_s", "seq/s"
+
+
+def load_peaks() -> tuple[dict, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            d = json.loads(p.read_text())
+            return {k: float(d[k]) for k in FALLBACK_PEAKS}, "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int) -> None:
+        self.gpu_index = gpu_index
+        self.rows: list[list[str]] = []
+        self.proc = None
+        self.thread = None
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+
+        def pump():
+            for line in self.proc.stdout:
+                parts = [x.strip() for x in line.split(",")]
+                if len(parts) >= 9:
+                    self.rows.append(parts)
+
+        self.thread = threading.Thread(target=pump, daemon=True)
+        self.thread.start()
+
+    def stop(self) -> dict:
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=3)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        busy = [c for c in sm if c > 0]
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------------------
+# CPU arm (the oracle, timed)
+# ------------------------------------------------------------------------------------------------------------
+def cpu_reference_sample(sd_cpu, cfg, n_seqs: int, repeats: int = 1) -> dict:
+    import torch
+
+    from oracle import cpu_ref, inputs
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    ids = inputs.token_ids(n_seqs, SEQ, cfg.vocab_size, seed=0)
+    cpu_ref.embed_forward(ids[:1, :64], cfg, sd_cpu)  # warm-up of the thread pool / kernels
+    best = math.inf
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        cpu_ref.embed_forward(ids, cfg, sd_cpu)
+        best = min(best, time.perf_counter() - t0)
+    return {"value": n_seqs / best, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{n_seqs} of {BATCH} sequences x {SEQ} tokens, eager CPU trunk, {best:.2f} s",
+            "seconds": best}
+
+
+def run_reference_arm(args) -> None:
+    """The reference's own CPU path for this workload: the PyTorch-eager trunk on the host cores."""
+    import torch
+
+    from oracle import inputs
+
+    rank = int(os.environ.get("RANK", 0))
+    if rank != 0:
+        return
+    cfg = inputs.EmbedModelConfig()
+    sd = inputs.embed_model_weights(cfg, seed=0)
+    per_step = 2
+    times = []
+    res = None
+    for i in range(args.warmup + args.steps):
+        res = cpu_reference_sample(sd, cfg, per_step)
+        if i >= args.warmup:
+            times.append(res["seconds"])
+    avg = sum(times) / len(times)
+    value = per_step / avg
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": avg * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "qwen3-embedding-0.6b-shaped forward, 64x512 tokens, last-token pool + L2",
+                   "sample_per_step": f"{per_step} sequences x {SEQ} tokens", "threads": torch.get_num_threads()},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": f"{per_step} sequences x {SEQ} tokens per step, eager CPU trunk (the module the "
+                                   "reference traces and checks against)"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------------------
+# Per-kernel configurations (rank 0, one GPU)
+# ------------------------------------------------------------------------------------------------------------
+def _graph_time_us(fn, reps: int, iters: int = 5) -> tuple[float, float]:
+    """Median and min microseconds per call of ``fn`` measured as a CUDA graph of ``reps`` back-to-back launches."""
+    import torch
+
+    fn()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for _ in range(reps):
+            fn()
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    samples = []
+    for _ in range(iters):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        g.replay()
+        e.record()
+        torch.cuda.synchronize()
+        samples.append(s.elapsed_time(e) * 1e3 / reps)
+    return statistics.median(samples), min(samples)
+
+
+def kernel_table(peaks: dict) -> list[dict]:
+    import torch
+
+    from deplodock_b200 import ops
+
+    rows = []
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(0)
+
+    def add(name, us, us_min, bound, work, unit_scale, peak, note=""):
+        achieved = work / (us * 1e-6) / unit_scale
+        rows.append({"kernel": name, "us": round(us, 2), "us_min": round(us_min, 2), "bound": bound,
+                     "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s" if bound == "hbm" else "TFLOP/s",
+                     "frac": round(achieved / peak, 4), "note": note})
+
+    # 1. RMSNorm [1,32,2048] f32 (0.5 MB: L2-resident, launch-latency bound) and a bandwidth-scale shape
+    x = torch.randn(1, 32, 2048, device=dev, generator=g)
+    w = 1 + 0.02 * torch.randn(2048, device=dev, generator=g)
+    y = torch.empty_like(x)
+    us, mn = _graph_time_us(lambda: ops.rmsnorm(x, w, 1e-6, out=y), 200)
+    add("k_rms_norm [1,32,2048] f32", us, mn, "hbm", 532480, 1e9, peaks["hbm_gbs"], "0.5 MB, L2-resident, latency-bound")
+    xs = [torch.randn(32768, 1024, device=dev, generator=g).bfloat16() for _ in range(3)]
+    ws = torch.ones(1024, device=dev, dtype=torch.bfloat16)
+    ys = [torch.empty_like(t) for t in xs]
+    state = {"i": 0}
+
+    def rms_big():
+        i = state["i"] = (state["i"] + 1) % 3
+        ops.rmsnorm(xs[i], ws, 1e-6, out=ys[i])
+
+    us, mn = _graph_time_us(rms_big, 30)
+    add("k_rms_norm [32768,1024] bf16", us, mn, "hbm", 2 * 32768 * 1024 * 2 + 2048, 1e9, peaks["hbm_gbs"],
+        "3 rotating 64 MB buffer pairs (> L2)")
+    del xs, ys
+    # 2. Softmax [1,28,2048,2048] f32
+    xsm = 3 * torch.randn(28 * 2048, 2048, device=dev, generator=g)
+    m = torch.rand(xsm.shape, device=dev, generator=g) < 0.01
+    m[:, 0] = False
+    xsm[m] = float("-inf")
+    del m
+    ysm = torch.empty_like(xsm)
+    us, mn = _graph_time_us(lambda: ops.softmax_lastdim(xsm, out=ysm), 10)
+    add("k_softmax [1,28,2048,2048] f32", us, mn, "hbm", 939524096, 1e9, peaks["hbm_gbs"], "470 MB in + 470 MB out (> L2)")
+    del xsm, ysm
+    # 3. Linear 4096x2048 -> 6144 bf16, and e4m3 weights
+    xl = torch.randn(4096, 2048, device=dev, generator=g).bfloat16()
+    w32 = 0.02 * torch.randn(6144, 2048, device=dev, generator=g)
+    wl = w32.bfloat16()
+    yl = torch.empty(4096, 6144, device=dev, dtype=torch.bfloat16)
+    us, mn = _graph_time_us(lambda: ops.linear(xl, wl, out=yl), 20)
+    add("k_linear 4096x2048x6144 bf16", us, mn, "tensor", 103079215104, 1e12, peaks["bf16_tflops"], "burst peak")
+    s = (w32.abs().amax(1) / 448.0).contiguous()
+    wq = (w32 / s[:, None]).to(torch.float8_e4m3fn)
+    us, mn = _graph_time_us(lambda: ops.linear_w8(xl, wq, s, out=yl), 20)
+    add("k_linear 4096x2048x6144 e4m3 weights", us, mn, "tensor", 103079215104, 1e12, peaks["bf16_tflops"], "burst peak")
+    del xl, wl, w32, wq, yl
+    # 4. SDPA B4 Hq16 Hkv8 S2048 D128
+    q = torch.randn(4, 16, 2048, 128, device=dev, generator=g).bfloat16()
+    k = torch.randn(4, 8, 2048, 128, device=dev, generator=g).bfloat16()
+    v = torch.randn(4, 8, 2048, 128, device=dev, generator=g).bfloat16()
+    o = torch.empty_like(q)
+    us, mn = _graph_time_us(lambda: ops.sdpa_causal_gqa(q, k, v, out=o), 20)
+    add("k_scaled_dot_product_attention B4 Hq16 Hkv8 S2048 D128", us, mn, "tensor", 68753031168, 1e12,
+        peaks["bf16_tflops"], "causal-useful flops, burst peak")
+    ops.device_status()
+    return rows
+
+
+# ------------------------------------------------------------------------------------------------------------
+# Main arm
+# ------------------------------------------------------------------------------------------------------------
+def gemm_event_pass(model) -> dict:
+    """One eager pass of the plan with CUDA events around every tcgen05 GEMM launch (on the launching stream):
+    total GEMM time and flops per forward of this rank's shard."""
+    import torch
+
+    from deplodock_b200 import ops
+
+    events = []
+    flops = 0
+    orig = ops.linear
+
+    def timed_linear(x, w, **kw):
+        nonlocal flops
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        r = orig(x, w, **kw)
+        e.record()
+        events.append((s, e))
+        flops += 2 * (x.numel() // x.shape[-1]) * x.shape[-1] * w.shape[0]
+        return r
+
+    ops.linear = timed_linear
+    try:
+        model.forward_eager()
+        torch.cuda.synchronize()
+        events.clear()
+        flops = 0
+        model.forward_eager()
+        torch.cuda.synchronize()
+    finally:
+        ops.linear = orig
+    total_ms = sum(s.elapsed_time(e) for s, e in events)
+    return {"launches": len(events), "ms": total_ms, "flops": flops}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel table")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    ap.add_argument("--chunk-seqs", type=int, default=0, help="sequences per activation chunk (0 = whole shard)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from deplodock_b200 import cabi, ops
+    from deplodock_b200.dist import gather_embeddings, init_process_group, shard_batch
+    from deplodock_b200.model import EmbedConfig, EmbedForward
+
+    cabi.load_library()  # fail loudly when the CUDA extension is missing
+    rank, local_rank, world = init_process_group()
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    peaks, peak_src = load_peaks()
+
+    cfg = EmbedConfig()
+    shard = shard_batch(BATCH, rank, world)
+
+    # Weights: N(0, 0.02) projections/embeddings, ones for the norms, generated on the device with a fixed seed
+    # (identical on every rank = replicated weights).
+    gen = torch.Generator(device=dev).manual_seed(0)
+
+    def rnd(*shape):
+        return (0.02 * torch.randn(*shape, device=dev, generator=gen)).bfloat16()
+
+    H, I, D = cfg.hidden_size, cfg.intermediate_size, cfg.head_dim
+    nq, nkv = cfg.num_attention_heads, cfg.num_key_value_heads
+    sd = {"embed_tokens.weight": rnd(cfg.vocab_size, H), "norm.weight": torch.ones(H, device=dev, dtype=torch.bfloat16)}
+    for i in range(cfg.num_hidden_layers):
+        p = f"layers.{i}."
+        sd[p + "input_layernorm.weight"] = torch.ones(H, device=dev, dtype=torch.bfloat16)
+        sd[p + "post_attention_layernorm.weight"] = torch.ones(H, device=dev, dtype=torch.bfloat16)
+        sd[p + "self_attn.q_norm.weight"] = torch.ones(D, device=dev, dtype=torch.bfloat16)
+        sd[p + "self_attn.k_norm.weight"] = torch.ones(D, device=dev, dtype=torch.bfloat16)
+        sd[p + "self_attn.q_proj.weight"] = rnd(nq * D, H)
+        sd[p + "self_attn.k_proj.weight"] = rnd(nkv * D, H)
+        sd[p + "self_attn.v_proj.weight"] = rnd(nkv * D, H)
+        sd[p + "self_attn.o_proj.weight"] = rnd(H, nq * D)
+        sd[p + "mlp.gate_proj.weight"] = rnd(I, H)
+        sd[p + "mlp.up_proj.weight"] = rnd(I, H)
+        sd[p + "mlp.down_proj.weight"] = rnd(H, I)
+
+    model = EmbedForward(cfg, sd, batch=shard.size, seq=SEQ, device=dev, chunk_seqs=args.chunk_seqs or None)
+    del sd
+    ids_all = torch.randint(0, cfg.vocab_size, (BATCH, SEQ), generator=torch.Generator().manual_seed(0))
+    ids_host = ids_all[shard.start:shard.stop].contiguous().pin_memory()
+    model.ids.copy_(ids_host)
+    model.capture()
+    gathered = torch.empty(BATCH, H, dtype=torch.float32, device=dev)
+    out_host = torch.empty(BATCH, H, dtype=torch.float32).pin_memory()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step_device():
+        model.replay()
+        gather_embeddings(model.out, BATCH, out=gathered)
+
+    def step_e2e():
+        model(ids_host)
+        gather_embeddings(model.out, BATCH, out=gathered)
+        out_host.copy_(gathered, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(steps):
+            fn()
+        e.record()
+        barrier()
+        ms = torch.tensor([s.elapsed_time(e)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item()
+
+    for _ in range(args.warmup):
+        step_device()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    total_ms = timed(step_device, args.steps)
+    clocks = sampler.stop() if sampler else None
+    for _ in range(2):
+        step_e2e()
+    e2e_ms = timed(step_e2e, args.steps)
+    ops.device_status()
+    finite = bool(torch.isfinite(gathered).all().item())
+
+    ms_per_step = total_ms / args.steps
+    value = BATCH / (ms_per_step * 1e-3)
+    e2e_value = BATCH / (e2e_ms / args.steps * 1e-3)
+
+    if rank == 0:
+        gp = gemm_event_pass(model)
+        gemm_tflops = gp["flops"] / (gp["ms"] * 1e-3) / 1e12
+        peak = peaks["bf16_tflops_sustained"]
+        roofline = {
+            "bound": "tensor", "kernel": "gemm_bf16_kernel (tcgen05, all four projections of every layer)",
+            "achieved": round(gemm_tflops, 1), "peak": peak, "peak_source": f"{peak_src} (sustained cuBLAS bf16)",
+            "unit": "TFLOP/s", "frac": round(gemm_tflops / peak, 4),
+            "launches_per_step": gp["launches"], "avg_launch_us": round(gp["ms"] * 1e3 / gp["launches"], 2),
+            "gemm_share_of_step": round(gp["ms"] / ms_per_step, 4),
+            "traffic": None,
+        }
+        step_flops = cfg.linear_flops_per_token() * BATCH * SEQ + cfg.attention_flops(BATCH, SEQ)
+        line = {
+            "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "qwen3-embedding-0.6b-shaped forward: 28 layers, hidden 1024, 16/8 heads x 128, "
+                                   "SwiGLU 3072, vocab 151669; 64 sequences x 512 uniform-random ids; causal; "
+                                   "last-token pool + L2; random-init N(0,0.02) bf16 weights",
+                       "global_batch": BATCH, "seq_len": SEQ, "parallelism": f"batch-shard x{world}, weights replicated",
+                       "l2_policy": "inputs larger than L2 (1.2 GB of weights + activations per step)",
+                       "cuda_graph": True, "chunk_seqs": model.chunk_seqs},
+            "step_tflops": round(step_flops / (ms_per_step * 1e-3) / 1e12, 1),
+            "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "h2d_bytes_per_step": BATCH * SEQ * 8,
+                    "d2h_bytes_per_step": BATCH * H * 4, "ms_per_step": round(e2e_ms / args.steps, 4)},
+            "gpu_launches": model.num_launches * args.steps,
+            "clocks": clocks, "roofline": roofline, "outputs_finite": finite,
+        }
+        if world == 1 and not args.no_kernels:
+            del model
+            torch.cuda.empty_cache()
+            line["kernels"] = kernel_table(peaks)
+        if world == 1 and not args.no_cpu:
+            from oracle import inputs as oin
+
+            ocfg = oin.EmbedModelConfig()
+            line["cpu_baseline"] = {k: v for k, v in cpu_reference_sample(
+                oin.embed_model_weights(ocfg, seed=0), ocfg, 2).items() if k != "seconds"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,433 @@
+"""``B200Backend``: the reference's ``Backend`` call surface over the hand-written sm_100a kernels.
+
+Mirrors ``emmy/compiler/backend/base.py:45-205`` (``RunResult``, ``LaunchTime``, ``BenchmarkResult``, ``Backend``) and
+``emmy/compiler/backend/cuda/backend.py:61-237`` (``CudaBackend``: constructor keywords, ``compile``, ``run``,
+``benchmark_async``, ``close_async_worker``). Where the reference lowers a Torch-IR graph through its rewrite pipeline
+to generated CUDA (``Pipeline.build(CUDA_PASSES).run``, ``backend.py:135-142``), ``compile`` here dispatches each
+Torch-IR op to one C-ABI kernel and returns a plan; nothing is generated or compiled at run time.
+
+    compiled = backend.compile(graph)                 # Graph | record dict | JSON path | reference Graph object
+    result, pre = backend.run(compiled, input_data={node_id: ndarray, ...})
+    bench = await backend.benchmark_async(compiled, warmup=5, num_iters=20)
+
+Conventions kept from the reference: ``input_data`` holds one numpy array per graph input and per weight
+``ConstantOp``; bf16 travels as ``uint16`` bit patterns (``emmy/compiler/dtype.py:69``); weights may arrive as fp32 and
+are cast to the node dtype (``emmy/commands/run.py:1264-1267``); scalar ``ConstantOp``s are materialised from
+``op.value`` (``backend/base.py:184-191``); a missing input raises ``KeyError``; kernel names keep the ``k_`` prefix.
+Ops without a hand-written kernel raise :class:`LoweringError` — there is no interpreter fallback.
+"""
+
+from __future__ import annotations
+
+import asyncio
+import statistics
+import zlib
+from abc import ABC, abstractmethod
+from collections.abc import Callable
+from dataclasses import dataclass, field
+from typing import Any
+
+import numpy as np
+
+from deplodock_b200.graph import Graph, Node
+
+
+# ------------------------------------------------------------------------------------------------------------
+# Result types (same fields as emmy/compiler/backend/base.py:45-91)
+# ------------------------------------------------------------------------------------------------------------
+@dataclass
+class RunResult:
+    outputs: dict[str, Any]
+    time_ms: float | None = None
+
+
+@dataclass
+class LaunchTime:
+    idx: int
+    kernel_name: str
+    time_ms: float
+    samples: tuple[float, ...] | None = None
+
+
+@dataclass
+class BenchmarkResult:
+    time_ms: float
+    min_ms: float | None = None
+    max_ms: float | None = None
+    num_launches: int = 0
+    per_launch: list[LaunchTime] | None = None
+    captured: bool = False
+    e2e_ms: float | None = None
+    e2e_min_ms: float | None = None
+
+
+class LoweringError(RuntimeError):
+    """No hand-written kernel covers a node (the reference raises ``LoweringError`` from its pipeline)."""
+
+
+class Backend(ABC):
+    """Abstract backend: Graph -> compiled artifact -> run (``emmy/compiler/backend/base.py:94-205``)."""
+
+    name: str = "stub"
+    bench_compile_timeout_s: float = 30.0
+    bench_run_timeout_s: float = 10.0
+    bench_wall_timeout_s: float | None = None
+
+    @abstractmethod
+    def compile(self, graph: Any) -> Any: ...
+
+    @abstractmethod
+    def run(self, compiled: Any, *, input_data: dict[str, np.ndarray] | None = None,
+            pre_run: Callable[[], Any] | None = None) -> tuple[RunResult, Any]: ...
+
+
+# ------------------------------------------------------------------------------------------------------------
+# Plan
+# ------------------------------------------------------------------------------------------------------------
+@dataclass
+class PlanStep:
+    """One kernel launch: reads ``args`` (node ids) from the value table and writes ``out``."""
+
+    kernel_name: str
+    entry: str          # C-ABI entry point
+    out: str
+    args: list[str]
+    attrs: dict[str, Any] = field(default_factory=dict)
+
+
+@dataclass
+class CompiledPlan:
+    """What ``compile`` returns. Exposes ``inputs/outputs/nodes/symbolic_env`` because the reference's callers read
+    them off the compiled artifact (``emmy/commands/run.py:214,254,1249-1256``; ``backend/cuda/backend.py:172-176``)."""
+
+    graph: Graph
+    steps: list[PlanStep]
+    aliases: dict[str, str]   # view-like nodes (reshape/contiguous/to) -> the node whose buffer they share
+
+    @property
+    def inputs(self) -> list[str]:
+        return self.graph.inputs
+
+    @property
+    def outputs(self) -> list[str]:
+        return self.graph.outputs
+
+    @property
+    def nodes(self) -> dict[str, Node]:
+        return self.graph.nodes
+
+    def symbolic_env(self, input_data=None) -> dict[str, int]:
+        return self.graph.symbolic_env(input_data)
+
+    def describe(self) -> str:
+        """The dispatch plan as text: one line per launch (what ``emmy compile --ir cuda`` prints for this backend)."""
+        lines = []
+        for i, s in enumerate(self.steps):
+            n = self.graph.nodes[s.out]
+            lines.append(f"{i:3d} {s.kernel_name:<44} {s.entry:<32} out={s.out} {list(n.output.shape)} {n.output.dtype}"
+                         f" args={s.args} {s.attrs if s.attrs else ''}")
+        return "\n".join(lines)
+
+
+_PASSTHROUGH = {"ContiguousOp", "CloneOp", "ToOp", "TypeAsOp", "DetachOp", "AliasOp"}
+_VIEWS = {"ReshapeOp", "ViewOp", "UnsqueezeOp", "SqueezeOp", "FlattenOp"}
+
+
+def _name(prefix: str, node: Node) -> str:
+    tag = zlib.crc32(f"{node.id}:{node.output.shape}:{node.output.dtype}".encode()) & 0xFFFFFF
+    return f"k_{prefix}_{tag:06x}"
+
+
+def _is_causal_mask_const(g: Graph, nid: str) -> bool:
+    n = g.nodes[nid]
+    return n.op == "ConstantOp" and "causal_mask" in str(n.op_fields.get("source_path") or n.id)
+
+
+def lower(graph: Graph) -> CompiledPlan:
+    """Op-by-op dispatch of a Torch-IR graph onto C-ABI entry points."""
+    steps: list[PlanStep] = []
+    aliases: dict[str, str] = {}
+
+    def src(nid: str) -> str:
+        while nid in aliases:
+            nid = aliases[nid]
+        return nid
+
+    for node in graph.compute_nodes():
+        op, f = node.op, node.op_fields
+        ins = [src(i) for i in node.inputs]
+        dt = node.output.dtype
+        if op in _PASSTHROUGH or op in _VIEWS:
+            aliases[node.id] = ins[0]
+        elif op == "RmsNormOp":
+            if dt not in ("f32", "bf16"):
+                raise LoweringError(f"{node.id}: RmsNormOp in {dt} has no kernel")
+            steps.append(PlanStep(_name("rms_norm", node), "emk_rmsnorm", node.id, ins[:2], {"eps": float(f.get("eps", 1e-6))}))
+        elif op == "SoftmaxOp":
+            axis = f.get("axis", -1)
+            rank = len(node.output.shape)
+            if axis not in (-1, rank - 1):
+                raise LoweringError(f"{node.id}: softmax over axis {axis} has no kernel (last axis only)")
+            steps.append(PlanStep(_name("softmax", node), "emk_softmax_lastdim", node.id, ins[:1]))
+        elif op in ("LinearOp", "MatmulOp"):
+            kn = op == "MatmulOp"
+            w_shape = graph.nodes[ins[1]].output.shape
+            if len(w_shape) != 2:
+                raise LoweringError(f"{node.id}: batched second operand {w_shape} has no kernel")
+            has_bias = bool(f.get("has_bias"))
+            if dt == "bf16":
+                K = w_shape[0] if kn else w_shape[1]
+                N = w_shape[1] if kn else w_shape[0]
+                entry = "emk_linear_bf16" if (K % 8 == 0 and N % 8 == 0) else "emk_linear_bf16_simt"
+            elif dt == "f32":
+                entry = "emk_linear_f32_simt"
+            else:
+                raise LoweringError(f"{node.id}: {op} in {dt} has no kernel")
+            steps.append(PlanStep(_name("linear", node), entry, node.id, ins[: 3 if has_bias else 2],
+                                  {"kn": kn, "has_bias": has_bias}))
+        elif op == "SdpaOp":
+            causal = bool(f.get("is_causal"))
+            if len(ins) > 3:
+                if _is_causal_mask_const(graph, ins[3]):
+                    causal = True   # the HF wrapper's additive 0/-inf causal buffer: implied, never read
+                else:
+                    raise LoweringError(f"{node.id}: SdpaOp with a general additive mask has no kernel")
+            q_shape = graph.nodes[ins[0]].output.shape
+            k_shape = graph.nodes[ins[1]].output.shape
+            if len(q_shape) != 4:
+                raise LoweringError(f"{node.id}: SdpaOp expects [B,H,S,D] operands, got {q_shape}")
+            fast = dt == "bf16" and causal and q_shape[-1] == 128 and q_shape[2] == k_shape[2]
+            steps.append(PlanStep(_name("scaled_dot_product_attention", node),
+                                  "emk_sdpa_causal_gqa_bf16" if fast else "emk_sdpa_simt", node.id, ins[:3],
+                                  {"causal": causal}))
+        else:
+            raise LoweringError(
+                f"{node.id}: Torch-IR op {op} has no hand-written kernel in this backend (whole Qwen3-shaped trunks go "
+                "through deplodock_b200.model.EmbedForward)")
+    return CompiledPlan(graph, steps, aliases)
+
+
+# ------------------------------------------------------------------------------------------------------------
+# Backend
+# ------------------------------------------------------------------------------------------------------------
+class B200Backend(Backend):
+    """Drop-in for ``CudaBackend`` on B200. Constructor keywords match ``CudaBackend.__init__``
+    (``backend/cuda/backend.py:70-112``); ``dump``, ``tune_db`` and the bench budgets are accepted and unused (there are
+    no variants to tune and nothing to compile)."""
+
+    name = "b200"
+
+    def __init__(self, *, debug: bool | None = None, dump=None, bench_wall_timeout_s: float | None = None,
+                 bench_compile_timeout_s: float = 30.0, bench_run_timeout_s: float = 10.0, tune_db=None,
+                 device_id: int | None = None) -> None:
+        self.debug = bool(debug)
+        self.dump = dump
+        self.bench_wall_timeout_s = bench_wall_timeout_s
+        self.bench_compile_timeout_s = bench_compile_timeout_s
+        self.bench_run_timeout_s = bench_run_timeout_s
+        self.tune_db = tune_db
+        self.device_id = device_id
+        self.last_debug_result = None
+
+    def close_async_worker(self) -> None:
+        """The reference kills its bench subprocess here; this backend benches in-process (every wait is bounded)."""
+
+    async def aclose_async_worker(self) -> None:
+        return None
+
+    # -- compile -----------------------------------------------------------------------------------------------
+    def compile(self, graph: Any) -> CompiledPlan:
+        if isinstance(graph, CompiledPlan):
+            return graph
+        return lower(Graph.coerce(graph))
+
+    # -- run ---------------------------------------------------------------------------------------------------
+    def _device(self):
+        import torch
+
+        return torch.device("cuda", self.device_id if self.device_id is not None else torch.cuda.current_device())
+
+    def _upload(self, plan: CompiledPlan, input_data: dict[str, Any]) -> dict[str, Any]:
+        """Host arrays -> device tensors for inputs and constants (cast to the node dtype)."""
+        import torch
+
+        dev = self._device()
+        vals: dict[str, torch.Tensor] = {}
+        g = plan.graph
+        for nid, node in g.nodes.items():
+            role = g.node_role(nid)
+            if role not in ("input", "constant"):
+                continue
+            info = node.output
+            if nid in input_data:
+                arr = input_data[nid]
+                if isinstance(arr, torch.Tensor):
+                    t = arr
+                else:
+                    a = np.ascontiguousarray(np.asarray(arr))
+                    if info.dtype == "bf16" and a.dtype == np.uint16:
+                        t = torch.from_numpy(a.view(np.int16)).view(torch.bfloat16)
+                    else:
+                        t = torch.from_numpy(a)
+                want = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16, "i64": torch.int64,
+                        "i32": torch.int32, "bool": torch.bool}[info.dtype]
+                t = t.to(device=dev, dtype=want).reshape(info.shape).contiguous()
+                vals[nid] = t
+            elif role == "input":
+                raise KeyError(f"Missing input for node {nid!r}")
+            elif node.op_fields.get("value") is not None:
+                vals[nid] = torch.tensor([float(node.op_fields["value"])], device=dev)
+            else:
+                used = any(nid in s.args for s in plan.steps)
+                if used:
+                    raise KeyError(f"ConstantOp {nid!r} has no value and was not supplied in input_data")
+        return vals
+
+    def _execute(self, plan: CompiledPlan, vals: dict[str, Any], step_idx: int | None = None) -> None:
+        from deplodock_b200 import ops
+
+        steps = plan.steps if step_idx is None else [plan.steps[step_idx]]
+        g = plan.graph
+        for s in steps:
+            a = [vals[i] for i in s.args]
+            shape = g.nodes[s.out].output.shape
+            if s.entry == "emk_rmsnorm":
+                y = ops.rmsnorm(a[0], a[1].reshape(-1), s.attrs["eps"])
+            elif s.entry == "emk_softmax_lastdim":
+                y = ops.softmax_lastdim(a[0])
+            elif s.entry in ("emk_linear_bf16", "emk_linear_bf16_simt"):
+                fn = ops.linear if s.entry == "emk_linear_bf16" else ops.linear_simt
+                y = fn(a[0], a[1], bias=a[2].reshape(-1) if s.attrs["has_bias"] else None, w_is_kn=s.attrs["kn"])
+            elif s.entry == "emk_linear_f32_simt":
+                y = ops.linear_f32(a[0], a[1], a[2].reshape(-1) if s.attrs["has_bias"] else None, s.attrs["kn"])
+            elif s.entry == "emk_sdpa_causal_gqa_bf16":
+                y = ops.sdpa_causal_gqa(a[0], a[1], a[2])
+            elif s.entry == "emk_sdpa_simt":
+                y = ops.sdpa_simt(a[0], a[1], a[2], s.attrs["causal"])
+            else:  # pragma: no cover - lower() only emits the entries above
+                raise LoweringError(f"no executor for {s.entry}")
+            vals[s.out] = y.reshape(shape)
+        for alias, target in plan.aliases.items():
+            if target in vals and (step_idx is None):
+                vals[alias] = vals[target].reshape(g.nodes[alias].output.shape)
+
+    def _download(self, plan: CompiledPlan, vals: dict[str, Any]) -> dict[str, np.ndarray]:
+        import torch
+
+        outs: dict[str, np.ndarray] = {}
+        for name in plan.outputs:
+            t = vals[name] if name in vals else vals[plan.aliases[name]]
+            info = plan.graph.nodes[name].output
+            t = t.reshape(info.shape).contiguous()
+            if info.dtype == "bf16":
+                outs[name] = t.view(torch.int16).cpu().numpy().view(np.uint16)
+            else:
+                outs[name] = t.cpu().numpy().astype(info.np_dtype, copy=False)
+        return outs
+
+    def run(self, compiled: Any, *, input_data: dict[str, np.ndarray] | None = None,
+            pre_run: Callable[[], Any] | None = None) -> tuple[RunResult, Any]:
+        import torch
+
+        from deplodock_b200 import ops
+
+        plan = self.compile(compiled)
+        pre_result = pre_run() if pre_run is not None else None
+        vals = self._upload(plan, input_data or {})
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        self._execute(plan, vals)
+        stop.record()
+        ops.device_status()  # synchronises; raises HungKernelError / RuntimeError on device-side failure
+        elapsed = start.elapsed_time(stop)
+        if plan.steps and elapsed <= 0.0:
+            raise RuntimeError("zero elapsed time for a non-empty program")  # reference: program.py:1027-1031
+        return RunResult(outputs=self._download(plan, vals), time_ms=elapsed), pre_result
+
+    # -- benchmark ---------------------------------------------------------------------------------------------
+    async def benchmark_async(self, compiled: Any, *, warmup: int = 5, num_iters: int | str = 20, on_iter=None,
+                              nvcc_flags: str | None = None, capture_graphs: bool = True,
+                              input_data: dict[str, np.ndarray] | None = None) -> BenchmarkResult:
+        """Per-launch median/min over CUDA-graph-captured windows and a whole-program window — the reference's
+        protocol (``backend/cuda/program.py:1152-1374``). Inputs not supplied are filled with the reference's
+        deterministic pattern ``0.01 * ((7 i + 13) mod 101 - 50)`` (``program.py:265-276``)."""
+        await asyncio.sleep(0)
+        return self._benchmark(self.compile(compiled), warmup, num_iters, on_iter, capture_graphs, input_data)
+
+    def benchmark(self, compiled: Any, **kw) -> BenchmarkResult:
+        """Synchronous form of :meth:`benchmark_async`."""
+        kw.pop("nvcc_flags", None)
+        return self._benchmark(self.compile(compiled), kw.get("warmup", 5), kw.get("num_iters", 20), kw.get("on_iter"),
+                               kw.get("capture_graphs", True), kw.get("input_data"))
+
+    @staticmethod
+    def _default_fill(shape: tuple[int, ...], dtype: str) -> np.ndarray:
+        n = int(np.prod(shape)) if shape else 1
+        i = np.arange(n, dtype=np.int64)
+        base = (0.01 * (((7 * i + 13) % 101) - 50)).astype(np.float32).reshape(shape)
+        if dtype in ("i64", "i32"):
+            return np.zeros(shape, dtype=np.int64)
+        return base
+
+    def _benchmark(self, plan: CompiledPlan, warmup, num_iters, on_iter, capture_graphs, input_data) -> BenchmarkResult:
+        import torch
+
+        from deplodock_b200 import ops
+
+        iters = 20 if num_iters == "auto" else int(num_iters)
+        data = dict(input_data or {})
+        for nid, node in plan.graph.nodes.items():
+            if plan.graph.node_role(nid) in ("input", "constant") and nid not in data \
+                    and node.op_fields.get("value") is None:
+                data[nid] = self._default_fill(node.output.shape, node.output.dtype)
+        vals = self._upload(plan, data)
+        for _ in range(max(1, warmup)):
+            self._execute(plan, vals)
+        ops.device_status()
+
+        def window(fn, reps: int) -> list[float]:
+            """``iters`` samples of ms per call, each a replay of ``reps`` captured back-to-back launches."""
+            graph = None
+            if capture_graphs:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    for _ in range(reps):
+                        fn()
+            samples = []
+            for it in range(iters):
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s.record()
+                if graph is not None:
+                    graph.replay()
+                else:
+                    for _ in range(reps):
+                        fn()
+                e.record()
+                torch.cuda.synchronize()
+                samples.append(s.elapsed_time(e) / reps)
+                if on_iter is not None:
+                    on_iter(it)
+            return samples
+
+        per_launch: list[LaunchTime] = []
+        for idx, step in enumerate(plan.steps):
+            s0, e0 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s0.record()
+            self._execute(plan, vals, idx)
+            e0.record()
+            torch.cuda.synchronize()
+            one = max(s0.elapsed_time(e0), 1e-3)
+            reps = int(min(512, max(1, round(1.0 / one))))  # ~1 ms windows, as the reference calibrates
+            samples = window(lambda i=idx: self._execute(plan, vals, i), reps)
+            per_launch.append(LaunchTime(idx, step.kernel_name, statistics.median(samples), tuple(samples)))
+        e2e = e2e_min = None
+        if len(plan.steps) > 1:
+            samples = window(lambda: self._execute(plan, vals), 1)
+            e2e, e2e_min = statistics.median(samples), min(samples)
+        ops.device_status()
+        return BenchmarkResult(
+            time_ms=sum(lt.time_ms for lt in per_launch),
+            min_ms=sum(min(lt.samples) for lt in per_launch),
+            max_ms=sum(max(lt.samples) for lt in per_launch),
+            num_launches=len(per_launch), per_launch=per_launch, captured=bool(capture_graphs),
+            e2e_ms=e2e, e2e_min_ms=e2e_min)

@@ -114,6 +114,26 @@ __global__ void __launch_bounds__(256) sdpa_simt_kernel(const T* __restrict__ q,
   }
 }
 
+// fp32 LinearOp / MatmulOp (+ bias) on CUDA cores: fp32 graphs (the reference's scalar FMA tier) have no tensor-core
+// path here; one thread per output element.
+__global__ void __launch_bounds__(256) gemm_f32_simt_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                            const float* __restrict__ bias, float* __restrict__ y,
+                                                            int64_t M, int64_t N, int64_t K, int wl) {
+  const int64_t total = M * N;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t m = i / N, n = i % N;
+    const float* xr = x + m * K;
+    float acc = 0.f;
+    if (wl == EMK_W_NK) {
+      const float* wr = w + n * K;
+      for (int64_t k = 0; k < K; ++k) acc = fmaf(xr[k], wr[k], acc);
+    } else {
+      for (int64_t k = 0; k < K; ++k) acc = fmaf(xr[k], w[k * N + n], acc);
+    }
+    y[i] = bias ? acc + bias[n] : acc;
+  }
+}
+
 }  // namespace
 
 extern "C" int emk_linear_bf16_simt(emk_handle_t h, const void* x, const void* w, const void* residual, void* y,
@@ -152,6 +172,18 @@ extern "C" int emk_sdpa_simt(emk_handle_t h, const void* q, const void* k, const
         Skv, (int)D, scale, causal);
   else
     return EMK_ERR_DTYPE;
+  EMK_LAUNCH_CHECK(h);
+  return EMK_OK;
+}
+
+extern "C" int emk_linear_f32_simt(emk_handle_t h, const float* x, const float* w, const float* bias, float* y,
+                                   int64_t M, int64_t N, int64_t K, int wlayout, emk_stream_t stream) {
+  if (!h || !x || !w || !y) return EMK_ERR_ARG;
+  if (M <= 0 || N <= 0 || K <= 0) return EMK_ERR_SHAPE;
+  if (wlayout != EMK_W_NK && wlayout != EMK_W_KN) return EMK_ERR_ARG;
+  int64_t blocks = (M * N + 255) / 256;
+  if (blocks > (int64_t)h->sm_count * 32) blocks = (int64_t)h->sm_count * 32;
+  gemm_f32_simt_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(x, w, bias, y, M, N, K, wlayout);
   EMK_LAUNCH_CHECK(h);
   return EMK_OK;
 }

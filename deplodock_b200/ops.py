@@ -44,6 +44,8 @@ def _check_cuda_contig(*tensors: torch.Tensor) -> None:
         if t is None:
             continue
         if not t.is_cuda:
+            if not torch.cuda.is_available():
+                raise RuntimeError("deplodock_b200 kernels need a CUDA device (sm_100a); there is no CPU fallback")
             raise ValueError("expected CUDA tensors")
         if not t.is_contiguous():
             raise ValueError("expected contiguous tensors")
@@ -133,6 +135,23 @@ def linear_simt(x, w, *, residual=None, bias=None, swiglu=False, w_is_kn=False, 
     """Same contract on CUDA cores: for K or N not a multiple of 8, and as a cross-check in the tests."""
     return _linear_common("emk_linear_bf16_simt", x, w, residual=residual, bias=bias, swiglu=swiglu, w_is_kn=w_is_kn,
                           out=out)
+
+
+def linear_f32(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, w_is_kn: bool = False) -> torch.Tensor:
+    """fp32 LinearOp / MatmulOp on CUDA cores (fp32 graphs have no tensor-core path)."""
+    _check_cuda_contig(x, w, bias)
+    if x.dtype != torch.float32 or w.dtype != torch.float32:
+        raise TypeError("linear_f32 expects float32 operands")
+    K = x.shape[-1]
+    M = x.numel() // K
+    N = w.shape[1] if w_is_kn else w.shape[0]
+    if (w.shape[0] if w_is_kn else w.shape[1]) != K:
+        raise ValueError("weight does not match x")
+    y = torch.empty(*x.shape[:-1], N, dtype=torch.float32, device=x.device)
+    h = handle()
+    h.check(h.lib.emk_linear_f32_simt(h.ptr, _ptr(x), _ptr(w), _ptr(bias), _ptr(y), M, N, K,
+                                      cabi.EMK_W_KN if w_is_kn else cabi.EMK_W_NK, _stream()), "emk_linear_f32_simt")
+    return y
 
 
 def linear_w8(x: torch.Tensor, w_e4m3: torch.Tensor, scale: torch.Tensor, out=None) -> torch.Tensor:

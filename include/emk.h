@@ -144,6 +144,11 @@ int emk_pool_norm_l2(emk_handle_t h, const void* hidden_states, const void* w, f
 int emk_linear_bf16_simt(emk_handle_t h, const void* x, const void* w, const void* residual, void* y, int64_t M,
                          int64_t N, int64_t K, int wlayout, int epilogue, emk_stream_t stream);
 
+/* fp32 LinearOp / MatmulOp (+ optional bias [N]) on CUDA cores, for fp32 graphs (the reference's scalar tier,
+ * emmy/compiler/pipeline/passes/lowering/kernel/_atom.py:572-597). Same layouts as emk_linear_bf16. */
+int emk_linear_f32_simt(emk_handle_t h, const float* x, const float* w, const float* bias, float* y, int64_t M,
+                        int64_t N, int64_t K, int wlayout, emk_stream_t stream);
+
 /* Generic attention on CUDA cores (one warp per query row, fp32 online softmax): any head_dim <= 256, causal or
  * full, EMK_F32 or EMK_BF16, q/o [B,Hq,Sq,D], k/v [B,Hkv,Skv,D] contiguous. Takes the SdpaOp shapes the tensor-core
  * kernel rejects (fp32 inputs, head_dim != 128, non-causal: the reference's scalar flash tier,

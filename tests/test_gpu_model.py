@@ -1,0 +1,61 @@
+"""Parity of the Qwen3-shaped embedding forward on the GPU with the CPU eager oracle."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+from oracle import cpu_ref, inputs
+
+pytestmark = pytest.mark.gpu
+
+
+def _cos(a, b):
+    return torch.nn.functional.cosine_similarity(a.double(), b.double(), dim=-1)
+
+
+@pytest.mark.parametrize("batch,seq,layers,chunk", [(2, 40, 2, None), (4, 130, 3, 2), (3, 512, 2, None)])
+def test_embed_forward_matches_eager_cpu(libemk, batch, seq, layers, chunk):
+    from deplodock_b200.model import EmbedForward
+
+    cfg = inputs.EmbedModelConfig().small(layers=layers, vocab=700)
+    sd = inputs.perturb_norm_weights(inputs.embed_model_weights(cfg))
+    ids = inputs.token_ids(batch, seq, cfg.vocab_size, seed=5)
+    model = EmbedForward(cfg, sd, batch=batch, seq=seq, chunk_seqs=chunk)
+    got = model(ids).cpu().clone()
+    ref = cpu_ref.embed_forward(ids, cfg, sd)
+    assert torch.isfinite(got).all()
+    assert _cos(got, ref).min().item() >= 0.999
+    assert (got - ref).abs().max().item() <= 2e-2
+    # replaying the captured graph with new ids gives the eager-launch result for those ids
+    ids2 = inputs.token_ids(batch, seq, cfg.vocab_size, seed=6)
+    again = model(ids2).cpu().clone()
+    model.ids.copy_(ids2)
+    eager = model.forward_eager().cpu().clone()
+    torch.cuda.synchronize()
+    assert torch.equal(again, eager)
+    assert not torch.equal(again, got)
+
+
+def test_embed_forward_vs_hf_module(libemk):
+    from deplodock_b200.model import EmbedForward
+
+    cfg = inputs.EmbedModelConfig().small(layers=2, vocab=300)
+    sd = inputs.perturb_norm_weights(inputs.embed_model_weights(cfg))
+    ids = inputs.token_ids(2, 64, cfg.vocab_size, seed=2)
+    got = EmbedForward(cfg, sd, batch=2, seq=64)(ids).cpu()
+    ref = cpu_ref.embed_forward_hf(ids, cfg, sd)
+    assert _cos(got, ref).min().item() >= 0.999
+    assert (got - ref).abs().max().item() <= 2e-2
+
+
+def test_sequences_are_independent(libemk):
+    """Batch sharding relies on it: the embedding of a sequence does not depend on its batch neighbours."""
+    from deplodock_b200.model import EmbedForward
+
+    cfg = inputs.EmbedModelConfig().small(layers=2, vocab=300)
+    sd = inputs.embed_model_weights(cfg)
+    ids = inputs.token_ids(4, 96, cfg.vocab_size, seed=8)
+    full = EmbedForward(cfg, sd, batch=4, seq=96)(ids).cpu().clone()
+    half = EmbedForward(cfg, sd, batch=2, seq=96)(ids[2:]).cpu().clone()
+    assert torch.equal(full[2:], half)

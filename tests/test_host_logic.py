@@ -1,0 +1,260 @@
+"""Host-side logic that needs no GPU: record loading, op dispatch, status mapping, sharding, gather (gloo ranks)."""
+
+from __future__ import annotations
+
+import os
+import socket
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from conftest import GOLDEN
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+# ---------------------------------------------------------------------------------------------------- graph records
+def test_graph_records_load_and_dispatch():
+    from deplodock_b200.backend import B200Backend
+    from deplodock_b200.graph import Graph
+
+    be = B200Backend()
+    expect = {
+        "cfg1_rmsnorm": ["emk_rmsnorm"],
+        "cfg2_softmax": ["emk_softmax_lastdim"],
+        "cfg3_linear_bf16": ["emk_linear_bf16"],
+        "cfg4_sdpa_bf16": ["emk_sdpa_causal_gqa_bf16"],
+        "linear_f32": ["emk_linear_f32_simt"],
+        "linear_bias_f32": ["emk_linear_f32_simt"],
+        "matmul_f32": ["emk_linear_f32_simt"],
+        "sdpa_causal_gqa_f32": ["emk_sdpa_simt"],
+        "sdpa_full_f32": ["emk_sdpa_simt"],
+    }
+    for name, entries in expect.items():
+        g = Graph.from_json(GOLDEN / "graphs" / f"{name}.json")
+        plan = be.compile(g)
+        assert [s.entry for s in plan.steps] == entries, name
+        assert all(s.kernel_name.startswith("k_") for s in plan.steps)
+        assert plan.inputs == g.inputs and plan.outputs == g.outputs and plan.symbolic_env({}) == {}
+        assert plan.describe()
+    plan = be.compile(GOLDEN / "graphs" / "cfg4_sdpa_bf16.json")
+    assert plan.steps[0].attrs["causal"] is True
+    assert be.compile(plan) is plan
+
+
+def test_kernel_names_are_stable_across_processes():
+    from deplodock_b200.backend import B200Backend
+
+    a = B200Backend().compile(GOLDEN / "graphs" / "cfg1_rmsnorm.json").steps[0].kernel_name
+    b = B200Backend().compile(GOLDEN / "graphs" / "cfg1_rmsnorm.json").steps[0].kernel_name
+    assert a == b and a.startswith("k_rms_norm_")
+
+
+def test_unsupported_ops_raise_lowering_error():
+    from deplodock_b200.backend import B200Backend, LoweringError
+
+    with pytest.raises(LoweringError):
+        B200Backend().compile(GOLDEN / "graphs" / "swiglu_f32.json")  # elementwise chain: no standalone kernel
+    rec = {"inputs": ["x"], "outputs": ["s"], "nodes": {
+        "x": {"op": "InputOp", "op_fields": {}, "inputs": [], "output": {"name": "x", "shape": [4, 8], "dtype": "f32"}},
+        "s": {"op": "SoftmaxOp", "op_fields": {"axis": 0}, "inputs": ["x"],
+              "output": {"name": "s", "shape": [4, 8], "dtype": "f32"}}}}
+    with pytest.raises(LoweringError):
+        B200Backend().compile(rec)
+
+
+def test_graph_validation_errors():
+    from deplodock_b200.graph import Graph
+
+    base = {"inputs": ["x"], "outputs": ["y"], "nodes": {
+        "x": {"op": "InputOp", "op_fields": {}, "inputs": [], "output": {"name": "x", "shape": [2], "dtype": "f32"}}}}
+    with pytest.raises(KeyError):
+        Graph.from_dict(base)
+    bad = {"inputs": ["x"], "outputs": ["x"], "nodes": {
+        "x": {"op": "InputOp", "op_fields": {}, "inputs": [], "output": {"name": "x", "shape": ["seq_len"], "dtype": "f32"}}}}
+    with pytest.raises(ValueError):
+        Graph.from_dict(bad)
+    bad["nodes"]["x"]["output"] = {"name": "x", "shape": [2], "dtype": "q4"}
+    with pytest.raises(TypeError):
+        Graph.from_dict(bad)
+
+
+def test_backend_constructor_matches_reference_keywords():
+    from deplodock_b200.backend import B200Backend, Backend
+
+    be = B200Backend(debug=False, dump=None, bench_wall_timeout_s=5.0, bench_compile_timeout_s=1.0,
+                     bench_run_timeout_s=2.0, tune_db="auto", device_id=0)
+    assert isinstance(be, Backend) and be.name == "b200"
+    assert be.bench_run_timeout_s == 2.0 and be.device_id == 0
+    be.close_async_worker()
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    from deplodock_b200 import cabi
+
+    monkeypatch.setattr(cabi, "_lib", None)
+    monkeypatch.setattr(cabi, "LIB_PATH", tmp_path / "libemk.so")
+    with pytest.raises(cabi.EmkLibraryMissing):
+        cabi.load_library()
+
+
+def test_ops_refuse_to_run_without_cuda(libemk):
+    from deplodock_b200 import ops
+
+    if torch.cuda.is_available():
+        pytest.skip("CUDA present")
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        ops.rmsnorm(torch.zeros(2, 8), torch.ones(8))
+
+
+def test_status_codes_map_to_reference_exception_types(libemk):
+    from deplodock_b200 import cabi
+
+    class FakeHandle(cabi.Handle):
+        def __init__(self):  # no device
+            self.lib = cabi.load_library()
+            self.ptr = None
+
+        def last_error(self):
+            return "detail"
+
+    h = FakeHandle()
+    h.check(cabi.EMK_OK, "ok")
+    for rc, exc in [(cabi.EMK_ERR_SHAPE, ValueError), (cabi.EMK_ERR_ALIGN, ValueError), (cabi.EMK_ERR_LIMIT, ValueError),
+                    (cabi.EMK_ERR_DTYPE, TypeError), (cabi.EMK_ERR_TIMEOUT, cabi.HungKernelError),
+                    (cabi.EMK_ERR_CUDA, RuntimeError)]:
+        with pytest.raises(exc):
+            h.check(rc, "call")
+    assert issubclass(cabi.HungKernelError, RuntimeError)
+
+
+# ---------------------------------------------------------------------------------------------------- model config
+def test_model_flop_accounting_matches_the_benchmark_figures():
+    from deplodock_b200.model import EmbedConfig
+
+    cfg = EmbedConfig()
+    lin = cfg.linear_flops_per_token() * 64 * 512
+    att = cfg.attention_flops(64, 512)
+    assert lin == 2 * 32768 * 440401920
+    assert att == 28 * 4 * 64 * 16 * 128 * 131328
+    assert abs((lin + att) / 3.079e13 - 1) < 2e-3
+
+
+# ---------------------------------------------------------------------------------------------------- sharding
+def test_shard_batch_covers_everything_once():
+    from deplodock_b200.dist import shard_batch
+
+    for total in (0, 1, 7, 64, 65):
+        for world in (1, 2, 3, 4, 8):
+            shards = [shard_batch(total, r, world) for r in range(world)]
+            assert shards[0].start == 0 and shards[-1].stop == total
+            assert all(a.stop == b.start for a, b in zip(shards, shards[1:]))
+            assert max(s.size for s in shards) - min(s.size for s in shards) <= 1
+    with pytest.raises(ValueError):
+        shard_batch(8, 2, 2)
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _gather_worker(rank: int, world: int, port: int, total: int, q) -> None:
+    sys.path.insert(0, str(ROOT))
+    os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port))
+    import torch.distributed as dist
+
+    from deplodock_b200.dist import gather_embeddings, init_process_group, shard_batch
+
+    r, _, w = init_process_group("gloo")
+    sh = shard_batch(total, r, w)
+    full = torch.arange(total * 4, dtype=torch.float32).reshape(total, 4)
+    got = gather_embeddings(full[sh.start:sh.stop].clone(), total)
+    q.put((rank, torch.equal(got, full)))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("total", [8, 7])
+def test_gather_embeddings_two_gloo_ranks(total):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_gather_worker, args=(r, 2, port, total, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = sorted(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert results == [(0, True), (1, True)]
+
+
+def _failing_rank_worker(rank: int, world: int, port: int, q) -> None:
+    """Rank 1 never joins the collective; rank 0's gather must end with an error within the group timeout."""
+    sys.path.insert(0, str(ROOT))
+    import datetime
+
+    import torch.distributed as dist
+
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=5))
+    if rank == 1:
+        q.put((1, "left"))
+        q.close()
+        q.join_thread()
+        os._exit(0)  # leaves between steps, no collective in flight
+    try:
+        t = torch.zeros(4, 4)
+        out = torch.empty(8, 4)
+        dist.all_gather_into_tensor(out, t)
+        q.put((0, "completed"))
+    except Exception as ex:  # noqa: BLE001
+        q.put((0, "error:" + type(ex).__name__))
+    q.close()
+    q.join_thread()
+    os._exit(0)
+
+
+def test_rank_that_leaves_is_detected_by_group_timeout():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_failing_rank_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = dict(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+    assert results[1] == "left"
+    assert results[0].startswith("error:"), results
+
+
+# ---------------------------------------------------------------------------------------------------- bench contract
+def test_bench_reference_arm_prints_contract_line(monkeypatch, capsys):
+    """The CPU arm of bench.py on a tiny stand-in model: one JSON line with the contract's keys."""
+    import json
+
+    sys.path.insert(0, str(ROOT))
+    import bench
+    from oracle import inputs
+
+    small = inputs.EmbedModelConfig().small(layers=1, vocab=128)
+    monkeypatch.setattr(inputs, "EmbedModelConfig", lambda: small)
+    monkeypatch.setattr(bench, "SEQ", 64)
+
+    class A:
+        gpus, steps, warmup = 1, 1, 0
+
+    bench.run_reference_arm(A())
+    line = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    for key in ("impl", "metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better",
+                "scaling", "vs_baseline", "dtype", "data", "config", "cpu_baseline", "e2e"):
+        assert key in line
+    assert line["impl"] == "reference" and line["value"] > 0 and line["e2e"]["h2d_bytes_per_step"] == 0
