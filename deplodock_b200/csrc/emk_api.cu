@@ -30,6 +30,8 @@ extern "C" int emk_create(int device, emk_handle_t* out) {
   if (!h) return EMK_ERR_ARG;
   h->device = device;
   h->wait_limit_ns = 2000ull * 1000ull * 1000ull;
+  const char* impl = getenv("EMK_GEMM_IMPL");
+  h->gemm_impl = impl ? atoi(impl) : 0;
   cudaError_t e = cudaSetDevice(device);
   if (e != cudaSuccess) {
     free(h);

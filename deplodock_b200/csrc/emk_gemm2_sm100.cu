@@ -1,0 +1,253 @@
+// bf16 GEMM on CTA pairs (tcgen05 cta_group::2): two CTAs of a 2-CTA cluster compute one 256x256 output tile.
+//
+// Same contraction and epilogues as emk_gemm_sm100.cu (LinearOp / MatmulOp, emmy/compiler/ir/frontend/ir.py:202-237).
+// Each CTA loads its own 128 rows of A and its own 128 columns (half) of the W tile, the leader CTA's single MMA thread
+// issues 256x256x16 instructions that read A from each CTA's own shared memory and W halves from both, and each CTA's
+// tensor memory receives the accumulator rows it owns. Per CTA and K-block that is 32 KB of operand traffic instead of
+// 48 KB for the same math, and the shared-memory ring is six stages deep instead of four.
+//
+//   warp 4      TMA producer (both CTAs; byte counts are credited to the LEADER's full barrier)
+//   warp 5      MMA issuer (leader CTA only); tcgen05.commit arrives on the empty / tmem_full barriers of BOTH CTAs
+//   warps 0..3  epilogue (both CTAs, own accumulator rows); arrive on the leader's tmem_empty barrier
+// No load uses cluster multicast. Every wait is bounded; the two cluster-wide barriers at start and end are reached by
+// all threads of both CTAs on every path.
+#include "emk_gemm_common.cuh"
+
+namespace {
+
+using namespace emk;
+
+constexpr int G2_BN = 256;
+constexpr int G2_HALF_N = 128;
+constexpr int G2_STAGES = 6;
+constexpr int G2_THREADS = 192;
+constexpr int G2_GROUP_M = 8;  // row-tiles of 256 per raster group
+constexpr int G2_B_STAGE_BYTES = G2_HALF_N * BK * 2;
+constexpr uint32_t G2_STAGE_TX = 2u * (A_STAGE_BYTES + G2_B_STAGE_BYTES);  // both CTAs' bytes land on the leader barrier
+constexpr uint32_t G2_TMEM_COLS = 2 * G2_BN;
+
+struct __align__(8) G2Barriers {
+  uint64_t full[G2_STAGES];
+  uint64_t empty[G2_STAGES];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <int WL>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2_THREADS, 1)
+gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                  const GemmArgs g) {
+  constexpr uint32_t IDESC = make_idesc_bf16(2 * BM, G2_BN, 0, WL);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + G2_STAGES * A_STAGE_BYTES;
+  G2Barriers* bars = reinterpret_cast<G2Barriers*>(sB + G2_STAGES * G2_B_STAGE_BYTES);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1;
+  const int npairs = gridDim.x >> 1;
+  const int ntiles = g.tiles_m * g.tiles_n;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < G2_STAGES; ++i) {
+      mbar_init(&bars->full[i], 1);
+      mbar_init(&bars->empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->tmem_full[i], 1);
+      mbar_init(&bars->tmem_empty[i], 8);  // 4 epilogue warps of each CTA
+    }
+    bars->abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 4 && lane == 0) {
+    tma_prefetch_desc(&tma_a);
+    tma_prefetch_desc(&tma_b);
+  }
+  if (warp == 0) {
+    tmem_alloc_pair(&bars->tmem_base, G2_TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+  const WaitCtx wc{&bars->abort_flag, g.status, g.limit_ns};
+
+  if (warp == 4) {
+    // ---------------- TMA producer (both CTAs) ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < ntiles && ok; tile += npairs) {
+        int tm, tn;
+        tile_coords(tile, g.tiles_m, g.tiles_n, G2_GROUP_M, tm, tn);
+        const int m0 = tm * 2 * BM + (int)rank * BM;
+        const int n0 = tn * G2_BN + (int)rank * G2_HALF_N;
+        for (int kb = 0; kb < g.kblocks; ++kb) {
+          if (!mbar_wait(&bars->empty[stage], phase ^ 1u, wc, EMK_DEV_TIMEOUT_PRODUCER)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full_leader = mapa_u32(smem_u32(&bars->full[stage]), 0);
+          if (leader) mbar_arrive_expect_tx(&bars->full[stage], G2_STAGE_TX);
+          tma_load_2d_pair(sA + stage * A_STAGE_BYTES, &tma_a, full_leader, kb * BK, m0);
+          if (WL == 0) {
+            tma_load_2d_pair(sB + stage * G2_B_STAGE_BYTES, &tma_b, full_leader, kb * BK, n0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < G2_HALF_N / 64; ++c)
+              tma_load_2d_pair(sB + stage * G2_B_STAGE_BYTES + c * (BK * 128), &tma_b, full_leader, n0 + c * 64,
+                               kb * BK);
+          }
+          if (++stage == G2_STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // ---------------- MMA issuer (leader CTA only) ----------------
+    if (leader && lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      for (int tile = pair; tile < ntiles && ok; tile += npairs, ++local) {
+        const int acc = local & 1;
+        const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
+        if (!mbar_wait(&bars->tmem_empty[acc], acc_phase ^ 1u, wc, EMK_DEV_TIMEOUT_MMA)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * G2_BN);
+        for (int kb = 0; kb < g.kblocks; ++kb) {
+          if (!mbar_wait(&bars->full[stage], phase, wc, EMK_DEV_TIMEOUT_MMA)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(sA + stage * A_STAGE_BYTES);
+          const uint32_t b_addr = smem_u32(sB + stage * G2_B_STAGE_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t adesc = make_smem_desc(a_addr + k * 32, 0, 1024);
+            const uint64_t bdesc = (WL == 0) ? make_smem_desc(b_addr + k * 32, 0, 1024)
+                                             : make_smem_desc(b_addr + k * 16 * 128, BK * 128, 1024);
+            umma_ss_pair(d_tmem, adesc, bdesc, IDESC, (uint32_t)((kb | k) != 0));
+          }
+          const uint32_t e_local = smem_u32(&bars->empty[stage]);
+          tc_commit_pair(e_local);
+          tc_commit_pair(mapa_u32(e_local, 1));
+          if (++stage == G2_STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) {
+          const uint32_t f_local = smem_u32(&bars->tmem_full[acc]);
+          tc_commit_pair(f_local);
+          tc_commit_pair(mapa_u32(f_local, 1));
+        }
+      }
+    }
+  } else {
+    // ---------------- epilogue warps 0..3 (both CTAs) ----------------
+    int local = 0;
+    for (int tile = pair; tile < ntiles; tile += npairs, ++local) {
+      const int acc = local & 1;
+      const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
+      if (!mbar_wait_warp(&bars->tmem_full[acc], acc_phase, wc, EMK_DEV_TIMEOUT_EPILOGUE)) break;
+      tc_fence_after();
+      int tm, tn;
+      tile_coords(tile, g.tiles_m, g.tiles_n, G2_GROUP_M, tm, tn);
+      const int row = tm * 2 * BM + (int)rank * BM + warp * 32 + lane;
+      const int n0 = tn * G2_BN;
+      const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(acc * G2_BN);
+#pragma unroll 1
+      for (int c = 0; c < G2_BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_x32(taddr + (uint32_t)(c * 32), r);
+        tmem_ld_wait();
+        epilogue_store32(g, r, row, n0 + c * 32);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&bars->tmem_empty[acc]), 0));
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (bars->abort_flag) abort_drain();
+  cluster_sync_all();  // the peer's shared and tensor memory stay alive until the leader's MMAs are done
+  if (warp == 0) tmem_dealloc_pair(tmem_base, G2_TMEM_COLS);
+}
+
+constexpr int G2_SMEM = G2_STAGES * (A_STAGE_BYTES + G2_B_STAGE_BYTES) + 1024 + (int)sizeof(G2Barriers);
+
+template <int WL>
+int launch_gemm2(emk_handle_t h, const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, cudaStream_t s) {
+  static bool configured[64] = {false};
+  static int max_pairs[64] = {0};
+  auto kern = gemm2_bf16_kernel<WL>;
+  const int d = h->device < 64 ? h->device : 0;
+  if (!configured[d]) {
+    EMK_CUDA_TRY(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(h->sm_count & ~1), 1, 1);
+    cfg.blockDim = dim3(G2_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = G2_SMEM;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int nclusters = 0;
+    cudaError_t e = cudaOccupancyMaxActiveClusters(&nclusters, kern, &cfg);
+    if (e != cudaSuccess || nclusters <= 0) {
+      (void)cudaGetLastError();
+      nclusters = h->sm_count / 2;
+    }
+    max_pairs[d] = nclusters < h->sm_count / 2 ? nclusters : h->sm_count / 2;
+    configured[d] = true;
+  }
+  const int ntiles = g.tiles_m * g.tiles_n;
+  const int pairs = ntiles < max_pairs[d] ? ntiles : max_pairs[d];
+  kern<<<2 * pairs, G2_THREADS, G2_SMEM, s>>>(ta, tb, g);
+  EMK_LAUNCH_CHECK(h);
+  return EMK_OK;
+}
+
+}  // namespace
+
+// Called by the dispatcher in emk_gemm_sm100.cu. `g` arrives with tiles_m / tiles_n unset for this tiling.
+int emk_gemm2_launch(emk_handle_t h, const void* x, const void* w, emk::GemmArgs g, int wlayout, cudaStream_t s) {
+  g.tiles_m = (g.M + 2 * BM - 1) / (2 * BM);
+  g.tiles_n = (g.N + G2_BN - 1) / G2_BN;
+  CUtensorMap ta, tb;
+  int rc = emk_make_tmap_2d(h, &ta, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, (uint64_t)g.K, (uint64_t)g.M,
+                            (uint64_t)g.K * 2, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != EMK_OK) return rc;
+  if (wlayout == EMK_W_NK) {
+    rc = emk_make_tmap_2d(h, &tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w, (uint64_t)g.K, (uint64_t)g.N,
+                          (uint64_t)g.K * 2, BK, G2_HALF_N, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != EMK_OK) return rc;
+    return launch_gemm2<0>(h, ta, tb, g, s);
+  }
+  rc = emk_make_tmap_2d(h, &tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.N * 2,
+                        64, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != EMK_OK) return rc;
+  return launch_gemm2<1>(h, ta, tb, g, s);
+}

@@ -23,6 +23,19 @@ struct GemmArgs {
   unsigned long long limit_ns;
 };
 
+// Tile order of the persistent kernels: tiles are walked in groups of GROUP_M row-tiles by all column-tiles, rows
+// fastest inside a group, so the CTAs running at one time share a few A row-blocks and a few W column-blocks and
+// re-read them from L2 instead of HBM.
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int group_m, int& tm, int& tn) {
+  const int per_group = group_m * tiles_n;
+  const int group = tile / per_group;
+  const int first_m = group * group_m;
+  const int gsize = min(tiles_m - first_m, group_m);
+  const int in_group = tile - group * per_group;
+  tm = first_m + in_group % gsize;
+  tn = in_group / gsize;
+}
+
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + __expf(-g)); }
 
 // Epilogue for 32 accumulator columns [col0, col0+32) of one output row held by this thread.

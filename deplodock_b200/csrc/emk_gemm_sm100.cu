@@ -14,11 +14,14 @@
 // Every wait is bounded (emk::mbar_wait); after an expiry all roles fall through to the common teardown.
 #include "emk_gemm_common.cuh"
 
+int emk_gemm2_launch(emk_handle_t h, const void* x, const void* w, emk::GemmArgs g, int wlayout, cudaStream_t s);
+
 namespace {
 
 using namespace emk;
 
 constexpr int GEMM_THREADS = 192;
+constexpr int GROUP_M = 16;
 
 struct __align__(8) GemmBarriers {
   uint64_t full[8];
@@ -82,8 +85,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % g.tiles_m) * BM;
-        const int n0 = (tile / g.tiles_m) * BN;
+        int tm, tn;
+        tile_coords(tile, g.tiles_m, g.tiles_n, GROUP_M, tm, tn);
+        const int m0 = tm * BM;
+        const int n0 = tn * BN;
         for (int kb = 0; kb < g.kblocks; ++kb) {
           if (!mbar_wait(&bars->empty[stage], phase ^ 1u, wc, EMK_DEV_TIMEOUT_PRODUCER)) {
             ok = false;
@@ -151,8 +156,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
       if (!mbar_wait_warp(&bars->tmem_full[acc], acc_phase, wc, EMK_DEV_TIMEOUT_EPILOGUE)) break;
       tc_fence_after();
-      const int m0 = (tile % g.tiles_m) * BM;
-      const int n0 = (tile / g.tiles_m) * BN;
+      int tm, tn;
+      tile_coords(tile, g.tiles_m, g.tiles_n, GROUP_M, tm, tn);
+      const int m0 = tm * BM;
+      const int n0 = tn * BN;
       const int row = m0 + warp * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(acc * BN);
 #pragma unroll 1
@@ -222,6 +229,10 @@ int gemm_dispatch(emk_handle_t h, const void* x, const void* w, const void* resi
   g.epi = epilogue;
   g.status = h->status_dev;
   g.limit_ns = h->wait_limit_ns;
+
+  // CTA-pair tiles (256x256) when the problem has at least one full pair tile; single-CTA tiles otherwise.
+  const bool pair_ok = M > BM && N > 128;
+  if (h->gemm_impl == 2 || (h->gemm_impl == 0 && pair_ok)) return emk_gemm2_launch(h, x, w, g, wlayout, s);
 
   CUtensorMap ta, tb;
   int rc = emk_make_tmap_2d(h, &ta, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2,

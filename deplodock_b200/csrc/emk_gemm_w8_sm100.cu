@@ -94,8 +94,10 @@ gemm_w8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % g.tiles_m) * BM;
-        const int n0 = (tile / g.tiles_m) * W8_BN;
+        int tm, tn;
+        tile_coords(tile, g.tiles_m, g.tiles_n, 16, tm, tn);
+        const int m0 = tm * BM;
+        const int n0 = tn * W8_BN;
         for (int kb = 0; kb < g.kblocks; ++kb) {
           if (!mbar_wait(&bars->empty[stage], phase ^ 1u, wc, EMK_DEV_TIMEOUT_PRODUCER)) {
             ok = false;
@@ -192,8 +194,10 @@ gemm_w8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
       if (!mbar_wait_warp(&bars->tmem_full[acc], acc_phase, wc, EMK_DEV_TIMEOUT_EPILOGUE)) break;
       tc_fence_after();
-      const int m0 = (tile % g.tiles_m) * BM;
-      const int n0 = (tile / g.tiles_m) * W8_BN;
+      int tm, tn;
+      tile_coords(tile, g.tiles_m, g.tiles_n, 16, tm, tn);
+      const int m0 = tm * BM;
+      const int n0 = tn * W8_BN;
       const int row = m0 + warp * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(acc * W8_BN);
 #pragma unroll 1
