@@ -17,29 +17,30 @@ namespace {
 
 using namespace emk;
 
-constexpr int G2_BN = 256;
-constexpr int G2_HALF_N = 128;
-constexpr int G2_STAGES = 6;
 constexpr int G2_THREADS = 192;
 constexpr int G2_GROUP_M = 8;  // row-tiles of 256 per raster group
-constexpr int G2_B_STAGE_BYTES = G2_HALF_N * BK * 2;
-constexpr uint32_t G2_STAGE_TX = 2u * (A_STAGE_BYTES + G2_B_STAGE_BYTES);  // both CTAs' bytes land on the leader barrier
-constexpr uint32_t G2_TMEM_COLS = 2 * G2_BN;
+constexpr int G2_MAX_STAGES = 8;
 
 struct __align__(8) G2Barriers {
-  uint64_t full[G2_STAGES];
-  uint64_t empty[G2_STAGES];
+  uint64_t full[G2_MAX_STAGES];
+  uint64_t empty[G2_MAX_STAGES];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
   int abort_flag;
 };
 
-template <int WL>
+// G2_BN: tile width (256, 192 or 128 columns; each CTA loads half of them). Stage = 16 KB of A + G2_BN/2 rows of W.
+template <int G2_BN, int G2_STAGES, int WL>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2_THREADS, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                   const GemmArgs g) {
+  constexpr int G2_HALF_N = G2_BN / 2;
+  constexpr int G2_B_STAGE_BYTES = G2_HALF_N * BK * 2;
+  constexpr uint32_t G2_STAGE_TX = 2u * (A_STAGE_BYTES + G2_B_STAGE_BYTES);  // both CTAs' bytes land on the leader barrier
+  constexpr uint32_t G2_TMEM_COLS = (2 * G2_BN > 256) ? 512 : 256;
   constexpr uint32_t IDESC = make_idesc_bf16(2 * BM, G2_BN, 0, WL);
+  static_assert(WL == 0 || G2_HALF_N % 64 == 0, "MN-major W needs whole 64-column chunks per CTA");
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -172,13 +173,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       const int row = tm * 2 * BM + (int)rank * BM + warp * 32 + lane;
       const int n0 = tn * G2_BN;
       const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(acc * G2_BN);
-#pragma unroll 1
-      for (int c = 0; c < G2_BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_x32(taddr + (uint32_t)(c * 32), r);
-        tmem_ld_wait();
-        epilogue_store32(g, r, row, n0 + c * 32);
-      }
+      epilogue_drain<G2_BN / 32>(g, taddr, row, n0);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&bars->tmem_empty[acc]), 0));
@@ -193,13 +188,12 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
   if (warp == 0) tmem_dealloc_pair(tmem_base, G2_TMEM_COLS);
 }
 
-constexpr int G2_SMEM = G2_STAGES * (A_STAGE_BYTES + G2_B_STAGE_BYTES) + 1024 + (int)sizeof(G2Barriers);
-
-template <int WL>
+template <int G2_BN, int G2_STAGES, int WL>
 int launch_gemm2(emk_handle_t h, const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, cudaStream_t s) {
+  constexpr int G2_SMEM = G2_STAGES * (A_STAGE_BYTES + (G2_BN / 2) * BK * 2) + 1024 + (int)sizeof(G2Barriers);
   static bool configured[64] = {false};
   static int max_pairs[64] = {0};
-  auto kern = gemm2_bf16_kernel<WL>;
+  auto kern = gemm2_bf16_kernel<G2_BN, G2_STAGES, WL>;
   const int d = h->device < 64 ? h->device : 0;
   if (!configured[d]) {
     EMK_CUDA_TRY(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM));
@@ -230,24 +224,49 @@ int launch_gemm2(emk_handle_t h, const CUtensorMap& ta, const CUtensorMap& tb, c
   return EMK_OK;
 }
 
+// Tile width by wave count: with P CTA pairs resident, a width BN costs ceil(tiles / P) waves of BN columns each.
+int pick_tile_width(emk_handle_t h, int M, int N, bool allow_192) {
+  const int pairs = h->sm_count / 2;
+  const int tiles_m = (M + 2 * BM - 1) / (2 * BM);
+  int best = 256;
+  long best_cost = -1;
+  const int cands[3] = {256, 192, 128};
+  for (int i = 0; i < 3; ++i) {
+    const int bn = cands[i];
+    if (bn == 192 && !allow_192) continue;
+    const long tiles = (long)tiles_m * ((N + bn - 1) / bn);
+    const long waves = (tiles + pairs - 1) / pairs;
+    const long cost = waves * (bn + 16);  // + fixed per-tile overhead
+    if (best_cost < 0 || cost < best_cost) {
+      best_cost = cost;
+      best = bn;
+    }
+  }
+  return best;
+}
+
 }  // namespace
 
 // Called by the dispatcher in emk_gemm_sm100.cu. `g` arrives with tiles_m / tiles_n unset for this tiling.
 int emk_gemm2_launch(emk_handle_t h, const void* x, const void* w, emk::GemmArgs g, int wlayout, cudaStream_t s) {
+  const int bn = pick_tile_width(h, g.M, g.N, wlayout == EMK_W_NK);
   g.tiles_m = (g.M + 2 * BM - 1) / (2 * BM);
-  g.tiles_n = (g.N + G2_BN - 1) / G2_BN;
+  g.tiles_n = (g.N + bn - 1) / bn;
   CUtensorMap ta, tb;
   int rc = emk_make_tmap_2d(h, &ta, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, (uint64_t)g.K, (uint64_t)g.M,
                             (uint64_t)g.K * 2, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != EMK_OK) return rc;
   if (wlayout == EMK_W_NK) {
     rc = emk_make_tmap_2d(h, &tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w, (uint64_t)g.K, (uint64_t)g.N,
-                          (uint64_t)g.K * 2, BK, G2_HALF_N, CU_TENSOR_MAP_SWIZZLE_128B);
+                          (uint64_t)g.K * 2, BK, (uint32_t)(bn / 2), CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != EMK_OK) return rc;
-    return launch_gemm2<0>(h, ta, tb, g, s);
+    if (bn == 256) return launch_gemm2<256, 6, 0>(h, ta, tb, g, s);
+    if (bn == 192) return launch_gemm2<192, 7, 0>(h, ta, tb, g, s);
+    return launch_gemm2<128, 8, 0>(h, ta, tb, g, s);
   }
   rc = emk_make_tmap_2d(h, &tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.N * 2,
                         64, BK, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != EMK_OK) return rc;
-  return launch_gemm2<1>(h, ta, tb, g, s);
+  if (bn == 256) return launch_gemm2<256, 6, 1>(h, ta, tb, g, s);
+  return launch_gemm2<128, 8, 1>(h, ta, tb, g, s);
 }

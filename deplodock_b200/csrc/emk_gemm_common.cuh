@@ -19,6 +19,7 @@ struct GemmArgs {
   int ldy;
   int tiles_m, tiles_n, kblocks;
   int epi;
+  int wide;  // y (and residual) rows are 32-byte aligned: use 256-bit accesses
   int* status;
   unsigned long long limit_ns;
 };
@@ -38,71 +39,106 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
 
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + __expf(-g)); }
 
-// Epilogue for 32 accumulator columns [col0, col0+32) of one output row held by this thread.
+// Epilogue for 32 accumulator columns [col0, col0+32) of one output row held by this thread. `g.wide` says rows of
+// y (and of the residual) are 32-byte aligned, so full 32-column groups move as 256-bit accesses.
 __device__ __forceinline__ void epilogue_store32(const GemmArgs& g, const uint32_t* r, int row, int col0) {
   if (row >= g.M || col0 >= g.N) return;
   if (g.epi == EMK_EPI_SWIGLU) {
-    // columns are (gate, up) pairs; 16 outputs
+    // columns are (gate, up) pairs; 16 outputs = 32 bytes
     __nv_bfloat16* out = g.y + (int64_t)row * g.ldy + (col0 >> 1);
+    uint32_t o[8];
 #pragma unroll
-    for (int q = 0; q < 2; ++q) {
-      if (col0 + q * 16 < g.N) {
-        uint32_t o[4];
+    for (int j = 0; j < 8; ++j) {
+      float v[2];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          float v[2];
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int idx = q * 16 + j * 4 + e * 2;
-            const float gate = bf16_round(__uint_as_float(r[idx]));
-            const float up = bf16_round(__uint_as_float(r[idx + 1]));
-            v[e] = bf16_round(silu_f(gate)) * up;
-          }
-          o[j] = pack_bf16x2(v[0], v[1]);
-        }
-        *reinterpret_cast<uint4*>(out + q * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+      for (int e = 0; e < 2; ++e) {
+        const int idx = j * 4 + e * 2;
+        const float gate = bf16_round(__uint_as_float(r[idx]));
+        const float up = bf16_round(__uint_as_float(r[idx + 1]));
+        v[e] = bf16_round(silu_f(gate)) * up;
       }
+      o[j] = pack_bf16x2(v[0], v[1]);
+    }
+    if (g.wide && col0 + 32 <= g.N) {
+      st_global_v8(out, o);
+    } else {
+      if (col0 < g.N) *reinterpret_cast<uint4*>(out) = make_uint4(o[0], o[1], o[2], o[3]);
+      if (col0 + 16 < g.N) *reinterpret_cast<uint4*>(out + 8) = make_uint4(o[4], o[5], o[6], o[7]);
     }
     return;
   }
-  __nv_bfloat16* out = g.y + (int64_t)row * g.ldy + col0;
+  const bool full = g.wide && (col0 + 32 <= g.N);
+  float v[32];
 #pragma unroll
-  for (int q = 0; q < 4; ++q) {
-    const int col = col0 + q * 8;
-    if (col < g.N) {
-      float v[8];
+  for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(r[e]);
+  if (g.scale != nullptr) {
 #pragma unroll
-      for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[q * 8 + e]);
-      if (g.scale != nullptr) {
-        const float4 s0 = __ldg(reinterpret_cast<const float4*>(g.scale + col));
-        const float4 s1 = __ldg(reinterpret_cast<const float4*>(g.scale + col + 4));
-        v[0] *= s0.x; v[1] *= s0.y; v[2] *= s0.z; v[3] *= s0.w;
-        v[4] *= s1.x; v[5] *= s1.y; v[6] *= s1.z; v[7] *= s1.w;
+    for (int q = 0; q < 8; ++q) {
+      if (col0 + q * 4 < g.N) {
+        const float4 s = __ldg(reinterpret_cast<const float4*>(g.scale + col0 + q * 4));
+        v[q * 4 + 0] *= s.x; v[q * 4 + 1] *= s.y; v[q * 4 + 2] *= s.z; v[q * 4 + 3] *= s.w;
       }
-      if (g.epi == EMK_EPI_RESIDUAL) {
-        const uint4 rv = *reinterpret_cast<const uint4*>(g.residual + (int64_t)row * g.ldy + col);
-        const uint32_t rr[4] = {rv.x, rv.y, rv.z, rv.w};
+    }
+  }
+  if (g.epi == EMK_EPI_RESIDUAL) {
+    const __nv_bfloat16* res = g.residual + (int64_t)row * g.ldy + col0;
+    uint32_t rr[16];
+    if (full) {
+      ld_global_v8(res, rr);
+      ld_global_v8(res + 16, rr + 8);
+    } else {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          v[2 * e] = bf16_round(v[2 * e]) + bf16_lo(rr[e]);
-          v[2 * e + 1] = bf16_round(v[2 * e + 1]) + bf16_hi(rr[e]);
-        }
-      } else if (g.epi == EMK_EPI_BIAS) {
-        const uint4 bv = __ldg(reinterpret_cast<const uint4*>(g.residual + col));
+      for (int q = 0; q < 4; ++q) {
+        uint4 t = make_uint4(0, 0, 0, 0);
+        if (col0 + q * 8 < g.N) t = *reinterpret_cast<const uint4*>(res + q * 8);
+        rr[q * 4 + 0] = t.x; rr[q * 4 + 1] = t.y; rr[q * 4 + 2] = t.z; rr[q * 4 + 3] = t.w;
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 16; ++e) {
+      v[2 * e] = bf16_round(v[2 * e]) + bf16_lo(rr[e]);
+      v[2 * e + 1] = bf16_round(v[2 * e + 1]) + bf16_hi(rr[e]);
+    }
+  } else if (g.epi == EMK_EPI_BIAS) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      if (col0 + q * 8 < g.N) {
+        const uint4 bv = __ldg(reinterpret_cast<const uint4*>(g.residual + col0 + q * 8));
         const uint32_t bb[4] = {bv.x, bv.y, bv.z, bv.w};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          v[2 * e] += bf16_lo(bb[e]);
-          v[2 * e + 1] += bf16_hi(bb[e]);
+          v[q * 8 + 2 * e] += bf16_lo(bb[e]);
+          v[q * 8 + 2 * e + 1] += bf16_hi(bb[e]);
         }
       }
-      uint4 o;
-      o.x = pack_bf16x2(v[0], v[1]);
-      o.y = pack_bf16x2(v[2], v[3]);
-      o.z = pack_bf16x2(v[4], v[5]);
-      o.w = pack_bf16x2(v[6], v[7]);
-      *reinterpret_cast<uint4*>(out + q * 8) = o;
     }
+  }
+  uint32_t o[16];
+#pragma unroll
+  for (int e = 0; e < 16; ++e) o[e] = pack_bf16x2(v[2 * e], v[2 * e + 1]);
+  __nv_bfloat16* out = g.y + (int64_t)row * g.ldy + col0;
+  if (full) {
+    st_global_v8(out, o);
+    st_global_v8(out + 16, o + 8);
+  } else {
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+      if (col0 + q * 8 < g.N)
+        *reinterpret_cast<uint4*>(out + q * 8) = make_uint4(o[q * 4], o[q * 4 + 1], o[q * 4 + 2], o[q * 4 + 3]);
+  }
+}
+
+// Drains one accumulator (NCHUNK x 32 columns of this thread's row) from tensor memory through the epilogue. The load
+// of chunk c+1 is in flight while chunk c is converted and stored.
+template <int NCHUNK>
+__device__ __forceinline__ void epilogue_drain(const GemmArgs& g, uint32_t taddr, int row, int n0) {
+  uint32_t r[2][32];
+  tmem_ld_x32(taddr, r[0]);
+#pragma unroll
+  for (int c = 0; c < NCHUNK; ++c) {
+    tmem_ld_wait_regs(r[c & 1]);
+    if (c + 1 < NCHUNK) tmem_ld_x32(taddr + (uint32_t)((c + 1) * 32), r[(c + 1) & 1]);
+    epilogue_store32(g, r[c & 1], row, n0 + c * 32);
   }
 }
 

@@ -162,13 +162,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       const int n0 = tn * BN;
       const int row = m0 + warp * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(acc * BN);
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_x32(taddr + (uint32_t)(c * 32), r);
-        tmem_ld_wait();
-        epilogue_store32(g, r, row, n0 + c * 32);
-      }
+epilogue_drain<BN / 32>(g, taddr, row, n0);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->tmem_empty[acc]);
@@ -227,6 +221,7 @@ int gemm_dispatch(emk_handle_t h, const void* x, const void* w, const void* resi
   g.tiles_n = (int)((N + BN - 1) / BN);
   g.kblocks = (int)((K + BK - 1) / BK);
   g.epi = epilogue;
+  g.wide = ((g.ldy % 16) == 0 && ((uintptr_t)y & 31u) == 0 && ((uintptr_t)residual & 31u) == 0) ? 1 : 0;
   g.status = h->status_dev;
   g.limit_ns = h->wait_limit_ns;
 

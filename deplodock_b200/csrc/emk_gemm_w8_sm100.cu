@@ -200,13 +200,7 @@ gemm_w8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       const int n0 = tn * W8_BN;
       const int row = m0 + warp * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(acc * W8_BN);
-#pragma unroll 1
-      for (int cc = 0; cc < W8_BN / 32; ++cc) {
-        uint32_t r[32];
-        tmem_ld_x32(taddr + (uint32_t)(cc * 32), r);
-        tmem_ld_wait();
-        epilogue_store32(g, r, row, n0 + cc * 32);
-      }
+epilogue_drain<W8_BN / 32>(g, taddr, row, n0);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->tmem_empty[acc]);
@@ -245,6 +239,7 @@ extern "C" int emk_linear_bf16_w8(emk_handle_t h, const void* x, const void* w_e
   g.tiles_n = (int)((N + W8_BN - 1) / W8_BN);
   g.kblocks = (int)((K + BK - 1) / BK);
   g.epi = EMK_EPI_NONE;
+  g.wide = ((N % 16) == 0 && ((uintptr_t)y & 31u) == 0) ? 1 : 0;
   g.status = h->status_dev;
   g.limit_ns = h->wait_limit_ns;
   CUtensorMap ta, tw;

@@ -29,48 +29,75 @@ __global__ void __launch_bounds__(256) embed_gather_kernel(const uint4* __restri
   for (int i = lane; i < vec_per_row; i += 32) dst[i] = __ldg(src + i);
 }
 
-// One CTA (8 warps) per token; warp w handles heads w, w+8, ... of the Hq query heads followed by the Hkv key heads.
-// A head is 128 bf16: lane l owns elements 4l..4l+3, its rotate-half partner (element +-64) lives in lane l^16.
+// Sixteen lanes per (token, head): a head is 128 bf16, lane j of the group owns elements 8j..8j+7 (one 16-byte
+// access); its rotate-half partner (element +-64) lives in lane j^8. Each thread handles two heads per pass so two
+// loads are in flight. cos/sin tables are bf16 [S,128] (the eager bf16 module multiplies by bf16 tables).
+__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
+  f[0] = bf16_lo(v.x); f[1] = bf16_hi(v.x); f[2] = bf16_lo(v.y); f[3] = bf16_hi(v.y);
+  f[4] = bf16_lo(v.z); f[5] = bf16_hi(v.z); f[6] = bf16_lo(v.w); f[7] = bf16_hi(v.w);
+}
+
 __global__ void __launch_bounds__(256) qknorm_rope_kernel(__nv_bfloat16* __restrict__ qkv,
                                                           const __nv_bfloat16* __restrict__ qw,
                                                           const __nv_bfloat16* __restrict__ kw,
-                                                          const float* __restrict__ cosb, const float* __restrict__ sinb,
-                                                          int64_t tokens, int S, int Hq, int Hkv, float eps) {
-  const int64_t t = blockIdx.x;
-  if (t >= tokens) return;
-  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-  const int s = (int)(t % S);
+                                                          const __nv_bfloat16* __restrict__ cosb,
+                                                          const __nv_bfloat16* __restrict__ sinb, int64_t tokens, int S,
+                                                          int Hq, int Hkv, float eps) {
+  const int sub = threadIdx.x & 15;
+  const int nh = Hq + Hkv;
   const int ld = (Hq + 2 * Hkv) * 128;
-  __nv_bfloat16* row = qkv + t * ld;
-  const float4 c4 = *reinterpret_cast<const float4*>(cosb + (int64_t)s * 128 + lane * 4);
-  const float4 s4 = *reinterpret_cast<const float4*>(sinb + (int64_t)s * 128 + lane * 4);
-  const float cs[4] = {c4.x, c4.y, c4.z, c4.w};
-  const float sn[4] = {s4.x, s4.y, s4.z, s4.w};
-  const uint2 qwv = *reinterpret_cast<const uint2*>(qw + lane * 4);
-  const uint2 kwv = *reinterpret_cast<const uint2*>(kw + lane * 4);
-  for (int head = wid; head < Hq + Hkv; head += 8) {
-    const uint2 wv = head < Hq ? qwv : kwv;
-    const float wf[4] = {bf16_lo(wv.x), bf16_hi(wv.x), bf16_lo(wv.y), bf16_hi(wv.y)};
-    __nv_bfloat16* p = row + head * 128 + lane * 4;
-    const uint2 xv = *reinterpret_cast<const uint2*>(p);
-    float xf[4] = {bf16_lo(xv.x), bf16_hi(xv.x), bf16_lo(xv.y), bf16_hi(xv.y)};
-    float ss = xf[0] * xf[0] + xf[1] * xf[1] + xf[2] * xf[2] + xf[3] * xf[3];
-    ss = warp_sum(ss);
-    const float r = 1.0f / sqrtf(ss * (1.0f / 128.0f) + eps);
-    float nrm[4], out[4];
+  const int64_t items = tokens * nh;
+  const int64_t groups = (int64_t)gridDim.x * (blockDim.x >> 4);
+  const int64_t gid = (int64_t)blockIdx.x * (blockDim.x >> 4) + (threadIdx.x >> 4);
+  float qwf[8], kwf[8];
+  unpack8(*reinterpret_cast<const uint4*>(qw + sub * 8), qwf);
+  unpack8(*reinterpret_cast<const uint4*>(kw + sub * 8), kwf);
+  // Items are walked in pairs (it, it + groups) so both loads are issued before either is used. The loop bound is
+  // taken from the first group of the warp so both 16-lane groups make the same number of trips (the shuffles below
+  // name the whole warp); a group without an item recomputes the last item and skips the store.
+  for (int64_t itb = gid & ~(int64_t)1; itb < items; itb += 2 * groups) {
+    const int64_t it_raw = itb + (gid & 1);
+    const bool has1 = it_raw < items;
+    const int64_t it = has1 ? it_raw : items - 1;
+    const int64_t it2 = it_raw + groups;
+    const bool has2 = it2 < items;
+    const int64_t t0 = it / nh, t1 = has2 ? it2 / nh : t0;
+    const int h0 = (int)(it % nh), h1 = has2 ? (int)(it2 % nh) : h0;
+    __nv_bfloat16* p0 = qkv + t0 * ld + h0 * 128 + sub * 8;
+    __nv_bfloat16* p1 = qkv + t1 * ld + h1 * 128 + sub * 8;
+    const uint4 x0 = *reinterpret_cast<const uint4*>(p0);
+    const uint4 x1 = *reinterpret_cast<const uint4*>(p1);
+    const int s0 = (int)(t0 % S), s1 = (int)(t1 % S);
+    const uint4 c0 = __ldg(reinterpret_cast<const uint4*>(cosb + (int64_t)s0 * 128 + sub * 8));
+    const uint4 n0 = __ldg(reinterpret_cast<const uint4*>(sinb + (int64_t)s0 * 128 + sub * 8));
+    const uint4 c1 = __ldg(reinterpret_cast<const uint4*>(cosb + (int64_t)s1 * 128 + sub * 8));
+    const uint4 n1 = __ldg(reinterpret_cast<const uint4*>(sinb + (int64_t)s1 * 128 + sub * 8));
 #pragma unroll
-    for (int e = 0; e < 4; ++e) nrm[e] = bf16_round(wf[e] * bf16_round(xf[e] * r));
+    for (int u = 0; u < 2; ++u) {
+      float xf[8], cs[8], sn[8];
+      unpack8(u ? x1 : x0, xf);
+      unpack8(u ? c1 : c0, cs);
+      unpack8(u ? n1 : n0, sn);
+      const float* wf = ((u ? h1 : h0) < Hq) ? qwf : kwf;
+      float ss = 0.f;
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const float partner = __shfl_xor_sync(0xffffffffu, nrm[e], 16);
-      // rotate_half: first half takes -x[i+64], second half takes x[i-64]
-      const float rot = lane < 16 ? -partner : partner;
-      out[e] = bf16_round(bf16_round(nrm[e] * cs[e]) + bf16_round(rot * sn[e]));
+      for (int e = 0; e < 8; ++e) ss = fmaf(xf[e], xf[e], ss);
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      const float r = 1.0f / sqrtf(ss * (1.0f / 128.0f) + eps);
+      float out[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float nrm = bf16_round(wf[e] * bf16_round(xf[e] * r));
+        const float partner = __shfl_xor_sync(0xffffffffu, nrm, 8);
+        const float rot = sub < 8 ? -partner : partner;  // rotate_half: first half takes -x[i+64], second x[i-64]
+        out[e] = bf16_round(nrm * cs[e]) + bf16_round(rot * sn[e]);
+      }
+      uint4 o;
+      o.x = pack_bf16x2(out[0], out[1]); o.y = pack_bf16x2(out[2], out[3]);
+      o.z = pack_bf16x2(out[4], out[5]); o.w = pack_bf16x2(out[6], out[7]);
+      if (u == 0 ? has1 : has2) *reinterpret_cast<uint4*>(u ? p1 : p0) = o;
     }
-    uint2 o;
-    o.x = pack_bf16x2(out[0], out[1]);
-    o.y = pack_bf16x2(out[2], out[3]);
-    *reinterpret_cast<uint2*>(p) = o;
   }
 }
 
@@ -128,15 +155,18 @@ extern "C" int emk_embed_gather(emk_handle_t h, const void* table, const int64_t
   return EMK_OK;
 }
 
-extern "C" int emk_qknorm_rope(emk_handle_t h, void* qkv, const void* qw, const void* kw, const float* cosb,
-                               const float* sinb, int64_t tokens, int64_t S, int64_t Hq, int64_t Hkv, float eps,
+extern "C" int emk_qknorm_rope(emk_handle_t h, void* qkv, const void* qw, const void* kw, const void* cosb,
+                               const void* sinb, int64_t tokens, int64_t S, int64_t Hq, int64_t Hkv, float eps,
                                emk_stream_t stream) {
   if (!h || !qkv || !qw || !kw || !cosb || !sinb) return EMK_ERR_ARG;
   if (tokens <= 0 || S <= 0 || Hq <= 0 || Hkv <= 0) return EMK_ERR_SHAPE;
   if ((((uintptr_t)qkv | (uintptr_t)qw | (uintptr_t)kw | (uintptr_t)cosb | (uintptr_t)sinb) & 15u)) return EMK_ERR_ALIGN;
-  qknorm_rope_kernel<<<(unsigned)tokens, 256, 0, (cudaStream_t)stream>>>(
-      (__nv_bfloat16*)qkv, (const __nv_bfloat16*)qw, (const __nv_bfloat16*)kw, cosb, sinb, tokens, (int)S, (int)Hq,
-      (int)Hkv, eps);
+  const int64_t items = tokens * (Hq + Hkv);
+  int64_t grid = (items + 31) / 32;  // 16 groups per CTA, two items per group and pass
+  if (grid > (int64_t)h->sm_count * 64) grid = (int64_t)h->sm_count * 64;
+  qknorm_rope_kernel<<<(unsigned)grid, 256, 0, (cudaStream_t)stream>>>(
+      (__nv_bfloat16*)qkv, (const __nv_bfloat16*)qw, (const __nv_bfloat16*)kw, (const __nv_bfloat16*)cosb,
+      (const __nv_bfloat16*)sinb, tokens, (int)S, (int)Hq, (int)Hkv, eps);
   EMK_LAUNCH_CHECK(h);
   return EMK_OK;
 }

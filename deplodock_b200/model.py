@@ -57,13 +57,12 @@ class EmbedConfig:
 
 
 def rope_tables(seq: int, head_dim: int, theta: float, device) -> tuple[torch.Tensor, torch.Tensor]:
-    """cos/sin ``[seq, head_dim]`` as HF builds them (``cat(freqs, freqs)``), rounded to bf16 like the eager bf16
-    module and stored as fp32 for the kernel."""
+    """cos/sin ``[seq, head_dim]`` bf16 as HF builds them for a bf16 module (``cat(freqs, freqs)``, cast to bf16)."""
     inv_freq = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.int64).float() / head_dim))
     freqs = torch.outer(torch.arange(seq, dtype=torch.float32), inv_freq)
     emb = torch.cat([freqs, freqs], dim=-1)
-    cos = emb.cos().to(torch.bfloat16).float().contiguous().to(device)
-    sin = emb.sin().to(torch.bfloat16).float().contiguous().to(device)
+    cos = emb.cos().to(torch.bfloat16).contiguous().to(device)
+    sin = emb.sin().to(torch.bfloat16).contiguous().to(device)
     return cos, sin
 
 

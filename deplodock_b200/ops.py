@@ -241,8 +241,8 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, out=None) -> torch.Tens
 def qknorm_rope_(qkv, q_weight, k_weight, cos, sin, S: int, Hq: int, Hkv: int, eps: float = 1e-6) -> torch.Tensor:
     """In place on the fused projection ``[T,(Hq+2Hkv)*128]``: per-head RMSNorm of q and k, then rotate-half RoPE."""
     _check_cuda_contig(qkv, q_weight, k_weight, cos, sin)
-    if qkv.dtype != torch.bfloat16 or cos.dtype != torch.float32 or sin.dtype != torch.float32:
-        raise TypeError("qknorm_rope_ expects bfloat16 qkv and float32 cos/sin tables")
+    if qkv.dtype != torch.bfloat16 or cos.dtype != torch.bfloat16 or sin.dtype != torch.bfloat16:
+        raise TypeError("qknorm_rope_ expects bfloat16 qkv and bfloat16 cos/sin tables")
     tokens = qkv.numel() // qkv.shape[-1]
     if qkv.shape[-1] != (Hq + 2 * Hkv) * 128 or cos.shape[-2:] != (S, 128) or tokens % S != 0:
         raise ValueError("qkv/cos shapes do not match S, Hq, Hkv")

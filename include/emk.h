@@ -125,11 +125,11 @@ int emk_sdpa_causal_gqa_bf16_tok(emk_handle_t h, const void* q, const void* k, c
 
 /* In place on the fused QKV projection output [T, (Hq+2*Hkv)*128] (T tokens, bf16, position of token t = t % S):
  * per-head RMSNorm (weights qw, kw [128] bf16, eps) on the Hq query heads and Hkv key heads, then rotate-half RoPE
- * with cos/sin tables [S,128] fp32; the value heads are left untouched. Replaces the k_mean_linear_reduce_* q/k-norm
+ * with cos/sin tables [S,128] bf16 (the eager bf16 module multiplies by bf16 tables); the value heads are left untouched. Replaces the k_mean_linear_reduce_* q/k-norm
  * kernels and the k_cat_slice_transpose_unsqueeze_pointwise_* RoPE kernel of the reference's lowering of the traced
  * layer (traced pattern: emmy/compiler/trace/huggingface.py:17-186). */
-int emk_qknorm_rope(emk_handle_t h, void* qkv, const void* qw, const void* kw, const float* cos_table,
-                    const float* sin_table, int64_t tokens, int64_t S, int64_t Hq, int64_t Hkv, float eps,
+int emk_qknorm_rope(emk_handle_t h, void* qkv, const void* qw, const void* kw, const void* cos_table,
+                    const void* sin_table, int64_t tokens, int64_t S, int64_t Hq, int64_t Hkv, float eps,
                     emk_stream_t stream);
 
 /* Last-token pooling + final RMSNorm + L2 normalisation: for each sequence b, takes row (b*S + S-1) of hidden

@@ -308,7 +308,7 @@ def test_qknorm_rope_bit_exact_vs_eager_module(ops):
     c4, s4 = cb[None, :, None, :], sb[None, :, None, :]
     ref[:, : Hq * D] = ((q * c4) + (rot(q) * s4)).reshape(B * S, -1)
     ref[:, Hq * D: (Hq + Hkv) * D] = ((k * c4) + (rot(k) * s4)).reshape(B * S, -1)
-    got = ops.qknorm_rope_(_dev(qkv), _dev(qw), _dev(kw), _dev(cb.float()), _dev(sb.float()), S, Hq, Hkv, 1e-6).cpu()
+    got = ops.qknorm_rope_(_dev(qkv), _dev(qw), _dev(kw), _dev(cb), _dev(sb), S, Hq, Hkv, 1e-6).cpu()
     ops.device_status()
     assert torch.equal(got[:, (Hq + Hkv) * D:], qkv[:, (Hq + Hkv) * D:])  # V untouched
     mism = (got != ref).float().mean().item()
