@@ -20,6 +20,7 @@
 #include "emk_common.cuh"
 
 #include <math_constants.h>
+#include <stdlib.h>
 
 namespace {
 
@@ -46,6 +47,7 @@ struct FmhaArgs {
   int o_cs, o_rb, o_rh;
   int64_t ld_o;
   float scale_log2;
+  int dbg;
   int* status;
   unsigned long long limit_ns;
 };
@@ -63,6 +65,31 @@ __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// Packed fp32 pairs (two lanes per instruction on the FMA pipe).
+__device__ __forceinline__ unsigned long long pack_f32x2(float lo, float hi) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(unsigned long long v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long fma_f32x2(unsigned long long a, unsigned long long b,
+                                                        unsigned long long c) {
+  unsigned long long d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ unsigned long long add_f32x2(unsigned long long a, unsigned long long b) {
+  unsigned long long d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
 }
 
 __global__ void __launch_bounds__(FMHA_THREADS, 1)
@@ -101,7 +128,7 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars->s_full[i], 1);
-      mbar_init(&bars->p_full[i], 128);
+      mbar_init(&bars->p_full[i], 4);  // one arrival per softmax warp
       mbar_init(&bars->o_done[i], 1);
     }
     bars->abort_flag = 0;
@@ -234,19 +261,23 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
 #pragma unroll
         for (int c = 0; c < FN / 32; ++c) tmem_ld_x32(tS + (uint32_t)(c * 32), s + c * 32);
         tmem_ld_wait();
-        float mx = -CUDART_INF_F;
         if (j == nblk - 1) {
           // diagonal block: key index k0 + i is visible to query q_row iff k0 + i <= q_row, k0 == q0 here
 #pragma unroll
-          for (int i = 0; i < FN; ++i) {
-            const float v = (i <= r_in_tile) ? __uint_as_float(s[i]) : -CUDART_INF_F;
-            s[i] = __float_as_uint(v);
-            mx = fmaxf(mx, v);
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < FN; ++i) mx = fmaxf(mx, __uint_as_float(s[i]));
+          for (int i = 0; i < FN; ++i)
+            if (i > r_in_tile) s[i] = __float_as_uint(-CUDART_INF_F);
         }
+        // four independent 3-input max chains instead of one 128-long dependency chain
+        float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F, mx2 = -CUDART_INF_F, mx3 = -CUDART_INF_F;
+#pragma unroll
+        for (int i = 0; i < FN; i += 8) {
+          mx0 = max3(mx0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+          mx1 = max3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+          mx2 = max3(mx2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
+          mx3 = max3(mx3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
+        }
+        float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+        if (a.dbg & 4) mx = 0.f;
         const float m_new = fmaxf(m_used, mx * a.scale_log2);
         const bool need = (m_new - m_used) > RESCALE_THRESHOLD;  // true on the first block (m_used = -inf)
         if (__any_sync(0xffffffffu, need)) {
@@ -271,22 +302,37 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
           }
           m_used = m_new;
         }
-        const float neg_m = -m_used;
-        float sum = 0.f;
+        const unsigned long long neg_m2 = pack_f32x2(-m_used, -m_used);
+        const unsigned long long scale2 = pack_f32x2(a.scale_log2, a.scale_log2);
+        unsigned long long sum_a = 0ull, sum_b = 0ull;  // two independent packed accumulators (4 partial sums)
         uint32_t p[FN / 2];
 #pragma unroll
-        for (int i = 0; i < FN / 2; ++i) {
-          const float p0 = ex2_approx(fmaf(__uint_as_float(s[2 * i]), a.scale_log2, neg_m));
-          const float p1 = ex2_approx(fmaf(__uint_as_float(s[2 * i + 1]), a.scale_log2, neg_m));
-          sum += p0 + p1;
+        for (int i = 0; i < FN / 2; i += 2) {
+          float t0, t1, t2, t3;
+          unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1])), scale2, neg_m2),
+                       t0, t1);
+          unpack_f32x2(
+              fma_f32x2(pack_f32x2(__uint_as_float(s[2 * i + 2]), __uint_as_float(s[2 * i + 3])), scale2, neg_m2), t2,
+              t3);
+          float p0, p1, p2, p3;
+          if (a.dbg & 1) { p0 = t0; p1 = t1; p2 = t2; p3 = t3; } else { p0 = ex2_approx(t0); p1 = ex2_approx(t1); p2 = ex2_approx(t2); p3 = ex2_approx(t3); }
+          sum_a = add_f32x2(sum_a, pack_f32x2(p0, p1));
+          sum_b = add_f32x2(sum_b, pack_f32x2(p2, p3));
           p[i] = pack_bf16x2(p0, p1);
+          p[i + 1] = pack_bf16x2(p2, p3);
         }
-        l += sum;
+        {
+          float a0, a1, b0, b1;
+          unpack_f32x2(sum_a, a0, a1);
+          unpack_f32x2(sum_b, b0, b1);
+          l += (a0 + a1) + (b0 + b1);
+        }
         tmem_st_x32(tS, p);
         tmem_st_x32(tS + 32u, p + 32);
         tmem_st_wait();
         tc_fence_before();
-        mbar_arrive(&bars->p_full[t]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->p_full[t]);
       }
       if (ok && mbar_wait_warp(&bars->o_done[t], (uint32_t)(nblk - 1) & 1u, wc, EMK_DEV_TIMEOUT_SOFTMAX)) {
         tc_fence_after();
@@ -354,6 +400,7 @@ int fmha_launch(emk_handle_t h, const void* q, const void* k, const void* v, voi
   a.scale_log2 = scale * 1.4426950408889634f;
   a.status = h->status_dev;
   a.limit_ns = h->wait_limit_ns;
+  { const char* d = getenv("EMK_FMHA_DBG"); a.dbg = d ? atoi(d) : 0; }
 
   CUtensorMap tq, tk, tv;
   int rc;

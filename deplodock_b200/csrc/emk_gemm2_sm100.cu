@@ -4,7 +4,8 @@
 // Each CTA loads its own 128 rows of A and its own 128 columns (half) of the W tile, the leader CTA's single MMA thread
 // issues 256x256x16 instructions that read A from each CTA's own shared memory and W halves from both, and each CTA's
 // tensor memory receives the accumulator rows it owns. Per CTA and K-block that is 32 KB of operand traffic instead of
-// 48 KB for the same math, and the shared-memory ring is six stages deep instead of four.
+// 48 KB for the same math. A ring stage carries two 64-wide K slices (eight MMAs per barrier round trip): with one
+// slice per stage the single MMA thread spent as long on waits and commits as the tensor core on the math.
 //
 //   warp 4      TMA producer (both CTAs; byte counts are credited to the LEADER's full barrier)
 //   warp 5      MMA issuer (leader CTA only); tcgen05.commit arrives on the empty / tmem_full barriers of BOTH CTAs
@@ -12,6 +13,8 @@
 // No load uses cluster multicast. Every wait is bounded; the two cluster-wide barriers at start and end are reached by
 // all threads of both CTAs on every path.
 #include "emk_gemm_common.cuh"
+
+#include <stdlib.h>
 
 namespace {
 
@@ -30,14 +33,17 @@ struct __align__(8) G2Barriers {
   int abort_flag;
 };
 
-// G2_BN: tile width (256, 192 or 128 columns; each CTA loads half of them). Stage = 16 KB of A + G2_BN/2 rows of W.
-template <int G2_BN, int G2_STAGES, int WL>
+// G2_BN: tile width (256 or 128 columns; each CTA loads half of them). A ring stage holds KSUB 64-wide K slices:
+// KSUB x (16 KB of A + G2_BN/2 rows of W).
+template <int G2_BN, int G2_STAGES, int WL, int KSUB>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2_THREADS, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                   const GemmArgs g) {
   constexpr int G2_HALF_N = G2_BN / 2;
-  constexpr int G2_B_STAGE_BYTES = G2_HALF_N * BK * 2;
-  constexpr uint32_t G2_STAGE_TX = 2u * (A_STAGE_BYTES + G2_B_STAGE_BYTES);  // both CTAs' bytes land on the leader barrier
+  constexpr int G2_B_SUB_BYTES = G2_HALF_N * BK * 2;        // one 64-wide K slice of this CTA's W half
+  constexpr int G2_A_STAGE = KSUB * A_STAGE_BYTES;          // a stage holds KSUB consecutive 64-wide K slices
+  constexpr int G2_B_STAGE_BYTES = KSUB * G2_B_SUB_BYTES;
+  constexpr uint32_t G2_STAGE_TX = 2u * (G2_A_STAGE + G2_B_STAGE_BYTES);  // both CTAs' bytes land on the leader barrier
   constexpr uint32_t G2_TMEM_COLS = (2 * G2_BN > 256) ? 512 : 256;
   constexpr uint32_t IDESC = make_idesc_bf16(2 * BM, G2_BN, 0, WL);
   static_assert(WL == 0 || G2_HALF_N % 64 == 0, "MN-major W needs whole 64-column chunks per CTA");
@@ -45,7 +51,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sA = smem;
-  uint8_t* sB = smem + G2_STAGES * A_STAGE_BYTES;
+  uint8_t* sB = smem + G2_STAGES * G2_A_STAGE;
   G2Barriers* bars = reinterpret_cast<G2Barriers*>(sB + G2_STAGES * G2_B_STAGE_BYTES);
 
   const int warp = threadIdx.x >> 5;
@@ -94,21 +100,25 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
         tile_coords(tile, g.tiles_m, g.tiles_n, G2_GROUP_M, tm, tn);
         const int m0 = tm * 2 * BM + (int)rank * BM;
         const int n0 = tn * G2_BN + (int)rank * G2_HALF_N;
-        for (int kb = 0; kb < g.kblocks; ++kb) {
+        for (int kb = 0; kb < g.kblocks; kb += KSUB) {
           if (!mbar_wait(&bars->empty[stage], phase ^ 1u, wc, EMK_DEV_TIMEOUT_PRODUCER)) {
             ok = false;
             break;
           }
           const uint32_t full_leader = mapa_u32(smem_u32(&bars->full[stage]), 0);
           if (leader) mbar_arrive_expect_tx(&bars->full[stage], G2_STAGE_TX);
-          tma_load_2d_pair(sA + stage * A_STAGE_BYTES, &tma_a, full_leader, kb * BK, m0);
-          if (WL == 0) {
-            tma_load_2d_pair(sB + stage * G2_B_STAGE_BYTES, &tma_b, full_leader, kb * BK, n0);
-          } else {
 #pragma unroll
-            for (int c = 0; c < G2_HALF_N / 64; ++c)
-              tma_load_2d_pair(sB + stage * G2_B_STAGE_BYTES + c * (BK * 128), &tma_b, full_leader, n0 + c * 64,
-                               kb * BK);
+          for (int u = 0; u < KSUB; ++u) {  // slices past K are zero-filled by TMA and add nothing
+            const int k0 = (kb + u) * BK;
+            tma_load_2d_pair(sA + stage * G2_A_STAGE + u * A_STAGE_BYTES, &tma_a, full_leader, k0, m0);
+            uint8_t* bdst = sB + stage * G2_B_STAGE_BYTES + u * G2_B_SUB_BYTES;
+            if (WL == 0) {
+              tma_load_2d_pair(bdst, &tma_b, full_leader, k0, n0);
+            } else {
+#pragma unroll
+              for (int c = 0; c < G2_HALF_N / 64; ++c)
+                tma_load_2d_pair(bdst + c * (BK * 128), &tma_b, full_leader, n0 + c * 64, k0);
+            }
           }
           if (++stage == G2_STAGES) {
             stage = 0;
@@ -130,20 +140,23 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
         if (!mbar_wait(&bars->tmem_empty[acc], acc_phase ^ 1u, wc, EMK_DEV_TIMEOUT_MMA)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * G2_BN);
-        for (int kb = 0; kb < g.kblocks; ++kb) {
+        for (int kb = 0; kb < g.kblocks; kb += KSUB) {
           if (!mbar_wait(&bars->full[stage], phase, wc, EMK_DEV_TIMEOUT_MMA)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(sA + stage * A_STAGE_BYTES);
-          const uint32_t b_addr = smem_u32(sB + stage * G2_B_STAGE_BYTES);
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k) {
-            const uint64_t adesc = make_smem_desc(a_addr + k * 32, 0, 1024);
-            const uint64_t bdesc = (WL == 0) ? make_smem_desc(b_addr + k * 32, 0, 1024)
-                                             : make_smem_desc(b_addr + k * 16 * 128, BK * 128, 1024);
-            umma_ss_pair(d_tmem, adesc, bdesc, IDESC, (uint32_t)((kb | k) != 0));
+          for (int u = 0; u < KSUB; ++u) {
+            const uint32_t a_addr = smem_u32(sA + stage * G2_A_STAGE + u * A_STAGE_BYTES);
+            const uint32_t b_addr = smem_u32(sB + stage * G2_B_STAGE_BYTES + u * G2_B_SUB_BYTES);
+#pragma unroll
+            for (int k = 0; k < BK / 16; ++k) {
+              const uint64_t adesc = make_smem_desc(a_addr + k * 32, 0, 1024);
+              const uint64_t bdesc = (WL == 0) ? make_smem_desc(b_addr + k * 32, 0, 1024)
+                                               : make_smem_desc(b_addr + k * 16 * 128, BK * 128, 1024);
+              umma_ss_pair(d_tmem, adesc, bdesc, IDESC, (uint32_t)((kb | u | k) != 0));
+            }
           }
           const uint32_t e_local = smem_u32(&bars->empty[stage]);
           tc_commit_pair(e_local);
@@ -188,12 +201,12 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
   if (warp == 0) tmem_dealloc_pair(tmem_base, G2_TMEM_COLS);
 }
 
-template <int G2_BN, int G2_STAGES, int WL>
+template <int G2_BN, int G2_STAGES, int WL, int KSUB>
 int launch_gemm2(emk_handle_t h, const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, cudaStream_t s) {
-  constexpr int G2_SMEM = G2_STAGES * (A_STAGE_BYTES + (G2_BN / 2) * BK * 2) + 1024 + (int)sizeof(G2Barriers);
+  constexpr int G2_SMEM = G2_STAGES * KSUB * (A_STAGE_BYTES + (G2_BN / 2) * BK * 2) + 1024 + (int)sizeof(G2Barriers);
   static bool configured[64] = {false};
   static int max_pairs[64] = {0};
-  auto kern = gemm2_bf16_kernel<G2_BN, G2_STAGES, WL>;
+  auto kern = gemm2_bf16_kernel<G2_BN, G2_STAGES, WL, KSUB>;
   const int d = h->device < 64 ? h->device : 0;
   if (!configured[d]) {
     EMK_CUDA_TRY(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM));
@@ -224,32 +237,13 @@ int launch_gemm2(emk_handle_t h, const CUtensorMap& ta, const CUtensorMap& tb, c
   return EMK_OK;
 }
 
-// Tile width by wave count: with P CTA pairs resident, a width BN costs ceil(tiles / P) waves of BN columns each.
-int pick_tile_width(emk_handle_t h, int M, int N, bool allow_192) {
-  const int pairs = h->sm_count / 2;
-  const int tiles_m = (M + 2 * BM - 1) / (2 * BM);
-  int best = 256;
-  long best_cost = -1;
-  const int cands[3] = {256, 192, 128};
-  for (int i = 0; i < 3; ++i) {
-    const int bn = cands[i];
-    if (bn == 192 && !allow_192) continue;
-    const long tiles = (long)tiles_m * ((N + bn - 1) / bn);
-    const long waves = (tiles + pairs - 1) / pairs;
-    const long cost = waves * (bn + 16);  // + fixed per-tile overhead
-    if (best_cost < 0 || cost < best_cost) {
-      best_cost = cost;
-      best = bn;
-    }
-  }
-  return best;
-}
-
 }  // namespace
 
 // Called by the dispatcher in emk_gemm_sm100.cu. `g` arrives with tiles_m / tiles_n unset for this tiling.
 int emk_gemm2_launch(emk_handle_t h, const void* x, const void* w, emk::GemmArgs g, int wlayout, cudaStream_t s) {
-  const int bn = pick_tile_width(h, g.M, g.N, wlayout == EMK_W_NK);
+  // 256-column tiles whenever the output is wider than 128 columns: narrower tiles cost almost the same time per
+  // K step (measured), so they only pay off when they avoid computing padding.
+  const int bn = g.N > 128 ? 256 : 128;
   g.tiles_m = (g.M + 2 * BM - 1) / (2 * BM);
   g.tiles_n = (g.N + bn - 1) / bn;
   CUtensorMap ta, tb;
@@ -260,13 +254,13 @@ int emk_gemm2_launch(emk_handle_t h, const void* x, const void* w, emk::GemmArgs
     rc = emk_make_tmap_2d(h, &tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w, (uint64_t)g.K, (uint64_t)g.N,
                           (uint64_t)g.K * 2, BK, (uint32_t)(bn / 2), CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != EMK_OK) return rc;
-    if (bn == 256) return launch_gemm2<256, 6, 0>(h, ta, tb, g, s);
-    if (bn == 192) return launch_gemm2<192, 7, 0>(h, ta, tb, g, s);
-    return launch_gemm2<128, 8, 0>(h, ta, tb, g, s);
+    // two 64-wide K slices per ring stage: the per-stage barrier/commit work of the MMA thread is paid half as often
+    if (bn == 256) return launch_gemm2<256, 3, 0, 2>(h, ta, tb, g, s);
+    return launch_gemm2<128, 4, 0, 2>(h, ta, tb, g, s);
   }
   rc = emk_make_tmap_2d(h, &tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.N * 2,
                         64, BK, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != EMK_OK) return rc;
-  if (bn == 256) return launch_gemm2<256, 6, 1>(h, ta, tb, g, s);
-  return launch_gemm2<128, 8, 1>(h, ta, tb, g, s);
+  if (bn == 256) return launch_gemm2<256, 3, 1, 2>(h, ta, tb, g, s);
+  return launch_gemm2<128, 4, 1, 2>(h, ta, tb, g, s);
 }
