@@ -268,8 +268,11 @@ def gemm_event_pass(model) -> dict:
         s.record()
         r = orig(x, w, **kw)
         e.record()
-        events.append((s, e))
-        flops += 2 * (x.numel() // x.shape[-1]) * x.shape[-1] * w.shape[0]
+        M = x.numel() // x.shape[-1]
+        fl = 2 * M * x.shape[-1] * w.shape[0]
+        epi = "residual" if kw.get("residual") is not None else ("swiglu" if kw.get("swiglu") else "none")
+        events.append((s, e, f"{M}x{w.shape[0]}x{x.shape[-1]}+{epi}", fl))
+        flops += fl
         return r
 
     ops.linear = timed_linear
@@ -282,8 +285,16 @@ def gemm_event_pass(model) -> dict:
         torch.cuda.synchronize()
     finally:
         ops.linear = orig
-    total_ms = sum(s.elapsed_time(e) for s, e in events)
-    return {"launches": len(events), "ms": total_ms, "flops": flops}
+    total_ms = sum(s.elapsed_time(e) for s, e, _, _ in events)
+    by_shape: dict[str, list] = {}
+    for s, e, key, fl in events:
+        acc = by_shape.setdefault(key, [0, 0.0, 0])
+        acc[0] += 1
+        acc[1] += s.elapsed_time(e)
+        acc[2] += fl
+    shapes = {k: {"launches": n, "avg_us": round(ms * 1e3 / n, 1), "tflops": round(fl / (ms * 1e-3) / 1e12, 1)}
+              for k, (n, ms, fl) in by_shape.items()}
+    return {"launches": len(events), "ms": total_ms, "flops": flops, "by_shape": shapes}
 
 
 def main() -> None:
@@ -407,7 +418,7 @@ def main() -> None:
             "achieved": round(gemm_tflops, 1), "peak": peak, "peak_source": f"{peak_src} (sustained cuBLAS bf16)",
             "unit": "TFLOP/s", "frac": round(gemm_tflops / peak, 4),
             "launches_per_step": gp["launches"], "avg_launch_us": round(gp["ms"] * 1e3 / gp["launches"], 2),
-            "gemm_share_of_step": round(gp["ms"] / ms_per_step, 4),
+            "gemm_share_of_step": round(gp["ms"] / ms_per_step, 4), "by_shape": gp["by_shape"],
             "traffic": None,
         }
         step_flops = cfg.linear_flops_per_token() * BATCH * SEQ + cfg.attention_flops(BATCH, SEQ)

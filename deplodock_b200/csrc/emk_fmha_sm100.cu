@@ -20,7 +20,6 @@
 #include "emk_common.cuh"
 
 #include <math_constants.h>
-#include <stdlib.h>
 
 namespace {
 
@@ -47,15 +46,14 @@ struct FmhaArgs {
   int o_cs, o_rb, o_rh;
   int64_t ld_o;
   float scale_log2;
-  int dbg;
   int* status;
   unsigned long long limit_ns;
 };
 
 struct __align__(8) FmhaBarriers {
   uint64_t q_full;
-  uint64_t k_full[KV_STAGES], k_empty[KV_STAGES];
-  uint64_t v_full[KV_STAGES], v_empty[KV_STAGES];
+  uint64_t k_full[KV_STAGES], v_full[KV_STAGES];
+  uint64_t kv_empty[KV_STAGES];  // one K tile and one V tile per stage, released together
   uint64_t s_full[2], p_full[2], o_done[2];
   uint32_t tmem_base;
   int abort_flag;
@@ -122,9 +120,8 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     mbar_init(&bars->q_full, 1);
     for (int i = 0; i < KV_STAGES; ++i) {
       mbar_init(&bars->k_full[i], 1);
-      mbar_init(&bars->k_empty[i], 1);
       mbar_init(&bars->v_full[i], 1);
-      mbar_init(&bars->v_empty[i], 1);
+      mbar_init(&bars->kv_empty[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars->s_full[i], 1);
@@ -165,11 +162,10 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
       for (int j = 0; j < nblk; ++j) {
         const int st = j % KV_STAGES;
         const uint32_t ph = (uint32_t)(j / KV_STAGES) & 1u;
-        if (!mbar_wait(&bars->k_empty[st], ph ^ 1u, wc, EMK_DEV_TIMEOUT_PRODUCER)) break;
+        if (!mbar_wait(&bars->kv_empty[st], ph ^ 1u, wc, EMK_DEV_TIMEOUT_PRODUCER)) break;
         mbar_arrive_expect_tx(&bars->k_full[st], TILE_BYTES);
         tma_load_2d(sK + st * TILE_BYTES, &tma_k, &bars->k_full[st], xkv, ykv + j * FN);
         tma_load_2d(sK + st * TILE_BYTES + HALF_BYTES, &tma_k, &bars->k_full[st], xkv + 64, ykv + j * FN);
-        if (!mbar_wait(&bars->v_empty[st], ph ^ 1u, wc, EMK_DEV_TIMEOUT_PRODUCER)) break;
         mbar_arrive_expect_tx(&bars->v_full[st], TILE_BYTES);
         tma_load_2d(sV + st * TILE_BYTES, &tma_v, &bars->v_full[st], xkv, ykv + j * FN);
         tma_load_2d(sV + st * TILE_BYTES + HALF_BYTES, &tma_v, &bars->v_full[st], xkv + 64, ykv + j * FN);
@@ -201,6 +197,10 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
                   (uint32_t)(accumulate || ks != 0));
         }
       };
+      // A tcgen05.commit stalls this thread for a few hundred cycles (it drains behind the MMAs issued so far), so
+      // only the commits the softmax warps cannot do without are issued: one per S tile, and one after the last PV.
+      // "PV of block j-1 is done" is implied by the S commit of block j (a commit covers every earlier MMA of this
+      // thread), and the K/V stage is released by a softmax thread that has seen that commit.
       bool ok = mbar_wait(&bars->q_full, 0, wc, EMK_DEV_TIMEOUT_MMA);
       if (ok) ok = mbar_wait(&bars->k_full[0], 0, wc, EMK_DEV_TIMEOUT_MMA);
       if (ok) {
@@ -209,7 +209,6 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
           issue_s(t, 0);
           tc_commit(&bars->s_full[t]);
         }
-        tc_commit(&bars->k_empty[0]);
       }
       for (int j = 0; j < nblk && ok; ++j) {
         const int st = j % KV_STAGES;
@@ -223,17 +222,15 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
           if (!ok) break;
           tc_fence_after();
           issue_pv(t, st, j > 0);
-          tc_commit(&bars->o_done[t]);
-          if (t == ntile - 1) tc_commit(&bars->v_empty[st]);
           if (has_next) {
             if (t == 0) {
               ok = mbar_wait(&bars->k_full[stn], phn, wc, EMK_DEV_TIMEOUT_MMA);
               if (!ok) break;
-              tc_fence_after();
             }
             issue_s(t, stn);
             tc_commit(&bars->s_full[t]);
-            if (t == ntile - 1) tc_commit(&bars->k_empty[stn]);
+          } else {
+            tc_commit(&bars->o_done[t]);
           }
         }
       }
@@ -257,6 +254,9 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
           break;
         }
         tc_fence_after();
+        // The S commit of block j covers the PV of block j-1 of both tiles (tile 0's MMAs precede tile 1's in the
+        // issuing thread), so the last tile's first softmax thread hands the K/V stage of block j-1 back here.
+        if (j > 0 && t == (two ? 1 : 0) && quarter == 0 && lane == 0) mbar_arrive(&bars->kv_empty[(j - 1) % KV_STAGES]);
         uint32_t s[FN];
 #pragma unroll
         for (int c = 0; c < FN / 32; ++c) tmem_ld_x32(tS + (uint32_t)(c * 32), s + c * 32);
@@ -276,17 +276,11 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
           mx2 = max3(mx2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
           mx3 = max3(mx3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
         }
-        float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-        if (a.dbg & 4) mx = 0.f;
+        const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
         const float m_new = fmaxf(m_used, mx * a.scale_log2);
         const bool need = (m_new - m_used) > RESCALE_THRESHOLD;  // true on the first block (m_used = -inf)
         if (__any_sync(0xffffffffu, need)) {
-          if (j > 0) {
-            if (!mbar_wait_warp(&bars->o_done[t], (uint32_t)(j - 1) & 1u, wc, EMK_DEV_TIMEOUT_SOFTMAX)) {
-              ok = false;
-              break;
-            }
-            tc_fence_after();
+          if (j > 0) {  // PV of block j-1 has completed: implied by the S commit waited on above
             const float alpha = ex2_approx(m_used - m_new);
             l *= alpha;
 #pragma unroll 1
@@ -314,8 +308,7 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
           unpack_f32x2(
               fma_f32x2(pack_f32x2(__uint_as_float(s[2 * i + 2]), __uint_as_float(s[2 * i + 3])), scale2, neg_m2), t2,
               t3);
-          float p0, p1, p2, p3;
-          if (a.dbg & 1) { p0 = t0; p1 = t1; p2 = t2; p3 = t3; } else { p0 = ex2_approx(t0); p1 = ex2_approx(t1); p2 = ex2_approx(t2); p3 = ex2_approx(t3); }
+          const float p0 = ex2_approx(t0), p1 = ex2_approx(t1), p2 = ex2_approx(t2), p3 = ex2_approx(t3);
           sum_a = add_f32x2(sum_a, pack_f32x2(p0, p1));
           sum_b = add_f32x2(sum_b, pack_f32x2(p2, p3));
           p[i] = pack_bf16x2(p0, p1);
@@ -334,7 +327,7 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->p_full[t]);
       }
-      if (ok && mbar_wait_warp(&bars->o_done[t], (uint32_t)(nblk - 1) & 1u, wc, EMK_DEV_TIMEOUT_SOFTMAX)) {
+      if (ok && mbar_wait_warp(&bars->o_done[t], 0u, wc, EMK_DEV_TIMEOUT_SOFTMAX)) {
         tc_fence_after();
         const float inv = 1.0f / l;
         const int hq = hq0 + t;
@@ -400,7 +393,6 @@ int fmha_launch(emk_handle_t h, const void* q, const void* k, const void* v, voi
   a.scale_log2 = scale * 1.4426950408889634f;
   a.status = h->status_dev;
   a.limit_ns = h->wait_limit_ns;
-  { const char* d = getenv("EMK_FMHA_DBG"); a.dbg = d ? atoi(d) : 0; }
 
   CUtensorMap tq, tk, tv;
   int rc;

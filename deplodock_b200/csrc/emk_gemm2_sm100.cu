@@ -134,6 +134,10 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       uint32_t phase = 0;
       int local = 0;
       bool ok = true;
+      // descriptor halves (see smem_desc_lo / smem_desc_hi): the low half advances by constants per K slice
+      const uint32_t desc_hi = smem_desc_hi(1024);
+      const uint32_t a_lo0 = smem_desc_lo(smem_u32(sA), 0);
+      const uint32_t b_lo0 = smem_desc_lo(smem_u32(sB), WL == 0 ? 0 : BK * 128);
       for (int tile = pair; tile < ntiles && ok; tile += npairs, ++local) {
         const int acc = local & 1;
         const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
@@ -145,19 +149,20 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
             ok = false;
             break;
           }
-          tc_fence_after();
+          // no tcgen05 fence here: the stage was written by TMA (async proxy) and the mbarrier wait orders it
+          const uint32_t a_st = a_lo0 + (uint32_t)(stage * (G2_A_STAGE >> 4));
+          const uint32_t b_st = b_lo0 + (uint32_t)(stage * (G2_B_STAGE_BYTES >> 4));
 #pragma unroll
           for (int u = 0; u < KSUB; ++u) {
-            const uint32_t a_addr = smem_u32(sA + stage * G2_A_STAGE + u * A_STAGE_BYTES);
-            const uint32_t b_addr = smem_u32(sB + stage * G2_B_STAGE_BYTES + u * G2_B_SUB_BYTES);
 #pragma unroll
             for (int k = 0; k < BK / 16; ++k) {
-              const uint64_t adesc = make_smem_desc(a_addr + k * 32, 0, 1024);
-              const uint64_t bdesc = (WL == 0) ? make_smem_desc(b_addr + k * 32, 0, 1024)
-                                               : make_smem_desc(b_addr + k * 16 * 128, BK * 128, 1024);
-              umma_ss_pair(d_tmem, adesc, bdesc, IDESC, (uint32_t)((kb | u | k) != 0));
+              const uint32_t a_lo = a_st + (uint32_t)((u * A_STAGE_BYTES + k * 32) >> 4);
+              const uint32_t b_lo = b_st + (uint32_t)((u * G2_B_SUB_BYTES + (WL == 0 ? k * 32 : k * 16 * 128)) >> 4);
+              umma_ss_pair_lohi(d_tmem, a_lo, b_lo, desc_hi, IDESC, (u | k) != 0 ? 1u : (uint32_t)(kb != 0));
             }
           }
+          // release the stage in both CTAs (relaying the peer's release through the leader's producer thread was
+          // measured 25 % slower: the peer's refills start late)
           const uint32_t e_local = smem_u32(&bars->empty[stage]);
           tc_commit_pair(e_local);
           tc_commit_pair(mapa_u32(e_local, 1));
