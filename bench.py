@@ -252,49 +252,63 @@ def kernel_table(peaks: dict) -> list[dict]:
 # Main arm
 # ------------------------------------------------------------------------------------------------------------
 def gemm_event_pass(model) -> dict:
-    """One eager pass of the plan with CUDA events around every tcgen05 GEMM launch (on the launching stream):
-    total GEMM time and flops per forward of this rank's shard."""
+    """One eager pass of the plan with CUDA events around every kernel launch (on the launching stream): time per
+    kernel family, and for the tcgen05 GEMM the flops and time per operand shape. Returns the GEMM totals of one
+    forward of this rank's shard plus the per-family breakdown."""
     import torch
 
     from deplodock_b200 import ops
 
+    names = ["embed_gather", "rmsnorm", "linear", "qknorm_rope_", "sdpa_causal_gqa_tok", "pool_norm_l2"]
+    originals = {n: getattr(ops, n) for n in names}
     events = []
-    flops = 0
-    orig = ops.linear
 
-    def timed_linear(x, w, **kw):
-        nonlocal flops
-        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s.record()
-        r = orig(x, w, **kw)
-        e.record()
-        M = x.numel() // x.shape[-1]
-        fl = 2 * M * x.shape[-1] * w.shape[0]
-        epi = "residual" if kw.get("residual") is not None else ("swiglu" if kw.get("swiglu") else "none")
-        events.append((s, e, f"{M}x{w.shape[0]}x{x.shape[-1]}+{epi}", fl))
-        flops += fl
-        return r
+    def wrap(name, fn):
+        def timed(*args, **kw):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            r = fn(*args, **kw)
+            e.record()
+            key, fl = name, 0
+            if name == "linear":
+                x, w = args[0], args[1]
+                M = x.numel() // x.shape[-1]
+                fl = 2 * M * x.shape[-1] * w.shape[0]
+                epi = "residual" if kw.get("residual") is not None else ("swiglu" if kw.get("swiglu") else "none")
+                key = f"{M}x{w.shape[0]}x{x.shape[-1]}+{epi}"
+            events.append((s, e, name, key, fl))
+            return r
+        return timed
 
-    ops.linear = timed_linear
+    for n in names:
+        setattr(ops, n, wrap(n, originals[n]))
     try:
         model.forward_eager()
         torch.cuda.synchronize()
         events.clear()
-        flops = 0
         model.forward_eager()
         torch.cuda.synchronize()
     finally:
-        ops.linear = orig
-    total_ms = sum(s.elapsed_time(e) for s, e, _, _ in events)
+        for n in names:
+            setattr(ops, n, originals[n])
+    families: dict[str, list] = {}
     by_shape: dict[str, list] = {}
-    for s, e, key, fl in events:
-        acc = by_shape.setdefault(key, [0, 0.0, 0])
-        acc[0] += 1
-        acc[1] += s.elapsed_time(e)
-        acc[2] += fl
+    for s, e, name, key, fl in events:
+        ms = s.elapsed_time(e)
+        f = families.setdefault(name, [0, 0.0])
+        f[0] += 1
+        f[1] += ms
+        if name == "linear":
+            acc = by_shape.setdefault(key, [0, 0.0, 0])
+            acc[0] += 1
+            acc[1] += ms
+            acc[2] += fl
     shapes = {k: {"launches": n, "avg_us": round(ms * 1e3 / n, 1), "tflops": round(fl / (ms * 1e-3) / 1e12, 1)}
               for k, (n, ms, fl) in by_shape.items()}
-    return {"launches": len(events), "ms": total_ms, "flops": flops, "by_shape": shapes}
+    fam = {k: {"launches": n, "ms": round(ms, 3)} for k, (n, ms) in families.items()}
+    lin = families.get("linear", [0, 0.0])
+    return {"launches": lin[0], "ms": lin[1], "flops": sum(v[2] for v in by_shape.values()), "by_shape": shapes,
+            "families": fam}
 
 
 def main() -> None:
@@ -437,6 +451,7 @@ def main() -> None:
                     "d2h_bytes_per_step": BATCH * H * 4, "ms_per_step": round(e2e_ms / args.steps, 4)},
             "gpu_launches": model.num_launches * args.steps,
             "clocks": clocks, "roofline": roofline, "outputs_finite": finite,
+            "step_breakdown_ms": gp["families"],
         }
         if world == 1 and not args.no_kernels:
             del model

@@ -37,7 +37,9 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   tn = in_group / gsize;
 }
 
-__device__ __forceinline__ float silu_f(float g) { return g / (1.0f + __expf(-g)); }
+// silu(g) = g / (1 + exp(-g)) with the approximate reciprocal (2 ulp): the result is rounded to bf16 right after, and
+// the IEEE division's slow path made the SwiGLU epilogue longer than the main loop of a K = 1024 tile.
+__device__ __forceinline__ float silu_f(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
 
 // Epilogue for 32 accumulator columns [col0, col0+32) of one output row held by this thread. `g.wide` says rows of
 // y (and of the residual) are 32-byte aligned, so full 32-column groups move as 256-bit accesses.

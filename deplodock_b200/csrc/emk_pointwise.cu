@@ -37,67 +37,65 @@ __device__ __forceinline__ void unpack8(const uint4& v, float* f) {
   f[4] = bf16_lo(v.z); f[5] = bf16_hi(v.z); f[6] = bf16_lo(v.w); f[7] = bf16_hi(v.w);
 }
 
-__global__ void __launch_bounds__(256) qknorm_rope_kernel(__nv_bfloat16* __restrict__ qkv,
-                                                          const __nv_bfloat16* __restrict__ qw,
-                                                          const __nv_bfloat16* __restrict__ kw,
-                                                          const __nv_bfloat16* __restrict__ cosb,
-                                                          const __nv_bfloat16* __restrict__ sinb, int64_t tokens, int S,
-                                                          int Hq, int Hkv, float eps) {
+// A CTA has 16 lanes per q/k head of a token (blockDim = 16 * (Hq + Hkv) rounded up to a warp, at most 512) and
+// handles QKR_TOKENS_PER_CTA tokens: all their 16-byte loads are issued first (HBM latency is paid once, with enough
+// bytes in flight per SM), the cos/sin rows come from L1/L2 when each token is processed. No division per element:
+// the head comes from the thread index, the position from one 32-bit remainder per token.
+constexpr int QKR_TOKENS_PER_CTA = 4;
+
+__global__ void __launch_bounds__(512, 2) qknorm_rope_kernel(__nv_bfloat16* __restrict__ qkv,
+                                                             const __nv_bfloat16* __restrict__ qw,
+                                                             const __nv_bfloat16* __restrict__ kw,
+                                                             const __nv_bfloat16* __restrict__ cosb,
+                                                             const __nv_bfloat16* __restrict__ sinb, int tokens, int S,
+                                                             int Hq, int Hkv, float eps) {
   const int sub = threadIdx.x & 15;
   const int nh = Hq + Hkv;
+  const int head_raw = threadIdx.x >> 4;
+  const bool live = head_raw < nh;          // padding groups of the last warp compute on head nh-1 and store nothing
+  const int head = live ? head_raw : nh - 1;
   const int ld = (Hq + 2 * Hkv) * 128;
-  const int64_t items = tokens * nh;
-  const int64_t groups = (int64_t)gridDim.x * (blockDim.x >> 4);
-  const int64_t gid = (int64_t)blockIdx.x * (blockDim.x >> 4) + (threadIdx.x >> 4);
-  float qwf[8], kwf[8];
-  unpack8(*reinterpret_cast<const uint4*>(qw + sub * 8), qwf);
-  unpack8(*reinterpret_cast<const uint4*>(kw + sub * 8), kwf);
-  // Items are walked in pairs (it, it + groups) so both loads are issued before either is used. The loop bound is
-  // taken from the first group of the warp so both 16-lane groups make the same number of trips (the shuffles below
-  // name the whole warp); a group without an item recomputes the last item and skips the store.
-  for (int64_t itb = gid & ~(int64_t)1; itb < items; itb += 2 * groups) {
-    const int64_t it_raw = itb + (gid & 1);
-    const bool has1 = it_raw < items;
-    const int64_t it = has1 ? it_raw : items - 1;
-    const int64_t it2 = it_raw + groups;
-    const bool has2 = it2 < items;
-    const int64_t t0 = it / nh, t1 = has2 ? it2 / nh : t0;
-    const int h0 = (int)(it % nh), h1 = has2 ? (int)(it2 % nh) : h0;
-    __nv_bfloat16* p0 = qkv + t0 * ld + h0 * 128 + sub * 8;
-    __nv_bfloat16* p1 = qkv + t1 * ld + h1 * 128 + sub * 8;
-    const uint4 x0 = *reinterpret_cast<const uint4*>(p0);
-    const uint4 x1 = *reinterpret_cast<const uint4*>(p1);
-    const int s0 = (int)(t0 % S), s1 = (int)(t1 % S);
-    const uint4 c0 = __ldg(reinterpret_cast<const uint4*>(cosb + (int64_t)s0 * 128 + sub * 8));
-    const uint4 n0 = __ldg(reinterpret_cast<const uint4*>(sinb + (int64_t)s0 * 128 + sub * 8));
-    const uint4 c1 = __ldg(reinterpret_cast<const uint4*>(cosb + (int64_t)s1 * 128 + sub * 8));
-    const uint4 n1 = __ldg(reinterpret_cast<const uint4*>(sinb + (int64_t)s1 * 128 + sub * 8));
+  const int t_base = blockIdx.x * QKR_TOKENS_PER_CTA;
+  uint4 x[QKR_TOKENS_PER_CTA];
 #pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      float xf[8], cs[8], sn[8];
-      unpack8(u ? x1 : x0, xf);
-      unpack8(u ? c1 : c0, cs);
-      unpack8(u ? n1 : n0, sn);
-      const float* wf = ((u ? h1 : h0) < Hq) ? qwf : kwf;
-      float ss = 0.f;
+  for (int i = 0; i < QKR_TOKENS_PER_CTA; ++i) {
+    const int t = min(t_base + i, tokens - 1);
+    x[i] = *reinterpret_cast<const uint4*>(qkv + (int64_t)t * ld + head * 128 + sub * 8);
+  }
+  // Everything after the fp32 statistic runs on packed bf16 pairs: a bf16x2 multiply/add rounds once to bf16, which
+  // is exactly what the eager bf16 module does at every step, at a quarter of the instructions of unpack-to-fp32.
+  const uint4 wv = __ldg(reinterpret_cast<const uint4*>((head < Hq ? qw : kw) + sub * 8));
+  const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wv);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) ss = fmaf(xf[e], xf[e], ss);
+  for (int i = 0; i < QKR_TOKENS_PER_CTA; ++i) {
+    const int t = min(t_base + i, tokens - 1);
+    const int s = t % S;
+    const uint4 cv = __ldg(reinterpret_cast<const uint4*>(cosb + s * 128 + sub * 8));
+    const uint4 sv = __ldg(reinterpret_cast<const uint4*>(sinb + s * 128 + sub * 8));
+    const __nv_bfloat162* c2 = reinterpret_cast<const __nv_bfloat162*>(&cv);
+    const __nv_bfloat162* s2 = reinterpret_cast<const __nv_bfloat162*>(&sv);
+    float xf[8];
+    unpack8(x[i], xf);
+    float ss = 0.f;
 #pragma unroll
-      for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      const float r = 1.0f / sqrtf(ss * (1.0f / 128.0f) + eps);
-      float out[8];
+    for (int e = 0; e < 8; ++e) ss = fmaf(xf[e], xf[e], ss);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const float nrm = bf16_round(wf[e] * bf16_round(xf[e] * r));
-        const float partner = __shfl_xor_sync(0xffffffffu, nrm, 8);
-        const float rot = sub < 8 ? -partner : partner;  // rotate_half: first half takes -x[i+64], second x[i-64]
-        out[e] = bf16_round(nrm * cs[e]) + bf16_round(rot * sn[e]);
-      }
-      uint4 o;
-      o.x = pack_bf16x2(out[0], out[1]); o.y = pack_bf16x2(out[2], out[3]);
-      o.z = pack_bf16x2(out[4], out[5]); o.w = pack_bf16x2(out[6], out[7]);
-      if (u == 0 ? has1 : has2) *reinterpret_cast<uint4*>(u ? p1 : p0) = o;
+    for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float r = 1.0f / sqrtf(ss * (1.0f / 128.0f) + eps);
+    uint4 ov;
+    uint32_t* o32 = reinterpret_cast<uint32_t*>(&ov);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const __nv_bfloat162 n = __hmul2_rn(w2[e], __floats2bfloat162_rn(xf[2 * e] * r, xf[2 * e + 1] * r));
+      uint32_t nb = *reinterpret_cast<const uint32_t*>(&n);
+      uint32_t pb = __shfl_xor_sync(0xffffffffu, nb, 8);
+      if (sub < 8) pb ^= 0x80008000u;  // rotate_half: first half takes -x[i+64], second half x[i-64]
+      const __nv_bfloat162 rot = *reinterpret_cast<const __nv_bfloat162*>(&pb);
+      const __nv_bfloat162 out = __hadd2_rn(__hmul2_rn(n, c2[e]), __hmul2_rn(rot, s2[e]));
+      o32[e] = *reinterpret_cast<const uint32_t*>(&out);
     }
+    if (live && t_base + i < tokens)
+      *reinterpret_cast<uint4*>(qkv + (int64_t)t * ld + head * 128 + sub * 8) = ov;
   }
 }
 
@@ -161,12 +159,12 @@ extern "C" int emk_qknorm_rope(emk_handle_t h, void* qkv, const void* qw, const 
   if (!h || !qkv || !qw || !kw || !cosb || !sinb) return EMK_ERR_ARG;
   if (tokens <= 0 || S <= 0 || Hq <= 0 || Hkv <= 0) return EMK_ERR_SHAPE;
   if ((((uintptr_t)qkv | (uintptr_t)qw | (uintptr_t)kw | (uintptr_t)cosb | (uintptr_t)sinb) & 15u)) return EMK_ERR_ALIGN;
-  const int64_t items = tokens * (Hq + Hkv);
-  int64_t grid = (items + 31) / 32;  // 16 groups per CTA, two items per group and pass
-  if (grid > (int64_t)h->sm_count * 64) grid = (int64_t)h->sm_count * 64;
-  qknorm_rope_kernel<<<(unsigned)grid, 256, 0, (cudaStream_t)stream>>>(
+  if (tokens > 0x7fffffffLL / 2 || (Hq + Hkv) > 32) return EMK_ERR_SHAPE;
+  const int threads = (int)(((Hq + Hkv) * 16 + 31) / 32 * 32);
+  const int64_t grid = (tokens + QKR_TOKENS_PER_CTA - 1) / QKR_TOKENS_PER_CTA;
+  qknorm_rope_kernel<<<(unsigned)grid, threads, 0, (cudaStream_t)stream>>>(
       (__nv_bfloat16*)qkv, (const __nv_bfloat16*)qw, (const __nv_bfloat16*)kw, (const __nv_bfloat16*)cosb,
-      (const __nv_bfloat16*)sinb, tokens, (int)S, (int)Hq, (int)Hkv, eps);
+      (const __nv_bfloat16*)sinb, (int)tokens, (int)S, (int)Hq, (int)Hkv, eps);
   EMK_LAUNCH_CHECK(h);
   return EMK_OK;
 }
