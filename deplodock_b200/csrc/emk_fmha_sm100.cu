@@ -40,6 +40,7 @@ struct FmhaArgs {
   __nv_bfloat16* o;
   int B, Hq, Hkv, S, group, pairs;
   int nqblk;
+  int n_items, n_rounds;
   // coordinates: x = h * cs + 64 * half, y = b * rb + h * rh + s  (q side indexed by query head, kv side by KV head)
   int q_cs, q_rb, q_rh;
   int kv_cs, kv_rb, kv_rh;
@@ -51,10 +52,10 @@ struct FmhaArgs {
 };
 
 struct __align__(8) FmhaBarriers {
-  uint64_t q_full;
+  uint64_t q_full, q_empty;
   uint64_t k_full[KV_STAGES], v_full[KV_STAGES];
   uint64_t kv_empty[KV_STAGES];  // one K tile and one V tile per stage, released together
-  uint64_t s_full[2], p_full[2], o_done[2];
+  uint64_t s_full[2], p_full[2], o_done[2], o_empty[2];
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -90,6 +91,34 @@ __device__ __forceinline__ unsigned long long add_f32x2(unsigned long long a, un
   return d;
 }
 
+// One unit of work: 128 query rows of the (up to) two query heads `hq0`, `hq0 + 1` that share KV head `hkv`.
+struct WorkItem {
+  int b, hkv, hq0, q0, nblk;
+  bool two;
+};
+
+// Items are numbered heaviest query block first and dealt to the CTAs in boustrophedon order (round r left to right,
+// round r+1 right to left), which evens out the causal triangle: every CTA gets about the same number of KV blocks.
+__device__ __forceinline__ int item_of_round(int round, int cta, int grid) {
+  return round * grid + ((round & 1) ? (grid - 1 - cta) : cta);
+}
+
+__device__ __forceinline__ WorkItem decode_item(const FmhaArgs& a, int w) {
+  WorkItem it;
+  const int per_qblk = a.B * a.Hkv * a.pairs;
+  const int qblk = a.nqblk - 1 - w / per_qblk;
+  int rem = w % per_qblk;
+  const int pair = rem % a.pairs;
+  rem /= a.pairs;
+  it.hkv = rem % a.Hkv;
+  it.b = rem / a.Hkv;
+  it.hq0 = it.hkv * a.group + 2 * pair;
+  it.two = (2 * pair + 1) < a.group;
+  it.q0 = qblk * FM;
+  it.nblk = qblk + 1;  // KV blocks 0..qblk (FM == FN)
+  return it;
+}
+
 __global__ void __launch_bounds__(FMHA_THREADS, 1)
 fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
                    const __grid_constant__ CUtensorMap tma_v, const FmhaArgs a) {
@@ -103,21 +132,9 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  // Work decode: heaviest query blocks first.
-  const int per_qblk = a.B * a.Hkv * a.pairs;
-  const int qblk = a.nqblk - 1 - (int)(blockIdx.x / per_qblk);
-  int rem = (int)(blockIdx.x % per_qblk);
-  const int pair = rem % a.pairs;
-  rem /= a.pairs;
-  const int hkv = rem % a.Hkv;
-  const int b = rem / a.Hkv;
-  const int hq0 = hkv * a.group + 2 * pair;
-  const bool two = (2 * pair + 1) < a.group;
-  const int q0 = qblk * FM;
-  const int nblk = qblk + 1;  // KV blocks 0..qblk (FM == FN)
-
   if (threadIdx.x == 0) {
     mbar_init(&bars->q_full, 1);
+    mbar_init(&bars->q_empty, 1);
     for (int i = 0; i < KV_STAGES; ++i) {
       mbar_init(&bars->k_full[i], 1);
       mbar_init(&bars->v_full[i], 1);
@@ -125,8 +142,9 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars->s_full[i], 1);
-      mbar_init(&bars->p_full[i], 4);  // one arrival per softmax warp
+      mbar_init(&bars->p_full[i], 4);   // one arrival per softmax warp
       mbar_init(&bars->o_done[i], 1);
+      mbar_init(&bars->o_empty[i], 4);  // one arrival per softmax warp
     }
     bars->abort_flag = 0;
     fence_barrier_init();
@@ -146,117 +164,160 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
   const WaitCtx wc{&bars->abort_flag, a.status, a.limit_ns};
 
+  // The CTA is persistent: it walks its work items in a loop, and every role keeps running counters for the barrier
+  // phases, so the loads of the next item start while the current one is still in its last softmax / epilogue.
   if (warp == 8) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      const int ntile = two ? 2 : 1;
-      mbar_arrive_expect_tx(&bars->q_full, (uint32_t)(ntile * TILE_BYTES));
-      for (int t = 0; t < ntile; ++t) {
-        const int hq = hq0 + t;
-        const int y = b * a.q_rb + hq * a.q_rh + q0;
-        tma_load_2d(sQ + t * TILE_BYTES, &tma_q, &bars->q_full, hq * a.q_cs, y);
-        tma_load_2d(sQ + t * TILE_BYTES + HALF_BYTES, &tma_q, &bars->q_full, hq * a.q_cs + 64, y);
-      }
-      const int ykv = b * a.kv_rb + hkv * a.kv_rh;
-      const int xkv = hkv * a.kv_cs;
-      for (int j = 0; j < nblk; ++j) {
-        const int st = j % KV_STAGES;
-        const uint32_t ph = (uint32_t)(j / KV_STAGES) & 1u;
-        if (!mbar_wait(&bars->kv_empty[st], ph ^ 1u, wc, EMK_DEV_TIMEOUT_PRODUCER)) break;
-        mbar_arrive_expect_tx(&bars->k_full[st], TILE_BYTES);
-        tma_load_2d(sK + st * TILE_BYTES, &tma_k, &bars->k_full[st], xkv, ykv + j * FN);
-        tma_load_2d(sK + st * TILE_BYTES + HALF_BYTES, &tma_k, &bars->k_full[st], xkv + 64, ykv + j * FN);
-        mbar_arrive_expect_tx(&bars->v_full[st], TILE_BYTES);
-        tma_load_2d(sV + st * TILE_BYTES, &tma_v, &bars->v_full[st], xkv, ykv + j * FN);
-        tma_load_2d(sV + st * TILE_BYTES + HALF_BYTES, &tma_v, &bars->v_full[st], xkv + 64, ykv + j * FN);
+      uint32_t kv_count = 0, item_i = 0;
+      bool ok = true;
+      for (int rnd = 0; rnd < a.n_rounds && ok; ++rnd) {
+        const int w = item_of_round(rnd, (int)blockIdx.x, (int)gridDim.x);
+        if (w >= a.n_items) continue;
+        const WorkItem it = decode_item(a, w);
+        const int ntile = it.two ? 2 : 1;
+        if (!mbar_wait(&bars->q_empty, (item_i & 1u) ^ 1u, wc, EMK_DEV_TIMEOUT_PRODUCER)) break;
+        mbar_arrive_expect_tx(&bars->q_full, (uint32_t)(ntile * TILE_BYTES));
+        for (int t = 0; t < ntile; ++t) {
+          const int hq = it.hq0 + t;
+          const int y = it.b * a.q_rb + hq * a.q_rh + it.q0;
+          tma_load_2d(sQ + t * TILE_BYTES, &tma_q, &bars->q_full, hq * a.q_cs, y);
+          tma_load_2d(sQ + t * TILE_BYTES + HALF_BYTES, &tma_q, &bars->q_full, hq * a.q_cs + 64, y);
+        }
+        const int ykv = it.b * a.kv_rb + it.hkv * a.kv_rh;
+        const int xkv = it.hkv * a.kv_cs;
+        for (int j = 0; j < it.nblk; ++j, ++kv_count) {
+          const int st = (int)(kv_count % KV_STAGES);
+          const uint32_t ph = (kv_count / KV_STAGES) & 1u;
+          if (!mbar_wait(&bars->kv_empty[st], ph ^ 1u, wc, EMK_DEV_TIMEOUT_PRODUCER)) {
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(&bars->k_full[st], TILE_BYTES);
+          tma_load_2d(sK + st * TILE_BYTES, &tma_k, &bars->k_full[st], xkv, ykv + j * FN);
+          tma_load_2d(sK + st * TILE_BYTES + HALF_BYTES, &tma_k, &bars->k_full[st], xkv + 64, ykv + j * FN);
+          mbar_arrive_expect_tx(&bars->v_full[st], TILE_BYTES);
+          tma_load_2d(sV + st * TILE_BYTES, &tma_v, &bars->v_full[st], xkv, ykv + j * FN);
+          tma_load_2d(sV + st * TILE_BYTES + HALF_BYTES, &tma_v, &bars->v_full[st], xkv + 64, ykv + j * FN);
+        }
+        ++item_i;
       }
     }
   } else if (warp == 9) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      const int ntile = two ? 2 : 1;
-      const uint32_t sq_addr = smem_u32(sQ);
-      const uint32_t sk_addr = smem_u32(sK);
-      const uint32_t sv_addr = smem_u32(sV);
+      const uint32_t hi = smem_desc_hi(1024);
+      const uint32_t q_lo = smem_desc_lo(smem_u32(sQ), 0);
+      const uint32_t k_lo = smem_desc_lo(smem_u32(sK), 0);
+      const uint32_t v_lo = smem_desc_lo(smem_u32(sV), HALF_BYTES);
       auto issue_s = [&](int t, int st) {
-        const uint32_t qa = sq_addr + t * TILE_BYTES;
-        const uint32_t ka = sk_addr + st * TILE_BYTES;
+        const uint32_t qa = q_lo + (uint32_t)(t * (TILE_BYTES >> 4));
+        const uint32_t ka = k_lo + (uint32_t)(st * (TILE_BYTES >> 4));
+        const uint32_t d = tmem_base + (uint32_t)(t * FN);
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
-          const uint32_t off = (uint32_t)((ks >> 2) * HALF_BYTES + (ks & 3) * 32);
-          umma_ss(tmem_base + (uint32_t)(t * FN), make_smem_desc(qa + off, 0, 1024), make_smem_desc(ka + off, 0, 1024),
-                  IDESC_S, (uint32_t)(ks != 0));
+          const uint32_t off = (uint32_t)(((ks >> 2) * HALF_BYTES + (ks & 3) * 32) >> 4);
+          umma_ss_lohi(d, qa + off, ka + off, hi, IDESC_S, ks != 0 ? 1u : 0u);
         }
       };
       auto issue_pv = [&](int t, int st, bool accumulate) {
-        const uint32_t va = sv_addr + st * TILE_BYTES;
+        const uint32_t va = v_lo + (uint32_t)(st * (TILE_BYTES >> 4));
+        const uint32_t d = tmem_base + 256u + (uint32_t)(t * HD);
+        const uint32_t pa = tmem_base + (uint32_t)(t * FN);
+        umma_ts_lohi(d, pa, va, hi, IDESC_PV, accumulate ? 1u : 0u);
 #pragma unroll
-        for (int ks = 0; ks < FN / 16; ++ks) {
-          umma_ts(tmem_base + 256u + (uint32_t)(t * HD), tmem_base + (uint32_t)(t * FN) + (uint32_t)(ks * 8),
-                  make_smem_desc(va + ks * 16 * 128, HALF_BYTES, 1024), IDESC_PV,
-                  (uint32_t)(accumulate || ks != 0));
-        }
+        for (int ks = 1; ks < FN / 16; ++ks)
+          umma_ts_lohi(d, pa + (uint32_t)(ks * 8), va + (uint32_t)((ks * 16 * 128) >> 4), hi, IDESC_PV, 1u);
       };
-      // A tcgen05.commit stalls this thread for a few hundred cycles (it drains behind the MMAs issued so far), so
-      // only the commits the softmax warps cannot do without are issued: one per S tile, and one after the last PV.
-      // "PV of block j-1 is done" is implied by the S commit of block j (a commit covers every earlier MMA of this
-      // thread), and the K/V stage is released by a softmax thread that has seen that commit.
-      bool ok = mbar_wait(&bars->q_full, 0, wc, EMK_DEV_TIMEOUT_MMA);
-      if (ok) ok = mbar_wait(&bars->k_full[0], 0, wc, EMK_DEV_TIMEOUT_MMA);
-      if (ok) {
-        tc_fence_after();
+      // A tcgen05.commit stalls this thread for a few hundred cycles, so only the commits the softmax warps cannot
+      // do without are issued: one per S tile and one after the last PV of an item. "PV of block j-1 is done" is
+      // implied by the S commit of block j (a commit covers every earlier MMA of this thread); the K/V stage and the
+      // Q buffer are handed back by a softmax thread that has seen that commit.
+      uint32_t kv_count = 0, item_i = 0;
+      uint32_t iters[2] = {0, 0};   // softmax round trips per tile (parity of s_full / p_full)
+      uint32_t items[2] = {0, 0};   // items per tile (parity of o_done / o_empty)
+      bool ok = true;
+      for (int rnd = 0; rnd < a.n_rounds && ok; ++rnd) {
+        const int w = item_of_round(rnd, (int)blockIdx.x, (int)gridDim.x);
+        if (w >= a.n_items) continue;
+        const WorkItem it = decode_item(a, w);
+        const int ntile = it.two ? 2 : 1;
+        ok = mbar_wait(&bars->q_full, item_i & 1u, wc, EMK_DEV_TIMEOUT_MMA);
+        if (ok) ok = mbar_wait(&bars->k_full[kv_count % KV_STAGES], (kv_count / KV_STAGES) & 1u, wc, EMK_DEV_TIMEOUT_MMA);
+        if (!ok) break;
         for (int t = 0; t < ntile; ++t) {
-          issue_s(t, 0);
+          issue_s(t, (int)(kv_count % KV_STAGES));
           tc_commit(&bars->s_full[t]);
         }
-      }
-      for (int j = 0; j < nblk && ok; ++j) {
-        const int st = j % KV_STAGES;
-        const uint32_t ph = (uint32_t)(j / KV_STAGES) & 1u;
-        const int stn = (j + 1) % KV_STAGES;
-        const uint32_t phn = (uint32_t)((j + 1) / KV_STAGES) & 1u;
-        const bool has_next = (j + 1) < nblk;
-        for (int t = 0; t < ntile && ok; ++t) {
-          ok = mbar_wait(&bars->p_full[t], (uint32_t)j & 1u, wc, EMK_DEV_TIMEOUT_MMA);
-          if (ok && t == 0) ok = mbar_wait(&bars->v_full[st], ph, wc, EMK_DEV_TIMEOUT_MMA);
-          if (!ok) break;
-          tc_fence_after();
-          issue_pv(t, st, j > 0);
-          if (has_next) {
-            if (t == 0) {
-              ok = mbar_wait(&bars->k_full[stn], phn, wc, EMK_DEV_TIMEOUT_MMA);
-              if (!ok) break;
+        for (int j = 0; j < it.nblk && ok; ++j, ++kv_count) {
+          const int st = (int)(kv_count % KV_STAGES);
+          const uint32_t ph = (kv_count / KV_STAGES) & 1u;
+          const int stn = (int)((kv_count + 1) % KV_STAGES);
+          const uint32_t phn = ((kv_count + 1) / KV_STAGES) & 1u;
+          const bool has_next = (j + 1) < it.nblk;
+          for (int t = 0; t < ntile && ok; ++t) {
+            ok = mbar_wait(&bars->p_full[t], iters[t] & 1u, wc, EMK_DEV_TIMEOUT_MMA);
+            if (ok && t == 0) ok = mbar_wait(&bars->v_full[st], ph, wc, EMK_DEV_TIMEOUT_MMA);
+            // the first PV of an item overwrites O: the epilogue of the previous item must have read it
+            if (ok && j == 0) ok = mbar_wait(&bars->o_empty[t], (items[t] & 1u) ^ 1u, wc, EMK_DEV_TIMEOUT_MMA);
+            if (!ok) break;
+            tc_fence_after();
+            issue_pv(t, st, j > 0);
+            ++iters[t];
+            if (has_next) {
+              if (t == 0) {
+                ok = mbar_wait(&bars->k_full[stn], phn, wc, EMK_DEV_TIMEOUT_MMA);
+                if (!ok) break;
+              }
+              issue_s(t, stn);
+              tc_commit(&bars->s_full[t]);
+            } else {
+              tc_commit(&bars->o_done[t]);
+              ++items[t];
             }
-            issue_s(t, stn);
-            tc_commit(&bars->s_full[t]);
-          } else {
-            tc_commit(&bars->o_done[t]);
           }
         }
+        ++item_i;
       }
     }
   } else {
     // ---------------- softmax / correction / epilogue: warps 0..3 tile 0, warps 4..7 tile 1 ----------------
     const int t = warp >> 2;
-    if (t == 0 || two) {
-      const int quarter = warp & 3;
-      const int r_in_tile = quarter * 32 + lane;
-      const int q_row = q0 + r_in_tile;  // position in the sequence
-      const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-      const uint32_t tS = tmem_base + lane_base + (uint32_t)(t * FN);
-      const uint32_t tO = tmem_base + lane_base + 256u + (uint32_t)(t * HD);
+    const int quarter = warp & 3;
+    const int r_in_tile = quarter * 32 + lane;
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const uint32_t tS = tmem_base + lane_base + (uint32_t)(t * FN);
+    const uint32_t tO = tmem_base + lane_base + 256u + (uint32_t)(t * HD);
+    const bool elected = quarter == 0 && lane == 0;
+    uint32_t kv_base = 0;   // KV blocks consumed by the CTA before the current item
+    uint32_t iter = 0;      // softmax round trips of this tile
+    uint32_t item_n = 0;    // items this tile took part in
+    bool ok = true;
+    for (int rnd = 0; rnd < a.n_rounds && ok; ++rnd) {
+      const int w = item_of_round(rnd, (int)blockIdx.x, (int)gridDim.x);
+      if (w >= a.n_items) continue;
+      const WorkItem it = decode_item(a, w);
+      const int nblk = it.nblk;
+      if (t == 1 && !it.two) {  // this tile sits the item out
+        kv_base += (uint32_t)nblk;
+        continue;
+      }
+      const bool last_tile = t == (it.two ? 1 : 0);  // its commits come last in the MMA thread's order
+      const int q_row = it.q0 + r_in_tile;           // position in the sequence
       float m_used = -CUDART_INF_F;
       float l = 0.f;
-      bool ok = true;
-      for (int j = 0; j < nblk; ++j) {
-        if (!mbar_wait_warp(&bars->s_full[t], (uint32_t)j & 1u, wc, EMK_DEV_TIMEOUT_SOFTMAX)) {
+      for (int j = 0; j < nblk; ++j, ++iter) {
+        if (!mbar_wait_warp(&bars->s_full[t], iter & 1u, wc, EMK_DEV_TIMEOUT_SOFTMAX)) {
           ok = false;
           break;
         }
         tc_fence_after();
-        // The S commit of block j covers the PV of block j-1 of both tiles (tile 0's MMAs precede tile 1's in the
-        // issuing thread), so the last tile's first softmax thread hands the K/V stage of block j-1 back here.
-        if (j > 0 && t == (two ? 1 : 0) && quarter == 0 && lane == 0) mbar_arrive(&bars->kv_empty[(j - 1) % KV_STAGES]);
+        if (last_tile && elected) {
+          // this S commit covers the PV of block j-1 of both tiles: hand that K/V stage back; after the last S of
+          // the item the Q tiles are free as well
+          if (j > 0) mbar_arrive(&bars->kv_empty[(kv_base + (uint32_t)j - 1u) % KV_STAGES]);
+          if (j == nblk - 1) mbar_arrive(&bars->q_empty);
+        }
         uint32_t s[FN];
 #pragma unroll
         for (int c = 0; c < FN / 32; ++c) tmem_ld_x32(tS + (uint32_t)(c * 32), s + c * 32);
@@ -327,30 +388,41 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->p_full[t]);
       }
-      if (ok && mbar_wait_warp(&bars->o_done[t], 0u, wc, EMK_DEV_TIMEOUT_SOFTMAX)) {
-        tc_fence_after();
-        const float inv = 1.0f / l;
-        const int hq = hq0 + t;
-        __nv_bfloat16* orow =
-            a.o + ((int64_t)b * a.o_rb + (int64_t)hq * a.o_rh + q_row) * a.ld_o + (int64_t)hq * a.o_cs;
-#pragma unroll 1
-        for (int c = 0; c < HD / 32; ++c) {
-          uint32_t o[32];
-          tmem_ld_x32(tO + (uint32_t)(c * 32), o);
-          tmem_ld_wait();
-          if (q_row < a.S) {
+      if (!ok) break;
+      if (!mbar_wait_warp(&bars->o_done[t], item_n & 1u, wc, EMK_DEV_TIMEOUT_SOFTMAX)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      // every MMA of the item is done: the last K/V stage goes back to the producer
+      if (last_tile && elected) mbar_arrive(&bars->kv_empty[(kv_base + (uint32_t)nblk - 1u) % KV_STAGES]);
+      const float inv = 1.0f / l;
+      const int hq = it.hq0 + t;
+      __nv_bfloat16* orow =
+          a.o + ((int64_t)it.b * a.o_rb + (int64_t)hq * a.o_rh + q_row) * a.ld_o + (int64_t)hq * a.o_cs;
+      uint32_t o[2][32];
+      tmem_ld_x32(tO, o[0]);
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              uint4 v;
-              v.x = pack_bf16x2(__uint_as_float(o[q * 8 + 0]) * inv, __uint_as_float(o[q * 8 + 1]) * inv);
-              v.y = pack_bf16x2(__uint_as_float(o[q * 8 + 2]) * inv, __uint_as_float(o[q * 8 + 3]) * inv);
-              v.z = pack_bf16x2(__uint_as_float(o[q * 8 + 4]) * inv, __uint_as_float(o[q * 8 + 5]) * inv);
-              v.w = pack_bf16x2(__uint_as_float(o[q * 8 + 6]) * inv, __uint_as_float(o[q * 8 + 7]) * inv);
-              *reinterpret_cast<uint4*>(orow + c * 32 + q * 8) = v;
-            }
-          }
+      for (int c = 0; c < HD / 32; ++c) {
+        tmem_ld_wait_regs(o[c & 1]);
+        if (c + 1 < HD / 32) tmem_ld_x32(tO + (uint32_t)((c + 1) * 32), o[(c + 1) & 1]);
+        if (c + 1 == HD / 32) {
+          // O is in registers: the MMA thread may overwrite it with the next item's first PV
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars->o_empty[t]);
+        }
+        if (q_row < a.S) {
+          uint32_t v[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            v[i] = pack_bf16x2(__uint_as_float(o[c & 1][2 * i]) * inv, __uint_as_float(o[c & 1][2 * i + 1]) * inv);
+          st_global_v8(orow + c * 32, v);
+          st_global_v8(orow + c * 32 + 16, v + 8);
         }
       }
+      ++item_n;
+      kv_base += (uint32_t)nblk;
     }
   }
 
@@ -432,8 +504,11 @@ int fmha_launch(emk_handle_t h, const void* q, const void* k, const void* v, voi
     EMK_CUDA_TRY(h, cudaFuncSetAttribute(fmha_causal_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FMHA_SMEM));
     configured[h->device] = true;
   }
-  const int64_t grid = (int64_t)a.nqblk * B * Hkv * a.pairs;
-  if (grid > 0x7fffffffLL) return EMK_ERR_SHAPE;
+  const int64_t n_items = (int64_t)a.nqblk * B * Hkv * a.pairs;
+  if (n_items > 0x7fffffffLL) return EMK_ERR_SHAPE;
+  a.n_items = (int)n_items;
+  const int grid = a.n_items < h->sm_count ? a.n_items : h->sm_count;  // persistent: one CTA per SM
+  a.n_rounds = (a.n_items + grid - 1) / grid;
   fmha_causal_kernel<<<(unsigned)grid, FMHA_THREADS, FMHA_SMEM, s>>>(tq, tk, tv, a);
   EMK_LAUNCH_CHECK(h);
   return EMK_OK;
