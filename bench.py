@@ -259,7 +259,7 @@ def gemm_event_pass(model) -> dict:
 
     from deplodock_b200 import ops
 
-    names = ["embed_gather", "rmsnorm", "linear", "qknorm_rope_", "sdpa_causal_gqa_tok", "pool_norm_l2"]
+    names = ["embed_gather", "rmsnorm", "linear", "linear_qknorm_rope", "sdpa_causal_gqa_tok", "pool_norm_l2"]
     originals = {n: getattr(ops, n) for n in names}
     events = []
 
@@ -269,14 +269,16 @@ def gemm_event_pass(model) -> dict:
             s.record()
             r = fn(*args, **kw)
             e.record()
-            key, fl = name, 0
-            if name == "linear":
+            fam, key, fl = name, name, 0
+            if name in ("linear", "linear_qknorm_rope"):
                 x, w = args[0], args[1]
                 M = x.numel() // x.shape[-1]
                 fl = 2 * M * x.shape[-1] * w.shape[0]
-                epi = "residual" if kw.get("residual") is not None else ("swiglu" if kw.get("swiglu") else "none")
+                epi = "qknorm_rope" if name != "linear" else (
+                    "residual" if kw.get("residual") is not None else ("swiglu" if kw.get("swiglu") else "none"))
                 key = f"{M}x{w.shape[0]}x{x.shape[-1]}+{epi}"
-            events.append((s, e, name, key, fl))
+                fam = "linear"
+            events.append((s, e, fam, key, fl))
             return r
         return timed
 

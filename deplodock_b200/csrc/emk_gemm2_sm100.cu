@@ -248,7 +248,7 @@ int launch_gemm2(emk_handle_t h, const CUtensorMap& ta, const CUtensorMap& tb, c
 int emk_gemm2_launch(emk_handle_t h, const void* x, const void* w, emk::GemmArgs g, int wlayout, cudaStream_t s) {
   // 256-column tiles whenever the output is wider than 128 columns: narrower tiles cost almost the same time per
   // K step (measured), so they only pay off when they avoid computing padding.
-  const int bn = g.N > 128 ? 256 : 128;
+  const int bn = (g.N > 128 || g.epi == EMK_EPI_QKNORM_ROPE_INTERNAL) ? 256 : 128;
   g.tiles_m = (g.M + 2 * BM - 1) / (2 * BM);
   g.tiles_n = (g.N + bn - 1) / bn;
   CUtensorMap ta, tb;

@@ -20,9 +20,18 @@ struct GemmArgs {
   int tiles_m, tiles_n, kblocks;
   int epi;
   int wide;  // y (and residual) rows are 32-byte aligned: use 256-bit accesses
+  // fused q/k-norm + RoPE epilogue (epi == EMK_EPI_QKNORM_ROPE_INTERNAL): output columns are heads of 128
+  const __nv_bfloat16* qk_qw;
+  const __nv_bfloat16* qk_kw;
+  const __nv_bfloat16* qk_cos;  // [S,128] bf16
+  const __nv_bfloat16* qk_sin;
+  int qk_S, qk_Hq, qk_Hkv;
+  float qk_eps;
   int* status;
   unsigned long long limit_ns;
 };
+
+constexpr int EMK_EPI_QKNORM_ROPE_INTERNAL = 100;
 
 // Tile order of the persistent kernels: tiles are walked in groups of GROUP_M row-tiles by all column-tiles, rows
 // fastest inside a group, so the CTAs running at one time share a few A row-blocks and a few W column-blocks and
@@ -130,10 +139,81 @@ __device__ __forceinline__ void epilogue_store32(const GemmArgs& g, const uint32
   }
 }
 
+
+// One head (128 accumulator columns of this thread's row) of the fused QKV projection: round to bf16 as the GEMM
+// output would be, then for query/key heads the per-head RMSNorm and the rotate-half RoPE on packed bf16 pairs with
+// the rounding steps of the eager bf16 module (normalised -> bf16, * weight -> bf16, each RoPE product -> bf16,
+// sum -> bf16); value heads are stored as they are. Thread-local: the row's 128 columns live in this thread.
+__device__ __forceinline__ void epilogue_head_qknorm_rope(const GemmArgs& g, uint32_t taddr, int row, int col0) {
+  uint32_t v[128];
+#pragma unroll
+  for (int c = 0; c < 4; ++c) tmem_ld_x32(taddr + (uint32_t)(c * 32), v + c * 32);
+  tmem_ld_wait();
+  if (row >= g.M || col0 >= g.N) return;
+  const int head = col0 >> 7;
+  uint32_t n[64];
+  float ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < 64; ++e) {
+    n[e] = pack_bf16x2(__uint_as_float(v[2 * e]), __uint_as_float(v[2 * e + 1]));
+    const float f0 = bf16_lo(n[e]), f1 = bf16_hi(n[e]);
+    ss = fmaf(f0, f0, ss);
+    ss = fmaf(f1, f1, ss);
+  }
+  __nv_bfloat16* out = g.y + (int64_t)row * g.ldy + col0;
+  if (head < g.qk_Hq + g.qk_Hkv) {
+    const float r = 1.0f / sqrtf(ss * (1.0f / 128.0f) + g.qk_eps);
+    const __nv_bfloat16* wp = head < g.qk_Hq ? g.qk_qw : g.qk_kw;
+#pragma unroll
+    for (int q = 0; q < 16; ++q) {
+      const uint4 wv = __ldg(reinterpret_cast<const uint4*>(wp + q * 8));
+      const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int e = q * 4 + j;
+        const __nv_bfloat162 xn = __floats2bfloat162_rn(bf16_lo(n[e]) * r, bf16_hi(n[e]) * r);
+        const __nv_bfloat162 res = __hmul2_rn(*reinterpret_cast<const __nv_bfloat162*>(&ww[j]), xn);
+        n[e] = *reinterpret_cast<const uint32_t*>(&res);
+      }
+    }
+    const int s = row % g.qk_S;
+    const __nv_bfloat16* cp = g.qk_cos + (int64_t)s * 128;  // cos[i] == cos[i + 64]: only the first half is read
+    const __nv_bfloat16* sp = g.qk_sin + (int64_t)s * 128;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const uint4 cv = __ldg(reinterpret_cast<const uint4*>(cp + q * 8));
+      const uint4 sv = __ldg(reinterpret_cast<const uint4*>(sp + q * 8));
+      const uint32_t cc[4] = {cv.x, cv.y, cv.z, cv.w};
+      const uint32_t sn[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int e = q * 4 + j;  // pair e holds elements 2e, 2e+1; its rotate-half partner is pair e + 32
+        const __nv_bfloat162 c2 = *reinterpret_cast<const __nv_bfloat162*>(&cc[j]);
+        const __nv_bfloat162 s2 = *reinterpret_cast<const __nv_bfloat162*>(&sn[j]);
+        const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&n[e]);
+        const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&n[e + 32]);
+        const uint32_t neg_hi_bits = n[e + 32] ^ 0x80008000u;
+        const __nv_bfloat162 neg_hi = *reinterpret_cast<const __nv_bfloat162*>(&neg_hi_bits);
+        const __nv_bfloat162 olo = __hadd2_rn(__hmul2_rn(lo, c2), __hmul2_rn(neg_hi, s2));
+        const __nv_bfloat162 ohi = __hadd2_rn(__hmul2_rn(hi, c2), __hmul2_rn(lo, s2));
+        n[e] = *reinterpret_cast<const uint32_t*>(&olo);
+        n[e + 32] = *reinterpret_cast<const uint32_t*>(&ohi);
+      }
+    }
+  }
+#pragma unroll
+  for (int q = 0; q < 8; ++q) st_global_v8(out + q * 16, n + q * 8);
+}
+
 // Drains one accumulator (NCHUNK x 32 columns of this thread's row) from tensor memory through the epilogue. The load
 // of chunk c+1 is in flight while chunk c is converted and stored.
 template <int NCHUNK>
 __device__ __forceinline__ void epilogue_drain(const GemmArgs& g, uint32_t taddr, int row, int n0) {
+  if (g.epi == EMK_EPI_QKNORM_ROPE_INTERNAL) {
+#pragma unroll 1
+    for (int hd = 0; hd < NCHUNK / 4; ++hd) epilogue_head_qknorm_rope(g, taddr + (uint32_t)(hd * 128), row, n0 + hd * 128);
+    return;
+  }
   uint32_t r[2][32];
   tmem_ld_x32(taddr, r[0]);
 #pragma unroll

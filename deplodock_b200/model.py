@@ -6,10 +6,12 @@ a captured CUDA graph per sequence (``emmy/serving/runner.py:204-236``); vLLM th
 (``emmy/serving/vllm_model.py:50-58``). The traced layer is GatherOp, five RMSNorm chains, seven LinearOps, a RoPE
 chain, repeat_kv, SdpaOp with an additive causal mask, and a SwiGLU — 18 generated kernels per layer.
 
-Here the same dataflow is a fixed plan of eight launches per layer over a whole batch of sequences:
+Here the same dataflow is a fixed plan of seven launches per layer over a whole batch of sequences:
 
-    rmsnorm -> GEMM(Wqkv) -> q/k-norm + RoPE (in place) -> causal GQA flash attention (token-major, no transposes)
+    rmsnorm -> GEMM(Wqkv) + q/k-norm + RoPE (epilogue) -> causal GQA flash attention (token-major, no transposes)
             -> GEMM(Wo) + residual -> rmsnorm -> GEMM(Wgate|Wup interleaved) + SwiGLU -> GEMM(Wdown) + residual
+
+(with 128 tokens or fewer per chunk the q/k-norm + RoPE runs as its own in-place kernel after the projection)
 
 and a last-token RMSNorm + L2 kernel. The whole forward is captured once in a CUDA graph and replayed. Sequences are
 independent, so a batch can be processed in chunks (``chunk_seqs``) whose activations stay resident in the 126 MB L2.
@@ -74,7 +76,7 @@ class EmbedForward:
     """Batch forward of the trunk on one GPU. ``state_dict`` uses the HF ``Qwen3Model`` parameter names."""
 
     #: kernel launches per layer / outside the layers, for launch accounting in the bench
-    LAUNCHES_PER_LAYER = 8
+    LAUNCHES_PER_LAYER = 7
     LAUNCHES_FIXED = 2
 
     def __init__(self, cfg, state_dict: dict[str, torch.Tensor], *, batch: int, seq: int, device=None,
@@ -129,7 +131,8 @@ class EmbedForward:
     @property
     def num_launches(self) -> int:
         chunks = self.batch // self.chunk_seqs
-        return chunks * (self.LAUNCHES_PER_LAYER * self.cfg.num_hidden_layers + self.LAUNCHES_FIXED)
+        per_layer = self.LAUNCHES_PER_LAYER + (1 if self.chunk_seqs * self.seq <= 128 else 0)
+        return chunks * (per_layer * self.cfg.num_hidden_layers + self.LAUNCHES_FIXED)
 
     def flops(self) -> int:
         return self.cfg.linear_flops_per_token() * self.batch * self.seq + self.cfg.attention_flops(self.batch,
@@ -143,8 +146,7 @@ class EmbedForward:
         ops.embed_gather(self.embed, ids, out=self.h)
         for lw in self.layers:
             ops.rmsnorm(self.h, lw.ln1, eps, out=self.x)
-            ops.linear(self.x, lw.wqkv, out=self.qkv)
-            ops.qknorm_rope_(self.qkv, lw.qn, lw.kn, self.cos, self.sin, S, nq, nkv, eps)
+            ops.linear_qknorm_rope(self.x, lw.wqkv, lw.qn, lw.kn, self.cos, self.sin, S, nq, nkv, eps, out=self.qkv)
             ops.sdpa_causal_gqa_tok(self.qkv, B, S, nq, nkv, self.attn)
             ops.linear(self.attn, lw.wo, residual=self.h, out=self.h)
             ops.rmsnorm(self.h, lw.ln2, eps, out=self.x)

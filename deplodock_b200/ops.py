@@ -137,6 +137,26 @@ def linear_simt(x, w, *, residual=None, bias=None, swiglu=False, w_is_kn=False, 
                           out=out)
 
 
+def linear_qknorm_rope(x, w_qkv, q_weight, k_weight, cos, sin, S: int, Hq: int, Hkv: int, eps: float = 1e-6,
+                       out=None) -> torch.Tensor:
+    """Fused QKV projection ``x @ w_qkv.T`` with per-head q/k RMSNorm and RoPE in the GEMM epilogue; the result is the
+    token-major ``[T, (Hq+2*Hkv)*128]`` buffer the attention kernel reads."""
+    _check_cuda_contig(x, w_qkv, q_weight, k_weight, cos, sin, out)
+    if not (x.dtype == w_qkv.dtype == cos.dtype == sin.dtype == torch.bfloat16):
+        raise TypeError("linear_qknorm_rope expects bfloat16 operands and tables")
+    K = x.shape[-1]
+    M = x.numel() // K
+    N = w_qkv.shape[0]
+    if w_qkv.shape[1] != K or cos.shape[-2:] != (S, 128):
+        raise ValueError("weight/table shapes do not match")
+    y = torch.empty(M, N, dtype=torch.bfloat16, device=x.device) if out is None else out
+    h = handle()
+    h.check(h.lib.emk_linear_bf16_qknorm_rope(h.ptr, _ptr(x), _ptr(w_qkv), _ptr(y), M, N, K, _ptr(q_weight),
+                                              _ptr(k_weight), _ptr(cos), _ptr(sin), S, Hq, Hkv, float(eps),
+                                              _stream()), "emk_linear_bf16_qknorm_rope")
+    return y
+
+
 def linear_f32(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, w_is_kn: bool = False) -> torch.Tensor:
     """fp32 LinearOp / MatmulOp on CUDA cores (fp32 graphs have no tensor-core path)."""
     _check_cuda_contig(x, w, bias)

@@ -341,3 +341,35 @@ def test_expired_device_wait_is_reported_and_context_survives(ops):
     x, w = inputs.rmsnorm_inputs((4,), 256)
     got = ops.rmsnorm(_dev(x), _dev(w)).cpu()
     metrics.assert_fp32_reduction(got, cpu_ref.rmsnorm(x, w), what="after expiry")
+
+
+@pytest.mark.parametrize("B,S", [(2, 40), (3, 130), (1, 512)])
+def test_linear_qknorm_rope_fused_equals_two_step(ops, B, S):
+    """The fused epilogue (taken above 128 rows) against projection + stand-alone q/k-norm+RoPE kernel, and against
+    the eager module's rounding sequence."""
+    Hq, Hkv, D, K = 16, 8, 128, 256
+    T = B * S
+    g = torch.Generator().manual_seed(21)
+    x = torch.randn(T, K, generator=g).bfloat16()
+    w = (0.06 * torch.randn((Hq + 2 * Hkv) * D, K, generator=g)).bfloat16()
+    qw = (1 + 0.1 * torch.randn(D, generator=g)).bfloat16()
+    kw = (1 + 0.1 * torch.randn(D, generator=g)).bfloat16()
+    cos, sin = inputs.rope_tables(S, D, 1e6)
+    cb, sb = cos.bfloat16(), sin.bfloat16()
+    fused = ops.linear_qknorm_rope(_dev(x), _dev(w), _dev(qw), _dev(kw), _dev(cb), _dev(sb), S, Hq, Hkv, 1e-6).cpu()
+    two = ops.qknorm_rope_(ops.linear(_dev(x), _dev(w)), _dev(qw), _dev(kw), _dev(cb), _dev(sb), S, Hq, Hkv, 1e-6).cpu()
+    ops.device_status()
+    assert (fused != two).float().mean().item() < 0.005  # same arithmetic; only the order of the fp32 row sum differs
+    metrics.assert_bf16_tensor_path(fused, two, what="fused vs two-step")
+
+    def rot(t):
+        return torch.cat([-t[..., D // 2:], t[..., : D // 2]], dim=-1)
+
+    proj = cpu_ref.linear(x, w)
+    q = cpu_ref.rmsnorm_hf(proj[:, : Hq * D].view(B, S, Hq, D), qw)
+    k = cpu_ref.rmsnorm_hf(proj[:, Hq * D: (Hq + Hkv) * D].view(B, S, Hkv, D), kw)
+    c4, s4 = cb[None, :, None, :], sb[None, :, None, :]
+    ref = proj.clone()
+    ref[:, : Hq * D] = ((q * c4) + (rot(q) * s4)).reshape(T, -1)
+    ref[:, Hq * D: (Hq + Hkv) * D] = ((k * c4) + (rot(k) * s4)).reshape(T, -1)
+    metrics.assert_bf16_tensor_path(fused, ref, abs_tol=6e-2, what="fused qkv vs eager")
