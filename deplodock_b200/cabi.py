@@ -56,7 +56,7 @@ _SIGNATURES: dict[str, list] = {
     "emk_linear_f32_simt": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int,
                             c_void_p],
     "emk_linear_bf16_qknorm_rope": [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p,
-                                    c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_float, c_void_p],
+                                    c_void_p, c_void_p, c_int64, c_int64, c_int64, c_float, c_void_p],
     "emk_linear_bf16_w8": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p],
     "emk_sdpa_causal_gqa_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                  c_int64, c_int64, c_float, c_void_p],

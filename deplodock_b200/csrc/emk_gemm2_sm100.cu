@@ -9,7 +9,8 @@
 //
 //   warp 4      TMA producer (both CTAs; byte counts are credited to the LEADER's full barrier)
 //   warp 5      MMA issuer (leader CTA only); tcgen05.commit arrives on the empty / tmem_full barriers of BOTH CTAs
-//   warps 0..3  epilogue (both CTAs, own accumulator rows); arrive on the leader's tmem_empty barrier
+//   warps 0..3, 6..9  epilogue (both CTAs, own accumulator rows; left / right half of the columns); arrive on the
+//               leader's tmem_empty barrier
 // No load uses cluster multicast. Every wait is bounded; the two cluster-wide barriers at start and end are reached by
 // all threads of both CTAs on every path.
 #include "emk_gemm_common.cuh"
@@ -20,7 +21,7 @@ namespace {
 
 using namespace emk;
 
-constexpr int G2_THREADS = 192;
+constexpr int G2_THREADS = 320;  // warps 0-3 and 6-9: epilogue (left / right half of the tile's columns), 4: TMA, 5: MMA
 constexpr int G2_GROUP_M = 8;  // row-tiles of 256 per raster group
 constexpr int G2_MAX_STAGES = 8;
 
@@ -69,7 +70,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars->tmem_full[i], 1);
-      mbar_init(&bars->tmem_empty[i], 8);  // 4 epilogue warps of each CTA
+      mbar_init(&bars->tmem_empty[i], 16);  // 8 epilogue warps of each CTA
     }
     bars->abort_flag = 0;
     fence_barrier_init();
@@ -179,7 +180,10 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       }
     }
   } else {
-    // ---------------- epilogue warps 0..3 (both CTAs) ----------------
+    // ---------------- epilogue: warps 0..3 drain the left half of the tile's columns, warps 6..9 the right half ------
+    // (a warp may only touch the TMEM lanes of its quarter, warp_id % 4, so two warps share each quarter)
+    const int quarter = warp & 3;
+    const int half = warp >= 6 ? 1 : 0;
     int local = 0;
     for (int tile = pair; tile < ntiles; tile += npairs, ++local) {
       const int acc = local & 1;
@@ -188,10 +192,11 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       tc_fence_after();
       int tm, tn;
       tile_coords(tile, g.tiles_m, g.tiles_n, G2_GROUP_M, tm, tn);
-      const int row = tm * 2 * BM + (int)rank * BM + warp * 32 + lane;
-      const int n0 = tn * G2_BN;
-      const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(acc * G2_BN);
-      epilogue_drain<G2_BN / 32>(g, taddr, row, n0);
+      const int row = tm * 2 * BM + (int)rank * BM + quarter * 32 + lane;
+      const int n0 = tn * G2_BN + half * (G2_BN / 2);
+      const uint32_t taddr =
+          tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * G2_BN + half * (G2_BN / 2));
+      epilogue_drain<G2_BN / 64>(g, taddr, row, n0);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&bars->tmem_empty[acc]), 0));

@@ -23,8 +23,7 @@ struct GemmArgs {
   // fused q/k-norm + RoPE epilogue (epi == EMK_EPI_QKNORM_ROPE_INTERNAL): output columns are heads of 128
   const __nv_bfloat16* qk_qw;
   const __nv_bfloat16* qk_kw;
-  const __nv_bfloat16* qk_cos;  // [S,128] bf16
-  const __nv_bfloat16* qk_sin;
+  const __nv_bfloat16* qk_rope;  // chunk-major cos|sin table [8][S][16] bf16 (see emk.h)
   int qk_S, qk_Hq, qk_Hkv;
   float qk_eps;
   int* status;
@@ -145,21 +144,29 @@ __device__ __forceinline__ void epilogue_store32(const GemmArgs& g, const uint32
 // the rounding steps of the eager bf16 module (normalised -> bf16, * weight -> bf16, each RoPE product -> bf16,
 // sum -> bf16); value heads are stored as they are. Thread-local: the row's 128 columns live in this thread.
 __device__ __forceinline__ void epilogue_head_qknorm_rope(const GemmArgs& g, uint32_t taddr, int row, int col0) {
-  uint32_t v[128];
-#pragma unroll
-  for (int c = 0; c < 4; ++c) tmem_ld_x32(taddr + (uint32_t)(c * 32), v + c * 32);
-  tmem_ld_wait();
-  if (row >= g.M || col0 >= g.N) return;
-  const int head = col0 >> 7;
+  // 32 columns at a time are packed to bf16 pairs as they arrive (the next load is in flight meanwhile), so the live
+  // state is the 64 packed pairs plus two 32-register load buffers.
   uint32_t n[64];
   float ss = 0.f;
+  {
+    uint32_t v[2][32];
+    tmem_ld_x32(taddr, v[0]);
 #pragma unroll
-  for (int e = 0; e < 64; ++e) {
-    n[e] = pack_bf16x2(__uint_as_float(v[2 * e]), __uint_as_float(v[2 * e + 1]));
-    const float f0 = bf16_lo(n[e]), f1 = bf16_hi(n[e]);
-    ss = fmaf(f0, f0, ss);
-    ss = fmaf(f1, f1, ss);
+    for (int c = 0; c < 4; ++c) {
+      tmem_ld_wait_regs(v[c & 1]);
+      if (c + 1 < 4) tmem_ld_x32(taddr + (uint32_t)((c + 1) * 32), v[(c + 1) & 1]);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const uint32_t pk = pack_bf16x2(__uint_as_float(v[c & 1][2 * i]), __uint_as_float(v[c & 1][2 * i + 1]));
+        const float f0 = bf16_lo(pk), f1 = bf16_hi(pk);
+        ss = fmaf(f0, f0, ss);
+        ss = fmaf(f1, f1, ss);
+        n[c * 16 + i] = pk;
+      }
+    }
   }
+  if (row >= g.M || col0 >= g.N) return;
+  const int head = col0 >> 7;
   __nv_bfloat16* out = g.y + (int64_t)row * g.ldy + col0;
   if (head < g.qk_Hq + g.qk_Hkv) {
     const float r = 1.0f / sqrtf(ss * (1.0f / 128.0f) + g.qk_eps);
@@ -176,15 +183,17 @@ __device__ __forceinline__ void epilogue_head_qknorm_rope(const GemmArgs& g, uin
         n[e] = *reinterpret_cast<const uint32_t*>(&res);
       }
     }
+    // The table is chunk-major: chunk q of position s is 32 bytes (8 cos then 8 sin values of elements 8q..8q+7;
+    // cos[i] == cos[i + 64] so the first 64 elements suffice). The lanes of a warp are consecutive rows, hence
+    // consecutive positions, so each of these loads is one contiguous kilobyte per warp.
     const int s = row % g.qk_S;
-    const __nv_bfloat16* cp = g.qk_cos + (int64_t)s * 128;  // cos[i] == cos[i + 64]: only the first half is read
-    const __nv_bfloat16* sp = g.qk_sin + (int64_t)s * 128;
+    const __nv_bfloat16* tp = g.qk_rope + (int64_t)s * 16;
 #pragma unroll
     for (int q = 0; q < 8; ++q) {
-      const uint4 cv = __ldg(reinterpret_cast<const uint4*>(cp + q * 8));
-      const uint4 sv = __ldg(reinterpret_cast<const uint4*>(sp + q * 8));
-      const uint32_t cc[4] = {cv.x, cv.y, cv.z, cv.w};
-      const uint32_t sn[4] = {sv.x, sv.y, sv.z, sv.w};
+      uint32_t cs[8];
+      ld_global_nc_v8(tp + (int64_t)q * g.qk_S * 16, cs);
+      const uint32_t* cc = cs;
+      const uint32_t* sn = cs + 4;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int e = q * 4 + j;  // pair e holds elements 2e, 2e+1; its rotate-half partner is pair e + 32

@@ -193,7 +193,7 @@ int launch_gemm(emk_handle_t h, const CUtensorMap& ta, const CUtensorMap& tb, co
 }
 
 struct QkRopeArgs {
-  const void *qw, *kw, *cosb, *sinb;
+  const void *qw, *kw, *rope;
   int S, Hq, Hkv;
   float eps;
 };
@@ -232,15 +232,14 @@ int gemm_dispatch(emk_handle_t h, const void* x, const void* w, const void* resi
   g.status = h->status_dev;
   g.limit_ns = h->wait_limit_ns;
 
-  g.qk_qw = g.qk_kw = g.qk_cos = g.qk_sin = nullptr;
+  g.qk_qw = g.qk_kw = g.qk_rope = nullptr;
   g.qk_S = g.qk_Hq = g.qk_Hkv = 0;
   g.qk_eps = 0.f;
   if (qk) {  // fused q/k-norm + RoPE epilogue: 256-column CTA-pair tiles only (two whole heads per tile)
     g.epi = EMK_EPI_QKNORM_ROPE_INTERNAL;
     g.qk_qw = (const __nv_bfloat16*)qk->qw;
     g.qk_kw = (const __nv_bfloat16*)qk->kw;
-    g.qk_cos = (const __nv_bfloat16*)qk->cosb;
-    g.qk_sin = (const __nv_bfloat16*)qk->sinb;
+    g.qk_rope = (const __nv_bfloat16*)qk->rope;
     g.qk_S = qk->S;
     g.qk_Hq = qk->Hq;
     g.qk_Hkv = qk->Hkv;
@@ -274,28 +273,16 @@ extern "C" int emk_linear_bf16(emk_handle_t h, const void* x, const void* w, con
   return gemm_dispatch(h, x, w, residual, nullptr, y, M, N, K, wlayout, epilogue, (cudaStream_t)stream);
 }
 
-extern "C" int emk_qknorm_rope(emk_handle_t h, void* qkv, const void* qw, const void* kw, const void* cosb,
-                               const void* sinb, int64_t tokens, int64_t S, int64_t Hq, int64_t Hkv, float eps,
-                               emk_stream_t stream);
-
 extern "C" int emk_linear_bf16_qknorm_rope(emk_handle_t h, const void* x, const void* w, void* y, int64_t M, int64_t N,
-                                           int64_t K, const void* qw, const void* kw, const void* cos_table,
-                                           const void* sin_table, int64_t S, int64_t Hq, int64_t Hkv, float eps,
-                                           emk_stream_t stream) {
-  if (!h || !x || !w || !y || !qw || !kw || !cos_table || !sin_table) return EMK_ERR_ARG;
+                                           int64_t K, const void* qw, const void* kw, const void* rope_chunk_major,
+                                           int64_t S, int64_t Hq, int64_t Hkv, float eps, emk_stream_t stream) {
+  if (!h || !x || !w || !y || !qw || !kw || !rope_chunk_major) return EMK_ERR_ARG;
   if (S <= 0 || Hq <= 0 || Hkv <= 0 || N != (Hq + 2 * Hkv) * 128 || M % S != 0) {
     EMK_SET_ERR(h, "emk_linear_bf16_qknorm_rope: N must be (Hq + 2*Hkv)*128 and M a multiple of S");
     return EMK_ERR_SHAPE;
   }
-  if ((((uintptr_t)qw | (uintptr_t)kw | (uintptr_t)cos_table | (uintptr_t)sin_table) & 15u) != 0 || ((uintptr_t)y & 31u))
+  if ((((uintptr_t)qw | (uintptr_t)kw) & 15u) != 0 || (((uintptr_t)y | (uintptr_t)rope_chunk_major) & 31u) != 0)
     return EMK_ERR_ALIGN;
-  cudaStream_t s = (cudaStream_t)stream;
-  if (M > BM && N > 128) {
-    QkRopeArgs qk{qw, kw, cos_table, sin_table, (int)S, (int)Hq, (int)Hkv, eps};
-    return gemm_dispatch(h, x, w, nullptr, nullptr, y, M, N, K, EMK_W_NK, EMK_EPI_NONE, s, &qk);
-  }
-  // a single row-tile: plain projection, then the stand-alone in-place kernel
-  int rc = gemm_dispatch(h, x, w, nullptr, nullptr, y, M, N, K, EMK_W_NK, EMK_EPI_NONE, s);
-  if (rc != EMK_OK) return rc;
-  return emk_qknorm_rope(h, y, qw, kw, cos_table, sin_table, M, S, Hq, Hkv, eps, stream);
+  QkRopeArgs qk{qw, kw, rope_chunk_major, (int)S, (int)Hq, (int)Hkv, eps};
+  return gemm_dispatch(h, x, w, nullptr, nullptr, y, M, N, K, EMK_W_NK, EMK_EPI_NONE, (cudaStream_t)stream, &qk);
 }

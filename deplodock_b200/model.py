@@ -11,7 +11,6 @@ Here the same dataflow is a fixed plan of seven launches per layer over a whole 
     rmsnorm -> GEMM(Wqkv) + q/k-norm + RoPE (epilogue) -> causal GQA flash attention (token-major, no transposes)
             -> GEMM(Wo) + residual -> rmsnorm -> GEMM(Wgate|Wup interleaved) + SwiGLU -> GEMM(Wdown) + residual
 
-(with 128 tokens or fewer per chunk the q/k-norm + RoPE runs as its own in-place kernel after the projection)
 
 and a last-token RMSNorm + L2 kernel. The whole forward is captured once in a CUDA graph and replayed. Sequences are
 independent, so a batch can be processed in chunks (``chunk_seqs``) whose activations stay resident in the 126 MB L2.
@@ -115,6 +114,7 @@ class EmbedForward:
             lw.wdown = w(p + "mlp.down_proj.weight")
             self.layers.append(lw)
         self.cos, self.sin = rope_tables(self.seq, c.head_dim, c.rope_theta, dev)
+        self.rope_cm = ops.rope_chunk_major(self.cos, self.sin)
 
         T = self.chunk_seqs * self.seq
         nq, nkv, D = c.num_attention_heads, c.num_key_value_heads, c.head_dim
@@ -131,7 +131,7 @@ class EmbedForward:
     @property
     def num_launches(self) -> int:
         chunks = self.batch // self.chunk_seqs
-        per_layer = self.LAUNCHES_PER_LAYER + (1 if self.chunk_seqs * self.seq <= 128 else 0)
+        per_layer = self.LAUNCHES_PER_LAYER
         return chunks * (per_layer * self.cfg.num_hidden_layers + self.LAUNCHES_FIXED)
 
     def flops(self) -> int:
@@ -146,7 +146,7 @@ class EmbedForward:
         ops.embed_gather(self.embed, ids, out=self.h)
         for lw in self.layers:
             ops.rmsnorm(self.h, lw.ln1, eps, out=self.x)
-            ops.linear_qknorm_rope(self.x, lw.wqkv, lw.qn, lw.kn, self.cos, self.sin, S, nq, nkv, eps, out=self.qkv)
+            ops.linear_qknorm_rope(self.x, lw.wqkv, lw.qn, lw.kn, self.rope_cm, S, nq, nkv, eps, out=self.qkv)
             ops.sdpa_causal_gqa_tok(self.qkv, B, S, nq, nkv, self.attn)
             ops.linear(self.attn, lw.wo, residual=self.h, out=self.h)
             ops.rmsnorm(self.h, lw.ln2, eps, out=self.x)

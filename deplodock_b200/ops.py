@@ -137,23 +137,33 @@ def linear_simt(x, w, *, residual=None, bias=None, swiglu=False, w_is_kn=False, 
                           out=out)
 
 
-def linear_qknorm_rope(x, w_qkv, q_weight, k_weight, cos, sin, S: int, Hq: int, Hkv: int, eps: float = 1e-6,
+def rope_chunk_major(cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """Re-lay bf16 cos/sin tables ``[S,128]`` as the chunk-major table ``[8,S,16]`` the fused QKV epilogue reads:
+    entry ``[q,s]`` = cos(s, 8q..8q+7) then sin(s, 8q..8q+7) of the first 64 elements (element i+64 shares the angle)."""
+    S = cos.shape[0]
+    c = cos[:, :64].reshape(S, 8, 8)
+    s_ = sin[:, :64].reshape(S, 8, 8)
+    return torch.cat([c, s_], dim=-1).permute(1, 0, 2).contiguous()
+
+
+def linear_qknorm_rope(x, w_qkv, q_weight, k_weight, rope_cm, S: int, Hq: int, Hkv: int, eps: float = 1e-6,
                        out=None) -> torch.Tensor:
     """Fused QKV projection ``x @ w_qkv.T`` with per-head q/k RMSNorm and RoPE in the GEMM epilogue; the result is the
-    token-major ``[T, (Hq+2*Hkv)*128]`` buffer the attention kernel reads."""
-    _check_cuda_contig(x, w_qkv, q_weight, k_weight, cos, sin, out)
-    if not (x.dtype == w_qkv.dtype == cos.dtype == sin.dtype == torch.bfloat16):
-        raise TypeError("linear_qknorm_rope expects bfloat16 operands and tables")
+    token-major ``[T, (Hq+2*Hkv)*128]`` buffer the attention kernel reads. ``rope_cm`` comes from
+    :func:`rope_chunk_major`."""
+    _check_cuda_contig(x, w_qkv, q_weight, k_weight, rope_cm, out)
+    if not (x.dtype == w_qkv.dtype == rope_cm.dtype == torch.bfloat16):
+        raise TypeError("linear_qknorm_rope expects bfloat16 operands and table")
     K = x.shape[-1]
     M = x.numel() // K
     N = w_qkv.shape[0]
-    if w_qkv.shape[1] != K or cos.shape[-2:] != (S, 128):
+    if w_qkv.shape[1] != K or tuple(rope_cm.shape) != (8, S, 16):
         raise ValueError("weight/table shapes do not match")
     y = torch.empty(M, N, dtype=torch.bfloat16, device=x.device) if out is None else out
     h = handle()
     h.check(h.lib.emk_linear_bf16_qknorm_rope(h.ptr, _ptr(x), _ptr(w_qkv), _ptr(y), M, N, K, _ptr(q_weight),
-                                              _ptr(k_weight), _ptr(cos), _ptr(sin), S, Hq, Hkv, float(eps),
-                                              _stream()), "emk_linear_bf16_qknorm_rope")
+                                              _ptr(k_weight), _ptr(rope_cm), S, Hq, Hkv, float(eps), _stream()),
+            "emk_linear_bf16_qknorm_rope")
     return y
 
 

@@ -113,12 +113,14 @@ int emk_sdpa_causal_gqa_bf16(emk_handle_t h, const void* q, const void* k, const
 
 /* The fused QKV projection with the q/k-norm + RoPE of emk_qknorm_rope applied in the GEMM epilogue (each thread of
  * the epilogue owns whole heads of its output row, so both are thread-local): y[M, (Hq+2*Hkv)*128] = x[M,K]·Wᵀ, then per
- * head RMSNorm(qw / kw, eps) and rotate-half RoPE with the bf16 tables [S,128] on the query and key heads; position of
- * row m is m % S. Replaces k_linear_* plus k_mean_linear_reduce_* plus the RoPE pointwise kernel of the reference's
- * lowering of the traced layer. M must be a multiple of S. */
+ * head RMSNorm(qw / kw, eps) and rotate-half RoPE on the query and key heads; position of row m is m % S.
+ * `rope_chunk_major` is the cos/sin table re-laid for coalesced reads by the epilogue (lanes = consecutive rows):
+ * bf16 [8][S][16], entry [q][s] = cos(s, 8q..8q+7) followed by sin(s, 8q..8q+7) for the first 64 elements of the
+ * head (element i + 64 uses the same angle). Replaces k_linear_* plus k_mean_linear_reduce_* plus the RoPE pointwise
+ * kernel of the reference's lowering of the traced layer. M must be a multiple of S. */
 int emk_linear_bf16_qknorm_rope(emk_handle_t h, const void* x, const void* w, void* y, int64_t M, int64_t N, int64_t K,
-                                const void* qw, const void* kw, const void* cos_table, const void* sin_table,
-                                int64_t S, int64_t Hq, int64_t Hkv, float eps, emk_stream_t stream);
+                                const void* qw, const void* kw, const void* rope_chunk_major, int64_t S, int64_t Hq,
+                                int64_t Hkv, float eps, emk_stream_t stream);
 
 /* Embedding row gather: out[t,:] = table[ids[t],:] (bf16 rows of `hidden` elements, hidden*2 a multiple of 16).
  * Replaces the GatherOp kernel of the traced trunk (emmy/compiler/trace/huggingface.py:17-186). ids are int64. */

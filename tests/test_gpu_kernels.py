@@ -345,7 +345,7 @@ def test_expired_device_wait_is_reported_and_context_survives(ops):
 
 @pytest.mark.parametrize("B,S", [(2, 40), (3, 130), (1, 512)])
 def test_linear_qknorm_rope_fused_equals_two_step(ops, B, S):
-    """The fused epilogue (taken above 128 rows) against projection + stand-alone q/k-norm+RoPE kernel, and against
+    """The fused epilogue against projection + stand-alone q/k-norm+RoPE kernel, and against
     the eager module's rounding sequence."""
     Hq, Hkv, D, K = 16, 8, 128, 256
     T = B * S
@@ -356,7 +356,8 @@ def test_linear_qknorm_rope_fused_equals_two_step(ops, B, S):
     kw = (1 + 0.1 * torch.randn(D, generator=g)).bfloat16()
     cos, sin = inputs.rope_tables(S, D, 1e6)
     cb, sb = cos.bfloat16(), sin.bfloat16()
-    fused = ops.linear_qknorm_rope(_dev(x), _dev(w), _dev(qw), _dev(kw), _dev(cb), _dev(sb), S, Hq, Hkv, 1e-6).cpu()
+    cm = ops.rope_chunk_major(_dev(cb), _dev(sb))
+    fused = ops.linear_qknorm_rope(_dev(x), _dev(w), _dev(qw), _dev(kw), cm, S, Hq, Hkv, 1e-6).cpu()
     two = ops.qknorm_rope_(ops.linear(_dev(x), _dev(w)), _dev(qw), _dev(kw), _dev(cb), _dev(sb), S, Hq, Hkv, 1e-6).cpu()
     ops.device_status()
     assert (fused != two).float().mean().item() < 0.005  # same arithmetic; only the order of the fp32 row sum differs
