@@ -259,7 +259,8 @@ def gemm_event_pass(model) -> dict:
 
     from deplodock_b200 import ops
 
-    names = ["embed_gather", "rmsnorm", "linear", "linear_qknorm_rope", "sdpa_causal_gqa_tok", "pool_norm_l2"]
+    names = ["embed_gather", "rmsnorm", "linear", "linear_qknorm_rope", "gemm_fused", "sdpa_causal_gqa_tok",
+             "pool_norm_l2"]
     originals = {n: getattr(ops, n) for n in names}
     events = []
 
@@ -270,12 +271,16 @@ def gemm_event_pass(model) -> dict:
             r = fn(*args, **kw)
             e.record()
             fam, key, fl = name, name, 0
-            if name in ("linear", "linear_qknorm_rope"):
+            if name in ("linear", "linear_qknorm_rope", "gemm_fused"):
                 x, w = args[0], args[1]
                 M = x.numel() // x.shape[-1]
                 fl = 2 * M * x.shape[-1] * w.shape[0]
-                epi = "qknorm_rope" if name != "linear" else (
-                    "residual" if kw.get("residual") is not None else ("swiglu" if kw.get("swiglu") else "none"))
+                if name == "gemm_fused":
+                    epi = kw.get("epilogue", "none") + ("+rmsnorm_in" if kw.get("row_sumsq_in") is not None else "") + (
+                        "+sumsq_out" if kw.get("row_sumsq_out") is not None else "")
+                else:
+                    epi = "qknorm_rope" if name != "linear" else (
+                        "residual" if kw.get("residual") is not None else ("swiglu" if kw.get("swiglu") else "none"))
                 key = f"{M}x{w.shape[0]}x{x.shape[-1]}+{epi}"
                 fam = "linear"
             events.append((s, e, fam, key, fl))
@@ -430,7 +435,7 @@ def main() -> None:
         gemm_tflops = gp["flops"] / (gp["ms"] * 1e-3) / 1e12
         peak = peaks["bf16_tflops_sustained"]
         roofline = {
-            "bound": "tensor", "kernel": "gemm_bf16_kernel (tcgen05, all four projections of every layer)",
+            "bound": "tensor", "kernel": "gemm2_bf16_kernel (tcgen05 cta_group::2, all four projections of every layer)",
             "achieved": round(gemm_tflops, 1), "peak": peak, "peak_source": f"{peak_src} (sustained cuBLAS bf16)",
             "unit": "TFLOP/s", "frac": round(gemm_tflops / peak, 4),
             "launches_per_step": gp["launches"], "avg_launch_us": round(gp["ms"] * 1e3 / gp["launches"], 2),

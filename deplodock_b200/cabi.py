@@ -27,7 +27,21 @@ EMK_ERR_LIMIT = 8
 
 EMK_F32, EMK_BF16, EMK_F16 = 0, 1, 2
 EMK_W_NK, EMK_W_KN = 0, 1
-EMK_EPI_NONE, EMK_EPI_RESIDUAL, EMK_EPI_SWIGLU, EMK_EPI_BIAS = 0, 1, 2, 3
+EMK_EPI_NONE, EMK_EPI_RESIDUAL, EMK_EPI_SWIGLU, EMK_EPI_BIAS, EMK_EPI_QKNORM_ROPE = 0, 1, 2, 3, 4
+
+
+class GemmDesc(ctypes.Structure):
+    """``emk_gemm_desc_t`` of ``include/emk.h``."""
+
+    _fields_ = [
+        ("x", c_void_p), ("w", c_void_p), ("residual", c_void_p), ("y", c_void_p),
+        ("M", c_int64), ("N", c_int64), ("K", c_int64),
+        ("wlayout", c_int), ("epilogue", c_int),
+        ("row_sumsq_in", c_void_p), ("norm_dim", c_int64), ("norm_eps", c_float),
+        ("row_sumsq_out", c_void_p),
+        ("q_norm_weight", c_void_p), ("k_norm_weight", c_void_p), ("rope_chunk_major", c_void_p),
+        ("seq_len", c_int64), ("num_q_heads", c_int64), ("num_kv_heads", c_int64), ("qk_eps", c_float),
+    ]
 
 
 class HungKernelError(RuntimeError):
@@ -57,6 +71,7 @@ _SIGNATURES: dict[str, list] = {
                             c_void_p],
     "emk_linear_bf16_qknorm_rope": [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p,
                                     c_void_p, c_void_p, c_int64, c_int64, c_int64, c_float, c_void_p],
+    "emk_gemm_bf16_fused": [c_void_p, c_void_p, c_void_p],
     "emk_linear_bf16_w8": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p],
     "emk_sdpa_causal_gqa_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                  c_int64, c_int64, c_float, c_void_p],
@@ -65,6 +80,7 @@ _SIGNATURES: dict[str, list] = {
     "emk_sdpa_simt": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
                       c_int64, c_float, c_int, c_int, c_void_p],
     "emk_embed_gather": [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p],
+    "emk_embed_gather_sumsq": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p],
     "emk_qknorm_rope": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                         c_int64, c_float, c_void_p],
     "emk_pool_norm_l2": [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_float, c_void_p],

@@ -26,6 +26,16 @@ struct GemmArgs {
   const __nv_bfloat16* qk_rope;  // chunk-major cos|sin table [8][S][16] bf16 (see emk.h)
   int qk_S, qk_Hq, qk_Hkv;
   float qk_eps;
+  // RMSNorm folded around the GEMM (the norm weight is folded into W by the caller):
+  //   ss_in   partial sums of squares [ss_in_segs][M] of the un-normalised input rows (one slot per 128 columns):
+  //           accumulator rows are scaled by rsqrt(sum_s ss_in[s][row] * ss_inv_dim + ss_eps) before the epilogue
+  //   ss_out  partial sums of squares [N/128][M] of the bf16 values this GEMM stores: every epilogue thread writes the
+  //           slot(s) of the columns it owns, so the buffer is fully overwritten, needs no clearing, and the sum the
+  //           consumer forms is the same on every run (no atomics)
+  const float* ss_in;
+  int ss_in_segs;
+  float ss_inv_dim, ss_eps;
+  float* ss_out;
   int* status;
   unsigned long long limit_ns;
 };
@@ -51,8 +61,8 @@ __device__ __forceinline__ float silu_f(float g) { return __fdividef(g, 1.0f + _
 
 // Epilogue for 32 accumulator columns [col0, col0+32) of one output row held by this thread. `g.wide` says rows of
 // y (and of the residual) are 32-byte aligned, so full 32-column groups move as 256-bit accesses.
-__device__ __forceinline__ void epilogue_store32(const GemmArgs& g, const uint32_t* r, int row, int col0) {
-  if (row >= g.M || col0 >= g.N) return;
+__device__ __forceinline__ float epilogue_store32(const GemmArgs& g, const uint32_t* r, int row, int col0, float rs) {
+  if (row >= g.M || col0 >= g.N) return 0.f;
   if (g.epi == EMK_EPI_SWIGLU) {
     // columns are (gate, up) pairs; 16 outputs = 32 bytes
     __nv_bfloat16* out = g.y + (int64_t)row * g.ldy + (col0 >> 1);
@@ -63,8 +73,8 @@ __device__ __forceinline__ void epilogue_store32(const GemmArgs& g, const uint32
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         const int idx = j * 4 + e * 2;
-        const float gate = bf16_round(__uint_as_float(r[idx]));
-        const float up = bf16_round(__uint_as_float(r[idx + 1]));
+        const float gate = bf16_round(__uint_as_float(r[idx]) * rs);
+        const float up = bf16_round(__uint_as_float(r[idx + 1]) * rs);
         v[e] = bf16_round(silu_f(gate)) * up;
       }
       o[j] = pack_bf16x2(v[0], v[1]);
@@ -75,12 +85,12 @@ __device__ __forceinline__ void epilogue_store32(const GemmArgs& g, const uint32
       if (col0 < g.N) *reinterpret_cast<uint4*>(out) = make_uint4(o[0], o[1], o[2], o[3]);
       if (col0 + 16 < g.N) *reinterpret_cast<uint4*>(out + 8) = make_uint4(o[4], o[5], o[6], o[7]);
     }
-    return;
+    return 0.f;
   }
   const bool full = g.wide && (col0 + 32 <= g.N);
   float v[32];
 #pragma unroll
-  for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(r[e]);
+  for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(r[e]) * rs;
   if (g.scale != nullptr) {
 #pragma unroll
     for (int q = 0; q < 8; ++q) {
@@ -126,6 +136,15 @@ __device__ __forceinline__ void epilogue_store32(const GemmArgs& g, const uint32
   uint32_t o[16];
 #pragma unroll
   for (int e = 0; e < 16; ++e) o[e] = pack_bf16x2(v[2 * e], v[2 * e + 1]);
+  float ss = 0.f;
+  if (g.ss_out != nullptr) {  // sum of squares of what is stored (columns past N hold zeros: their weights are zero-filled)
+#pragma unroll
+    for (int e = 0; e < 16; ++e) {
+      const float f0 = bf16_lo(o[e]), f1 = bf16_hi(o[e]);
+      ss = fmaf(f0, f0, ss);
+      ss = fmaf(f1, f1, ss);
+    }
+  }
   __nv_bfloat16* out = g.y + (int64_t)row * g.ldy + col0;
   if (full) {
     st_global_v8(out, o);
@@ -136,6 +155,7 @@ __device__ __forceinline__ void epilogue_store32(const GemmArgs& g, const uint32
       if (col0 + q * 8 < g.N)
         *reinterpret_cast<uint4*>(out + q * 8) = make_uint4(o[q * 4], o[q * 4 + 1], o[q * 4 + 2], o[q * 4 + 3]);
   }
+  return ss;
 }
 
 
@@ -143,7 +163,8 @@ __device__ __forceinline__ void epilogue_store32(const GemmArgs& g, const uint32
 // output would be, then for query/key heads the per-head RMSNorm and the rotate-half RoPE on packed bf16 pairs with
 // the rounding steps of the eager bf16 module (normalised -> bf16, * weight -> bf16, each RoPE product -> bf16,
 // sum -> bf16); value heads are stored as they are. Thread-local: the row's 128 columns live in this thread.
-__device__ __forceinline__ void epilogue_head_qknorm_rope(const GemmArgs& g, uint32_t taddr, int row, int col0) {
+__device__ __forceinline__ void epilogue_head_qknorm_rope(const GemmArgs& g, uint32_t taddr, int row, int col0,
+                                                          float rs) {
   // 32 columns at a time are packed to bf16 pairs as they arrive (the next load is in flight meanwhile), so the live
   // state is the 64 packed pairs plus two 32-register load buffers.
   uint32_t n[64];
@@ -157,7 +178,7 @@ __device__ __forceinline__ void epilogue_head_qknorm_rope(const GemmArgs& g, uin
       if (c + 1 < 4) tmem_ld_x32(taddr + (uint32_t)((c + 1) * 32), v[(c + 1) & 1]);
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
-        const uint32_t pk = pack_bf16x2(__uint_as_float(v[c & 1][2 * i]), __uint_as_float(v[c & 1][2 * i + 1]));
+        const uint32_t pk = pack_bf16x2(__uint_as_float(v[c & 1][2 * i]) * rs, __uint_as_float(v[c & 1][2 * i + 1]) * rs);
         const float f0 = bf16_lo(pk), f1 = bf16_hi(pk);
         ss = fmaf(f0, f0, ss);
         ss = fmaf(f1, f1, ss);
@@ -218,18 +239,36 @@ __device__ __forceinline__ void epilogue_head_qknorm_rope(const GemmArgs& g, uin
 // of chunk c+1 is in flight while chunk c is converted and stored.
 template <int NCHUNK>
 __device__ __forceinline__ void epilogue_drain(const GemmArgs& g, uint32_t taddr, int row, int n0) {
+  // row scale of a folded RMSNorm on the input side (1 when there is none)
+  float rs = 1.0f;
+  if (g.ss_in != nullptr && row < g.M) {
+    float tot = 0.f;
+    for (int sg = 0; sg < g.ss_in_segs; ++sg) tot += __ldg(g.ss_in + (int64_t)sg * g.M + row);
+    rs = 1.0f / sqrtf(tot * g.ss_inv_dim + g.ss_eps);
+  }
   if (g.epi == EMK_EPI_QKNORM_ROPE_INTERNAL) {
 #pragma unroll 1
-    for (int hd = 0; hd < NCHUNK / 4; ++hd) epilogue_head_qknorm_rope(g, taddr + (uint32_t)(hd * 128), row, n0 + hd * 128);
+    for (int hd = 0; hd < NCHUNK / 4; ++hd)
+      epilogue_head_qknorm_rope(g, taddr + (uint32_t)(hd * 128), row, n0 + hd * 128, rs);
     return;
   }
   uint32_t r[2][32];
+  float ss = 0.f;
   tmem_ld_x32(taddr, r[0]);
 #pragma unroll
   for (int c = 0; c < NCHUNK; ++c) {
     tmem_ld_wait_regs(r[c & 1]);
     if (c + 1 < NCHUNK) tmem_ld_x32(taddr + (uint32_t)((c + 1) * 32), r[(c + 1) & 1]);
-    epilogue_store32(g, r[c & 1], row, n0 + c * 32);
+    ss += epilogue_store32(g, r[c & 1], row, n0 + c * 32, rs);
+  }
+  if (g.ss_out != nullptr && row < g.M) {
+    // this thread owns columns [n0, n0 + 32*NCHUNK): its total goes to the first 128-column slot it covers, zeros to
+    // the others
+    const int slot0 = n0 >> 7;
+    const int nslots = (g.N + 127) >> 7;
+#pragma unroll
+    for (int k = 0; k < (NCHUNK * 32 + 127) / 128; ++k)
+      if (slot0 + k < nslots) g.ss_out[(int64_t)(slot0 + k) * g.M + row] = k == 0 ? ss : 0.f;
   }
 }
 

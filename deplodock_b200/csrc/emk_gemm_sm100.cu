@@ -198,9 +198,16 @@ struct QkRopeArgs {
   float eps;
 };
 
+struct RowStatArgs {
+  const float* ss_in;
+  int in_segs;
+  float inv_dim, eps;
+  float* ss_out;
+};
+
 int gemm_dispatch(emk_handle_t h, const void* x, const void* w, const void* residual, const float* scale, void* y,
                   int64_t M, int64_t N, int64_t K, int wlayout, int epilogue, cudaStream_t s,
-                  const QkRopeArgs* qk = nullptr) {
+                  const QkRopeArgs* qk = nullptr, const RowStatArgs* rsx = nullptr) {
   if (!h || !x || !w || !y) return EMK_ERR_ARG;
   if (M <= 0 || N <= 0 || K <= 0 || M > 0x7fffffff || N > 0x7fffffff || K > 0x7fffffff) return EMK_ERR_SHAPE;
   if (wlayout != EMK_W_NK && wlayout != EMK_W_KN) return EMK_ERR_ARG;
@@ -216,7 +223,7 @@ int gemm_dispatch(emk_handle_t h, const void* x, const void* w, const void* resi
     return EMK_ERR_ALIGN;
   }
   const int BN = (N > 128) ? 256 : 128;
-  GemmArgs g;
+  GemmArgs g = {};
   g.y = (__nv_bfloat16*)y;
   g.residual = (const __nv_bfloat16*)residual;
   g.scale = scale;
@@ -232,6 +239,13 @@ int gemm_dispatch(emk_handle_t h, const void* x, const void* w, const void* resi
   g.status = h->status_dev;
   g.limit_ns = h->wait_limit_ns;
 
+  if (rsx) {
+    g.ss_in = rsx->ss_in;
+    g.ss_in_segs = rsx->in_segs;
+    g.ss_inv_dim = rsx->inv_dim;
+    g.ss_eps = rsx->eps;
+    g.ss_out = rsx->ss_out;
+  }
   g.qk_qw = g.qk_kw = g.qk_rope = nullptr;
   g.qk_S = g.qk_Hq = g.qk_Hkv = 0;
   g.qk_eps = 0.f;
@@ -276,13 +290,43 @@ extern "C" int emk_linear_bf16(emk_handle_t h, const void* x, const void* w, con
 extern "C" int emk_linear_bf16_qknorm_rope(emk_handle_t h, const void* x, const void* w, void* y, int64_t M, int64_t N,
                                            int64_t K, const void* qw, const void* kw, const void* rope_chunk_major,
                                            int64_t S, int64_t Hq, int64_t Hkv, float eps, emk_stream_t stream) {
-  if (!h || !x || !w || !y || !qw || !kw || !rope_chunk_major) return EMK_ERR_ARG;
-  if (S <= 0 || Hq <= 0 || Hkv <= 0 || N != (Hq + 2 * Hkv) * 128 || M % S != 0) {
-    EMK_SET_ERR(h, "emk_linear_bf16_qknorm_rope: N must be (Hq + 2*Hkv)*128 and M a multiple of S");
-    return EMK_ERR_SHAPE;
+  emk_gemm_desc_t d;
+  memset(&d, 0, sizeof(d));
+  d.x = x; d.w = w; d.y = y; d.M = M; d.N = N; d.K = K;
+  d.wlayout = EMK_W_NK; d.epilogue = EMK_EPI_QKNORM_ROPE;
+  d.q_norm_weight = qw; d.k_norm_weight = kw; d.rope_chunk_major = rope_chunk_major;
+  d.seq_len = S; d.num_q_heads = Hq; d.num_kv_heads = Hkv; d.qk_eps = eps;
+  return emk_gemm_bf16_fused(h, &d, stream);
+}
+
+extern "C" int emk_gemm_bf16_fused(emk_handle_t h, const emk_gemm_desc_t* d, emk_stream_t stream) {
+  if (!h || !d) return EMK_ERR_ARG;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (d->row_sumsq_in && (d->norm_dim <= 0 || d->norm_dim % 128 != 0)) {
+    EMK_SET_ERR(h, "row_sumsq_in needs norm_dim > 0 and a multiple of 128 (one partial slot per 128 columns)");
+    return EMK_ERR_ARG;
   }
-  if ((((uintptr_t)qw | (uintptr_t)kw) & 15u) != 0 || (((uintptr_t)y | (uintptr_t)rope_chunk_major) & 31u) != 0)
-    return EMK_ERR_ALIGN;
-  QkRopeArgs qk{qw, kw, rope_chunk_major, (int)S, (int)Hq, (int)Hkv, eps};
-  return gemm_dispatch(h, x, w, nullptr, nullptr, y, M, N, K, EMK_W_NK, EMK_EPI_NONE, (cudaStream_t)stream, &qk);
+  RowStatArgs rs{d->row_sumsq_in, d->row_sumsq_in ? (int)(d->norm_dim / 128) : 0,
+                 d->row_sumsq_in ? 1.0f / (float)d->norm_dim : 0.f, d->norm_eps, d->row_sumsq_out};
+  const bool any_rs = d->row_sumsq_in || d->row_sumsq_out;
+  if (d->row_sumsq_out && d->epilogue != EMK_EPI_RESIDUAL && d->epilogue != EMK_EPI_NONE && d->epilogue != EMK_EPI_BIAS) {
+    EMK_SET_ERR(h, "row_sumsq_out is produced by the none / residual / bias epilogues only");
+    return EMK_ERR_ARG;
+  }
+  if (d->epilogue == EMK_EPI_QKNORM_ROPE) {
+    if (!d->x || !d->w || !d->y || !d->q_norm_weight || !d->k_norm_weight || !d->rope_chunk_major) return EMK_ERR_ARG;
+    const int64_t S = d->seq_len, Hq = d->num_q_heads, Hkv = d->num_kv_heads;
+    if (S <= 0 || Hq <= 0 || Hkv <= 0 || d->N != (Hq + 2 * Hkv) * 128 || d->M % S != 0 || d->wlayout != EMK_W_NK) {
+      EMK_SET_ERR(h, "q/k-norm + RoPE epilogue: N must be (Hq + 2*Hkv)*128, M a multiple of seq_len, W [N,K]");
+      return EMK_ERR_SHAPE;
+    }
+    if ((((uintptr_t)d->q_norm_weight | (uintptr_t)d->k_norm_weight) & 15u) != 0 ||
+        (((uintptr_t)d->y | (uintptr_t)d->rope_chunk_major) & 31u) != 0)
+      return EMK_ERR_ALIGN;
+    QkRopeArgs qk{d->q_norm_weight, d->k_norm_weight, d->rope_chunk_major, (int)S, (int)Hq, (int)Hkv, d->qk_eps};
+    return gemm_dispatch(h, d->x, d->w, nullptr, nullptr, d->y, d->M, d->N, d->K, EMK_W_NK, EMK_EPI_NONE, s, &qk,
+                         any_rs ? &rs : nullptr);
+  }
+  return gemm_dispatch(h, d->x, d->w, d->residual, nullptr, d->y, d->M, d->N, d->K, d->wlayout, d->epilogue, s, nullptr,
+                       any_rs ? &rs : nullptr);
 }

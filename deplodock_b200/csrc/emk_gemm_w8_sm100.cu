@@ -227,7 +227,7 @@ extern "C" int emk_linear_bf16_w8(emk_handle_t h, const void* x, const void* w_e
     return EMK_ERR_ALIGN;
   }
   if ((((uintptr_t)x | (uintptr_t)w_e4m3 | (uintptr_t)y | (uintptr_t)scale) & 15u) != 0) return EMK_ERR_ALIGN;
-  GemmArgs g;
+  GemmArgs g = {};
   g.y = (__nv_bfloat16*)y;
   g.residual = nullptr;
   g.scale = scale;

@@ -18,7 +18,8 @@ using namespace emk;
 // out[t,:] = table[ids[t],:]; one warp per token, 16-byte vectors.
 __global__ void __launch_bounds__(256) embed_gather_kernel(const uint4* __restrict__ table,
                                                            const int64_t* __restrict__ ids, uint4* __restrict__ out,
-                                                           int64_t tokens, int vec_per_row, int64_t vocab) {
+                                                           float* __restrict__ row_sumsq, int64_t tokens,
+                                                           int vec_per_row, int64_t vocab) {
   const int lane = threadIdx.x & 31;
   const int64_t warp = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (warp >= tokens) return;
@@ -26,7 +27,22 @@ __global__ void __launch_bounds__(256) embed_gather_kernel(const uint4* __restri
   id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);  // clamp instead of reading out of bounds
   const uint4* src = table + id * vec_per_row;
   uint4* dst = out + warp * vec_per_row;
-  for (int i = lane; i < vec_per_row; i += 32) dst[i] = __ldg(src + i);
+  float ss = 0.f;
+  for (int i = lane; i < vec_per_row; i += 32) {
+    const uint4 v = __ldg(src + i);
+    dst[i] = v;
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      ss = fmaf(bf16_lo(u[e]), bf16_lo(u[e]), ss);
+      ss = fmaf(bf16_hi(u[e]), bf16_hi(u[e]), ss);
+    }
+  }
+  if (row_sumsq != nullptr) {
+    ss = warp_sum(ss);
+    const int nslots = vec_per_row / 16;  // one slot per 128 columns; slot 0 takes the total
+    for (int k = lane; k < nslots; k += 32) row_sumsq[(int64_t)k * tokens + warp] = k == 0 ? ss : 0.f;
+  }
 }
 
 // Sixteen lanes per (token, head): a head is 128 bf16, lane j of the group owns elements 8j..8j+7 (one 16-byte
@@ -141,14 +157,23 @@ __global__ void __launch_bounds__(256) pool_norm_l2_kernel(const __nv_bfloat16* 
 
 }  // namespace
 
+extern "C" int emk_embed_gather_sumsq(emk_handle_t h, const void* table, const int64_t* ids, void* out, float* row_sumsq,
+                                      int64_t tokens, int64_t hidden, int64_t vocab, emk_stream_t stream);
+
 extern "C" int emk_embed_gather(emk_handle_t h, const void* table, const int64_t* ids, void* out, int64_t tokens,
                                 int64_t hidden, int64_t vocab, emk_stream_t stream) {
+  return emk_embed_gather_sumsq(h, table, ids, out, nullptr, tokens, hidden, vocab, stream);
+}
+
+extern "C" int emk_embed_gather_sumsq(emk_handle_t h, const void* table, const int64_t* ids, void* out, float* row_sumsq,
+                                      int64_t tokens, int64_t hidden, int64_t vocab, emk_stream_t stream) {
   if (!h || !table || !ids || !out) return EMK_ERR_ARG;
   if (tokens <= 0 || hidden <= 0 || vocab <= 0) return EMK_ERR_SHAPE;
   if ((hidden * 2) % 16 != 0 || (((uintptr_t)table | (uintptr_t)out) & 15u)) return EMK_ERR_ALIGN;
+  if (row_sumsq != nullptr && hidden % 128 != 0) return EMK_ERR_SHAPE;
   const int64_t grid = (tokens + 7) / 8;
-  embed_gather_kernel<<<(unsigned)grid, 256, 0, (cudaStream_t)stream>>>((const uint4*)table, ids, (uint4*)out, tokens,
-                                                                       (int)(hidden / 8), vocab);
+  embed_gather_kernel<<<(unsigned)grid, 256, 0, (cudaStream_t)stream>>>((const uint4*)table, ids, (uint4*)out, row_sumsq,
+                                                                       tokens, (int)(hidden / 8), vocab);
   EMK_LAUNCH_CHECK(h);
   return EMK_OK;
 }

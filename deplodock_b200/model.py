@@ -75,12 +75,16 @@ class EmbedForward:
     """Batch forward of the trunk on one GPU. ``state_dict`` uses the HF ``Qwen3Model`` parameter names."""
 
     #: kernel launches per layer / outside the layers, for launch accounting in the bench
-    LAUNCHES_PER_LAYER = 7
     LAUNCHES_FIXED = 2
 
+    @property
+    def LAUNCHES_PER_LAYER(self) -> int:
+        return 5 if self.fold_rmsnorm else 7
+
     def __init__(self, cfg, state_dict: dict[str, torch.Tensor], *, batch: int, seq: int, device=None,
-                 chunk_seqs: int | None = None) -> None:
+                 chunk_seqs: int | None = None, fold_rmsnorm: bool = True) -> None:
         self.cfg = EmbedConfig.from_any(cfg)
+        self.fold_rmsnorm = bool(fold_rmsnorm)
         c = self.cfg
         if c.head_dim != 128:
             raise ValueError("the attention kernel is built for head_dim 128")
@@ -112,6 +116,10 @@ class EmbedForward:
             # rows interleaved (gate_0, up_0, gate_1, up_1, ...) so one accumulator row holds both halves of a pair
             lw.wgu = torch.stack([gate, up], dim=1).reshape(2 * c.intermediate_size, c.hidden_size).contiguous()
             lw.wdown = w(p + "mlp.down_proj.weight")
+            if self.fold_rmsnorm:
+                # RMSNorm folded around the GEMMs: y = rsqrt(mean(h^2)+eps) * (h @ (W * w_norm)^T)
+                lw.wqkv = (lw.wqkv.float() * lw.ln1.float()[None, :]).to(bf).contiguous()
+                lw.wgu = (lw.wgu.float() * lw.ln2.float()[None, :]).to(bf).contiguous()
             self.layers.append(lw)
         self.cos, self.sin = rope_tables(self.seq, c.head_dim, c.rope_theta, dev)
         self.rope_cm = ops.rope_chunk_major(self.cos, self.sin)
@@ -125,6 +133,10 @@ class EmbedForward:
         self.attn = torch.empty(T, nq * D, dtype=bf, device=dev)
         self.mlp = torch.empty(T, c.intermediate_size, dtype=bf, device=dev)
         self.out = torch.empty(self.batch, c.hidden_size, dtype=torch.float32, device=dev)
+        # scratch of the two folded RMSNorms: partial row sums of squares, one slot per 128 hidden columns, fully
+        # overwritten by every producer (no clearing, no atomics)
+        self.ss1 = torch.zeros(c.hidden_size // 128, T, dtype=torch.float32, device=dev)
+        self.ss2 = torch.zeros(c.hidden_size // 128, T, dtype=torch.float32, device=dev)
         self._graph: torch.cuda.CUDAGraph | None = None
 
     # -----------------------------------------------------------------------------------------------------------
@@ -143,6 +155,22 @@ class EmbedForward:
         B, S = ids.shape
         nq, nkv = c.num_attention_heads, c.num_key_value_heads
         eps = c.rms_norm_eps
+        if self.fold_rmsnorm:
+            H = c.hidden_size
+            ops.embed_gather(self.embed, ids, out=self.h, row_sumsq=self.ss1)
+            for lw in self.layers:
+                ops.gemm_fused(self.h, lw.wqkv, self.qkv, epilogue="qknorm_rope", row_sumsq_in=self.ss1, norm_dim=H,
+                               norm_eps=eps, q_weight=lw.qn, k_weight=lw.kn, rope_cm=self.rope_cm, S=S, Hq=nq, Hkv=nkv,
+                               qk_eps=eps)
+                ops.sdpa_causal_gqa_tok(self.qkv, B, S, nq, nkv, self.attn)
+                ops.gemm_fused(self.attn, lw.wo, self.h, epilogue="residual", residual=self.h,
+                               row_sumsq_out=self.ss2)
+                ops.gemm_fused(self.h, lw.wgu, self.mlp, epilogue="swiglu", row_sumsq_in=self.ss2, norm_dim=H,
+                               norm_eps=eps)
+                ops.gemm_fused(self.mlp, lw.wdown, self.h, epilogue="residual", residual=self.h,
+                               row_sumsq_out=self.ss1)
+            ops.pool_norm_l2(self.h, self.final_norm, B, S, eps, out=out)
+            return
         ops.embed_gather(self.embed, ids, out=self.h)
         for lw in self.layers:
             ops.rmsnorm(self.h, lw.ln1, eps, out=self.x)

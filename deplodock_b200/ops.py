@@ -167,6 +167,42 @@ def linear_qknorm_rope(x, w_qkv, q_weight, k_weight, rope_cm, S: int, Hq: int, H
     return y
 
 
+def gemm_fused(x, w, out, *, epilogue: str = "none", residual=None, w_is_kn: bool = False, row_sumsq_in=None,
+               norm_dim: int = 0, norm_eps: float = 1e-6, row_sumsq_out=None, q_weight=None,
+               k_weight=None, rope_cm=None, S: int = 0, Hq: int = 0, Hkv: int = 0, qk_eps: float = 1e-6):
+    """``emk_gemm_bf16_fused``: the tcgen05 GEMM with an epilogue (``none | residual | bias | swiglu | qknorm_rope``)
+    and an RMSNorm folded around it through per-row partial sum-of-squares buffers ``[dim/128, M]`` fp32 (see
+    ``emk_gemm_desc_t``)."""
+    import ctypes as _ct
+
+    _check_cuda_contig(x, w, out, residual, row_sumsq_in, row_sumsq_out, q_weight, k_weight, rope_cm)
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise TypeError("gemm_fused expects bfloat16 operands")
+    for t in (row_sumsq_in, row_sumsq_out):
+        if t is not None and t.dtype != torch.float32:
+            raise TypeError("row sum-of-squares buffers are float32")
+    epi = {"none": cabi.EMK_EPI_NONE, "residual": cabi.EMK_EPI_RESIDUAL, "swiglu": cabi.EMK_EPI_SWIGLU,
+           "bias": cabi.EMK_EPI_BIAS, "qknorm_rope": cabi.EMK_EPI_QKNORM_ROPE}[epilogue]
+    K = x.shape[-1]
+    d = cabi.GemmDesc()
+    d.x, d.w, d.y = x.data_ptr(), w.data_ptr(), out.data_ptr()
+    d.residual = residual.data_ptr() if residual is not None else None
+    d.M, d.K = x.numel() // K, K
+    d.N = w.shape[1] if w_is_kn else w.shape[0]
+    d.wlayout = cabi.EMK_W_KN if w_is_kn else cabi.EMK_W_NK
+    d.epilogue = epi
+    d.row_sumsq_in = row_sumsq_in.data_ptr() if row_sumsq_in is not None else None
+    d.norm_dim, d.norm_eps = int(norm_dim), float(norm_eps)
+    d.row_sumsq_out = row_sumsq_out.data_ptr() if row_sumsq_out is not None else None
+    d.q_norm_weight = q_weight.data_ptr() if q_weight is not None else None
+    d.k_norm_weight = k_weight.data_ptr() if k_weight is not None else None
+    d.rope_chunk_major = rope_cm.data_ptr() if rope_cm is not None else None
+    d.seq_len, d.num_q_heads, d.num_kv_heads, d.qk_eps = int(S), int(Hq), int(Hkv), float(qk_eps)
+    h = handle()
+    h.check(h.lib.emk_gemm_bf16_fused(h.ptr, _ct.byref(d), _stream()), "emk_gemm_bf16_fused")
+    return out
+
+
 def linear_f32(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, w_is_kn: bool = False) -> torch.Tensor:
     """fp32 LinearOp / MatmulOp on CUDA cores (fp32 graphs have no tensor-core path)."""
     _check_cuda_contig(x, w, bias)
@@ -254,17 +290,18 @@ def sdpa_simt(q, k, v, causal: bool, scale: float | None = None) -> torch.Tensor
     return o
 
 
-def embed_gather(table: torch.Tensor, ids: torch.Tensor, out=None) -> torch.Tensor:
-    """GatherOp of the embedding table (bf16 rows) by int64 token ids."""
-    _check_cuda_contig(table, ids, out)
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, out=None, row_sumsq=None) -> torch.Tensor:
+    """GatherOp of the embedding table (bf16 rows) by int64 token ids; ``row_sumsq`` (fp32 ``[hidden/128, tokens]``)
+    optionally receives the sum of squares of every gathered row (slot 0; the other slots are zeroed)."""
+    _check_cuda_contig(table, ids, out, row_sumsq)
     if table.dtype != torch.bfloat16 or ids.dtype != torch.int64:
         raise TypeError("embed_gather expects a bfloat16 table and int64 ids")
     vocab, hidden = table.shape
     tokens = ids.numel()
     y = torch.empty(tokens, hidden, dtype=table.dtype, device=table.device) if out is None else out
     h = handle()
-    h.check(h.lib.emk_embed_gather(h.ptr, _ptr(table), _ptr(ids), _ptr(y), tokens, hidden, vocab, _stream()),
-            "emk_embed_gather")
+    h.check(h.lib.emk_embed_gather_sumsq(h.ptr, _ptr(table), _ptr(ids), _ptr(y), _ptr(row_sumsq), tokens, hidden,
+                                         vocab, _stream()), "emk_embed_gather_sumsq")
     return y
 
 

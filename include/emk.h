@@ -51,7 +51,13 @@ typedef enum { EMK_W_NK = 0, EMK_W_KN = 1 } emk_wlayout_t;
  *   EMK_EPI_RESIDUAL y = bf16(bf16(acc) + residual)          residual is [M,N] bf16
  *   EMK_EPI_SWIGLU   W rows interleaved (gate_j, up_j); y[M,N/2] = bf16(bf16(silu(g)) * u), g,u = bf16(acc)
  *   EMK_EPI_BIAS     y = bf16(acc + bias[n])                  bias is [N] bf16 passed as `residual` */
-typedef enum { EMK_EPI_NONE = 0, EMK_EPI_RESIDUAL = 1, EMK_EPI_SWIGLU = 2, EMK_EPI_BIAS = 3 } emk_epilogue_t;
+typedef enum {
+  EMK_EPI_NONE = 0,
+  EMK_EPI_RESIDUAL = 1,
+  EMK_EPI_SWIGLU = 2,
+  EMK_EPI_BIAS = 3,
+  EMK_EPI_QKNORM_ROPE = 4 /* emk_gemm_bf16_fused / emk_linear_bf16_qknorm_rope only */
+} emk_epilogue_t;
 
 typedef struct emk_handle_s* emk_handle_t;
 typedef void* emk_stream_t; /* a cudaStream_t */
@@ -122,10 +128,44 @@ int emk_linear_bf16_qknorm_rope(emk_handle_t h, const void* x, const void* w, vo
                                 const void* qw, const void* kw, const void* rope_chunk_major, int64_t S, int64_t Hq,
                                 int64_t Hkv, float eps, emk_stream_t stream);
 
+/* One descriptor for the tcgen05 GEMM with everything that can be fused around it; unused pointers are NULL.
+ * Besides the epilogues of emk_linear_bf16 it can fold an RMSNorm across two GEMMs (the reference fuses norm -> linear
+ * as k_linear_mean_reduce_* / k_mean_linear_reduce_*, emmy/compiler/pipeline/passes/loop/fusion/010_merge_loop_ops.py:131):
+ * the GEMM that PRODUCES a hidden state writes partial sums of squares of every stored row to row_sumsq_out, fp32
+ * [ceil(N/128)][M], one slot per 128 output columns (plain stores by the thread that owns the columns: no atomics, no
+ * clearing, the same bits on every run); the GEMM that CONSUMES the hidden state reads row_sumsq_in [norm_dim/128][M]
+ * and scales its accumulator rows by rsqrt(sum_s row_sumsq_in[s][m] / norm_dim + norm_eps) before its epilogue, with
+ * the norm weight folded into W by the caller (W' = W * diag(w_norm)). The sum-of-squares buffers are scratch memory
+ * owned by the caller. */
+typedef struct {
+  const void* x;        /* [M,K] bf16 */
+  const void* w;        /* [N,K] (EMK_W_NK) or [K,N] (EMK_W_KN) bf16 */
+  const void* residual; /* [M,N] (EMK_EPI_RESIDUAL) or [N] bias (EMK_EPI_BIAS) */
+  void* y;              /* [M,N] bf16, [M,N/2] for EMK_EPI_SWIGLU */
+  int64_t M, N, K;
+  int wlayout, epilogue;
+  const float* row_sumsq_in; /* fp32 [norm_dim/128][M] */
+  int64_t norm_dim;          /* multiple of 128 */
+  float norm_eps;
+  float* row_sumsq_out;      /* fp32 [ceil(N/128)][M], overwritten */
+  /* EMK_EPI_QKNORM_ROPE (see emk_linear_bf16_qknorm_rope) */
+  const void* q_norm_weight;
+  const void* k_norm_weight;
+  const void* rope_chunk_major;
+  int64_t seq_len, num_q_heads, num_kv_heads;
+  float qk_eps;
+} emk_gemm_desc_t;
+int emk_gemm_bf16_fused(emk_handle_t h, const emk_gemm_desc_t* desc, emk_stream_t stream);
+
 /* Embedding row gather: out[t,:] = table[ids[t],:] (bf16 rows of `hidden` elements, hidden*2 a multiple of 16).
  * Replaces the GatherOp kernel of the traced trunk (emmy/compiler/trace/huggingface.py:17-186). ids are int64. */
 int emk_embed_gather(emk_handle_t h, const void* table, const int64_t* ids, void* out, int64_t tokens,
                      int64_t hidden, int64_t vocab, emk_stream_t stream);
+/* Same gather that also writes the sum of squares of every gathered row in the partial layout of emk_gemm_desc_t
+ * (fp32 [hidden/128][tokens]: slot 0 holds the row's total, the other slots zero): the statistic the first folded
+ * RMSNorm of the trunk needs. hidden must be a multiple of 128. */
+int emk_embed_gather_sumsq(emk_handle_t h, const void* table, const int64_t* ids, void* out, float* row_sumsq,
+                           int64_t tokens, int64_t hidden, int64_t vocab, emk_stream_t stream);
 
 /* Same attention over token-major operands, so the fused QKV projection output can be consumed without a transpose:
  * q[(b*S+s)*ld_q + h*128 + d], likewise k, v (head index over Hkv) and o; ld_* are row pitches in elements

@@ -374,3 +374,44 @@ def test_linear_qknorm_rope_fused_equals_two_step(ops, B, S):
     ref[:, : Hq * D] = ((q * c4) + (rot(q) * s4)).reshape(T, -1)
     ref[:, Hq * D: (Hq + Hkv) * D] = ((k * c4) + (rot(k) * s4)).reshape(T, -1)
     metrics.assert_bf16_tensor_path(fused, ref, abs_tol=6e-2, what="fused qkv vs eager")
+
+
+def test_gemm_fused_row_sumsq_protocol(ops):
+    """Producer GEMM writes the partial row sums of squares of what it stores; the consumer GEMM scales its rows by
+    rsqrt(mean + eps) with the norm weight folded into W: together they equal linear -> rmsnorm -> linear with
+    stand-alone kernels. The partial buffer is overwritten, not accumulated, and the result is bitwise repeatable."""
+    M, K, H, N2 = 300, 256, 512, 768
+    g = torch.Generator().manual_seed(31)
+    x = torch.randn(M, K, generator=g).bfloat16()
+    w1 = (0.06 * torch.randn(H, K, generator=g)).bfloat16()
+    res = torch.randn(M, H, generator=g).bfloat16()
+    wn = (1 + 0.1 * torch.randn(H, generator=g)).bfloat16()
+    w2 = (0.05 * torch.randn(N2, H, generator=g)).bfloat16()
+    xd, w1d, w2d, wnd = _dev(x), _dev(w1), _dev(w2), _dev(wn)
+    ss = torch.full((H // 128, M), 123.0, dtype=torch.float32, device="cuda")  # stale contents must not matter
+    h = torch.empty(M, H, dtype=torch.bfloat16, device="cuda")
+    ops.gemm_fused(xd, w1d, h, epilogue="residual", residual=_dev(res), row_sumsq_out=ss)
+    ops.device_status()
+    want_ss = h.float().pow(2).sum(-1)
+    assert torch.allclose(ss.sum(0), want_ss, rtol=1e-4, atol=1e-3)
+    metrics.assert_bf16_tensor_path(h.cpu(), cpu_ref.linear(x, w1) + res, what="producer output")
+    w2_folded = (w2d.float() * wnd.float()[None, :]).bfloat16().contiguous()
+    y = torch.empty(M, N2, dtype=torch.bfloat16, device="cuda")
+    ops.gemm_fused(h, w2_folded, y, epilogue="none", row_sumsq_in=ss, norm_dim=H, norm_eps=1e-6)
+    two_step = ops.linear(ops.rmsnorm(h, wnd, 1e-6), w2d)
+    ops.device_status()
+    metrics.assert_bf16_tensor_path(y.cpu(), two_step.cpu(), what="folded rmsnorm vs stand-alone")
+    ref = cpu_ref.linear(cpu_ref.rmsnorm_hf(h.cpu(), wn, 1e-6), w2)
+    metrics.assert_bf16_tensor_path(y.cpu(), ref, what="folded rmsnorm vs eager")
+    y2 = torch.empty_like(y)
+    ss2 = torch.zeros_like(ss)
+    h2 = torch.empty_like(h)
+    ops.gemm_fused(xd, w1d, h2, epilogue="residual", residual=_dev(res), row_sumsq_out=ss2)
+    ops.gemm_fused(h2, w2_folded, y2, epilogue="none", row_sumsq_in=ss2, norm_dim=H, norm_eps=1e-6)
+    assert torch.equal(ss, ss2) and torch.equal(y, y2)
+    # the gather writes the same layout
+    table = torch.randn(64, H, generator=g).bfloat16()
+    ids = inputs.token_ids(2, 9, 64)
+    ssg = torch.full((H // 128, 18), -1.0, dtype=torch.float32, device="cuda")
+    rows = ops.embed_gather(_dev(table), _dev(ids), row_sumsq=ssg)
+    assert torch.allclose(ssg.sum(0), rows.float().pow(2).sum(-1), rtol=1e-5) and float(ssg[1:].abs().max()) == 0.0

@@ -37,6 +37,23 @@ def test_embed_forward_matches_eager_cpu(libemk, batch, seq, layers, chunk):
     assert not torch.equal(again, got)
 
 
+def test_folded_and_unfolded_rmsnorm_plans_agree(libemk):
+    """The plan with RMSNorm folded around the GEMMs (row sum-of-squares scratch, norm weight folded into W) against
+    the plan with stand-alone RMSNorm kernels."""
+    from deplodock_b200.model import EmbedForward
+
+    cfg = inputs.EmbedModelConfig().small(layers=3, vocab=400)
+    sd = inputs.perturb_norm_weights(inputs.embed_model_weights(cfg))
+    ids = inputs.token_ids(3, 200, cfg.vocab_size, seed=4)
+    folded = EmbedForward(cfg, sd, batch=3, seq=200, fold_rmsnorm=True)
+    a = folded(ids).cpu().clone()
+    b = EmbedForward(cfg, sd, batch=3, seq=200, fold_rmsnorm=False)(ids).cpu().clone()
+    ref = cpu_ref.embed_forward(ids, cfg, sd)
+    assert _cos(a, b).min().item() >= 0.9995
+    for got in (a, b):
+        assert _cos(got, ref).min().item() >= 0.999 and (got - ref).abs().max().item() <= 2e-2
+
+
 def test_embed_forward_vs_hf_module(libemk):
     from deplodock_b200.model import EmbedForward
 
