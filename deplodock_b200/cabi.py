@@ -72,6 +72,8 @@ _SIGNATURES: dict[str, list] = {
     "emk_linear_bf16_qknorm_rope": [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p,
                                     c_void_p, c_void_p, c_int64, c_int64, c_int64, c_float, c_void_p],
     "emk_gemm_bf16_fused": [c_void_p, c_void_p, c_void_p],
+    "emk_linear_residual_rmsnorm_bf16_noalloc": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                 c_int64, c_int64, c_int64, c_float, c_void_p],
     "emk_linear_bf16_w8": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p],
     "emk_sdpa_causal_gqa_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                  c_int64, c_int64, c_float, c_void_p],

@@ -203,6 +203,27 @@ def gemm_fused(x, w, out, *, epilogue: str = "none", residual=None, w_is_kn: boo
     return out
 
 
+def linear_residual_rmsnorm_noalloc(x, w, residual, norm_weight, eps: float = 1e-6, out_hidden=None, out_norm=None):
+    """``emk_linear_residual_rmsnorm_bf16_noalloc``: ``h = bf16(bf16(x @ w.T) + residual)`` and ``RMSNorm(h)`` with the
+    scratch between the two kernels held in a fixed array inside the library (no device allocation by the call; the
+    output tensors are the caller's). Returns ``(h, norm)``. Size limit ``M * ceil(N/128) <= 2**20``."""
+    _check_cuda_contig(x, w, residual, norm_weight, out_hidden, out_norm)
+    if not (x.dtype == w.dtype == residual.dtype == norm_weight.dtype == torch.bfloat16):
+        raise TypeError("linear_residual_rmsnorm_noalloc expects bfloat16 tensors")
+    K = x.shape[-1]
+    M = x.numel() // K
+    N = w.shape[0]
+    if w.shape[1] != K or residual.numel() != M * N or norm_weight.numel() != N:
+        raise ValueError("shapes do not match")
+    hid = torch.empty(M, N, dtype=torch.bfloat16, device=x.device) if out_hidden is None else out_hidden
+    nrm = torch.empty(M, N, dtype=torch.bfloat16, device=x.device) if out_norm is None else out_norm
+    h = handle()
+    h.check(h.lib.emk_linear_residual_rmsnorm_bf16_noalloc(h.ptr, _ptr(x), _ptr(w), _ptr(residual), _ptr(norm_weight),
+                                                           _ptr(hid), _ptr(nrm), M, N, K, float(eps), _stream()),
+            "emk_linear_residual_rmsnorm_bf16_noalloc")
+    return hid, nrm
+
+
 def linear_f32(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, w_is_kn: bool = False) -> torch.Tensor:
     """fp32 LinearOp / MatmulOp on CUDA cores (fp32 graphs have no tensor-core path)."""
     _check_cuda_contig(x, w, bias)

@@ -157,6 +157,18 @@ typedef struct {
 } emk_gemm_desc_t;
 int emk_gemm_bf16_fused(emk_handle_t h, const emk_gemm_desc_t* desc, emk_stream_t stream);
 
+/* y_hidden = bf16(bf16(x·Wᵀ) + residual) [M,N] and y_norm = RMSNorm(y_hidden; norm_weight, eps) [M,N], W [N,K], all
+ * bf16 — the "projection + residual, then norm" step of a decoder layer in one call that allocates NOTHING: the
+ * scratch between its two kernels (partial row sums of squares) is a fixed 4 MiB array inside the library, held by
+ * every GPU that loads it. For callers that cannot call cudaMalloc: plugins inside a server that owns the whole device
+ * heap, code under stream capture, latency-critical loops. Limit: M * ceil(N/128) <= 1048576, else EMK_ERR_LIMIT.
+ * All calls on a device share the array, so calls that overlap on the GPU race; nothing in it needs zeroing. The
+ * first call on a device resolves the array's address and sets kernel attributes: make it before any stream capture.
+ * This entry point has no counterpart in the reference. */
+int emk_linear_residual_rmsnorm_bf16_noalloc(emk_handle_t h, const void* x, const void* w, const void* residual,
+                                             const void* norm_weight, void* y_hidden, void* y_norm, int64_t M,
+                                             int64_t N, int64_t K, float eps, emk_stream_t stream);
+
 /* Embedding row gather: out[t,:] = table[ids[t],:] (bf16 rows of `hidden` elements, hidden*2 a multiple of 16).
  * Replaces the GatherOp kernel of the traced trunk (emmy/compiler/trace/huggingface.py:17-186). ids are int64. */
 int emk_embed_gather(emk_handle_t h, const void* table, const int64_t* ids, void* out, int64_t tokens,
