@@ -188,12 +188,13 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     for (int tile = pair; tile < ntiles; tile += npairs, ++local) {
       const int acc = local & 1;
       const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
-      if (!mbar_wait_warp(&bars->tmem_full[acc], acc_phase, wc, EMK_DEV_TIMEOUT_EPILOGUE)) break;
-      tc_fence_after();
       int tm, tn;
       tile_coords(tile, g.tiles_m, g.tiles_n, G2_GROUP_M, tm, tn);
       const int row = tm * 2 * BM + (int)rank * BM + quarter * 32 + lane;
       const int n0 = tn * G2_BN + half * (G2_BN / 2);
+      epilogue_prefetch(g, row, n0, G2_BN / 2);
+      if (!mbar_wait_warp(&bars->tmem_full[acc], acc_phase, wc, EMK_DEV_TIMEOUT_EPILOGUE)) break;
+      tc_fence_after();
       const uint32_t taddr =
           tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * G2_BN + half * (G2_BN / 2));
       epilogue_drain<G2_BN / 64>(g, taddr, row, n0);

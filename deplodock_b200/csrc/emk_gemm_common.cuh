@@ -27,9 +27,9 @@ struct GemmArgs {
   int qk_S, qk_Hq, qk_Hkv;
   float qk_eps;
   // RMSNorm folded around the GEMM (the norm weight is folded into W by the caller):
-  //   ss_in   partial sums of squares [ss_in_segs][M] of the un-normalised input rows (one slot per 128 columns):
+  //   ss_in   partial sums of squares [M][ss_in_segs] of the un-normalised input rows (one slot per 128 columns):
   //           accumulator rows are scaled by rsqrt(sum_s ss_in[s][row] * ss_inv_dim + ss_eps) before the epilogue
-  //   ss_out  partial sums of squares [N/128][M] of the bf16 values this GEMM stores: every epilogue thread writes the
+  //   ss_out  partial sums of squares [M][N/128] of the bf16 values this GEMM stores: every epilogue thread writes the
   //           slot(s) of the columns it owns, so the buffer is fully overwritten, needs no clearing, and the sum the
   //           consumer forms is the same on every run (no atomics)
   const float* ss_in;
@@ -159,6 +159,26 @@ __device__ __forceinline__ float epilogue_store32(const GemmArgs& g, const uint3
 }
 
 
+// Issued by an epilogue thread BEFORE it waits for its accumulator: everything the epilogue will read from global
+// memory for this row segment is pulled towards the SM while the tensor core is still working on the tile, so the
+// epilogue (two warps per scheduler, little latency hiding of its own) finds it in L1 / L2.
+__device__ __forceinline__ void epilogue_prefetch(const GemmArgs& g, int row, int n0, int ncols) {
+  if (row >= g.M || n0 >= g.N) return;
+  if (g.ss_in != nullptr) {
+    asm volatile("prefetch.global.L1 [%0];" ::"l"(g.ss_in + (int64_t)row * g.ss_in_segs));
+  }
+  if (g.epi == EMK_EPI_QKNORM_ROPE_INTERNAL) {
+    if ((n0 >> 7) < g.qk_Hq + g.qk_Hkv) {
+      const __nv_bfloat16* tp = g.qk_rope + (int64_t)(row % g.qk_S) * 16;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) asm volatile("prefetch.global.L1 [%0];" ::"l"(tp + (int64_t)q * g.qk_S * 16));
+    }
+  } else if (g.epi == EMK_EPI_RESIDUAL) {
+    const __nv_bfloat16* res = g.residual + (int64_t)row * g.ldy + n0;
+    for (int c = 0; c < ncols; c += 64) asm volatile("prefetch.global.L2 [%0];" ::"l"(res + c));
+  }
+}
+
 // One head (128 accumulator columns of this thread's row) of the fused QKV projection: round to bf16 as the GEMM
 // output would be, then for query/key heads the per-head RMSNorm and the rotate-half RoPE on packed bf16 pairs with
 // the rounding steps of the eager bf16 module (normalised -> bf16, * weight -> bf16, each RoPE product -> bf16,
@@ -242,8 +262,16 @@ __device__ __forceinline__ void epilogue_drain(const GemmArgs& g, uint32_t taddr
   // row scale of a folded RMSNorm on the input side (1 when there is none)
   float rs = 1.0f;
   if (g.ss_in != nullptr && row < g.M) {
+    const float* pr = g.ss_in + (int64_t)row * g.ss_in_segs;  // the row's partial sums are contiguous
     float tot = 0.f;
-    for (int sg = 0; sg < g.ss_in_segs; ++sg) tot += __ldg(g.ss_in + (int64_t)sg * g.M + row);
+    if (g.ss_in_segs == 8) {
+      uint32_t u[8];
+      ld_global_nc_v8(pr, u);
+      tot = ((__uint_as_float(u[0]) + __uint_as_float(u[1])) + (__uint_as_float(u[2]) + __uint_as_float(u[3]))) +
+            ((__uint_as_float(u[4]) + __uint_as_float(u[5])) + (__uint_as_float(u[6]) + __uint_as_float(u[7])));
+    } else {
+      for (int sg = 0; sg < g.ss_in_segs; ++sg) tot += __ldg(pr + sg);
+    }
     rs = 1.0f / sqrtf(tot * g.ss_inv_dim + g.ss_eps);
   }
   if (g.epi == EMK_EPI_QKNORM_ROPE_INTERNAL) {
@@ -268,7 +296,7 @@ __device__ __forceinline__ void epilogue_drain(const GemmArgs& g, uint32_t taddr
     const int nslots = (g.N + 127) >> 7;
 #pragma unroll
     for (int k = 0; k < (NCHUNK * 32 + 127) / 128; ++k)
-      if (slot0 + k < nslots) g.ss_out[(int64_t)(slot0 + k) * g.M + row] = k == 0 ? ss : 0.f;
+      if (slot0 + k < nslots) g.ss_out[(int64_t)row * nslots + slot0 + k] = k == 0 ? ss : 0.f;
   }
 }
 

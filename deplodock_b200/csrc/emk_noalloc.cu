@@ -28,7 +28,7 @@ namespace {
 
 using namespace emk;
 
-// y_norm[m,:] = bf16(w * bf16(h[m,:] * rsqrt(sum_s partial[s][m] / N + eps))): one warp per row, 16-byte accesses.
+// y_norm[m,:] = bf16(w * bf16(h[m,:] * rsqrt(sum_s partial[m][s] / N + eps))): one warp per row, 16-byte accesses.
 __global__ void __launch_bounds__(256) rmsnorm_from_partials_kernel(const __nv_bfloat16* __restrict__ hbuf,
                                                                     const __nv_bfloat16* __restrict__ w,
                                                                     const float* __restrict__ partial,
@@ -38,7 +38,7 @@ __global__ void __launch_bounds__(256) rmsnorm_from_partials_kernel(const __nv_b
   const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
   if (row >= M) return;
   float tot = 0.f;
-  for (int s = 0; s < nslots; ++s) tot += partial[(int64_t)s * M + row];
+  for (int s = 0; s < nslots; ++s) tot += partial[(int64_t)row * nslots + s];
   const float r = 1.0f / sqrtf(tot / (float)N + eps);
   const __nv_bfloat16* hr = hbuf + (int64_t)row * N;
   __nv_bfloat16* yr = y + (int64_t)row * N;

@@ -41,7 +41,7 @@ __global__ void __launch_bounds__(256) embed_gather_kernel(const uint4* __restri
   if (row_sumsq != nullptr) {
     ss = warp_sum(ss);
     const int nslots = vec_per_row / 16;  // one slot per 128 columns; slot 0 takes the total
-    for (int k = lane; k < nslots; k += 32) row_sumsq[(int64_t)k * tokens + warp] = k == 0 ? ss : 0.f;
+    for (int k = lane; k < nslots; k += 32) row_sumsq[warp * nslots + k] = k == 0 ? ss : 0.f;
   }
 }
 

@@ -135,8 +135,8 @@ class EmbedForward:
         self.out = torch.empty(self.batch, c.hidden_size, dtype=torch.float32, device=dev)
         # scratch of the two folded RMSNorms: partial row sums of squares, one slot per 128 hidden columns, fully
         # overwritten by every producer (no clearing, no atomics)
-        self.ss1 = torch.zeros(c.hidden_size // 128, T, dtype=torch.float32, device=dev)
-        self.ss2 = torch.zeros(c.hidden_size // 128, T, dtype=torch.float32, device=dev)
+        self.ss1 = torch.zeros(T, c.hidden_size // 128, dtype=torch.float32, device=dev)
+        self.ss2 = torch.zeros(T, c.hidden_size // 128, dtype=torch.float32, device=dev)
         self._graph: torch.cuda.CUDAGraph | None = None
 
     # -----------------------------------------------------------------------------------------------------------

@@ -171,7 +171,7 @@ def gemm_fused(x, w, out, *, epilogue: str = "none", residual=None, w_is_kn: boo
                norm_dim: int = 0, norm_eps: float = 1e-6, row_sumsq_out=None, q_weight=None,
                k_weight=None, rope_cm=None, S: int = 0, Hq: int = 0, Hkv: int = 0, qk_eps: float = 1e-6):
     """``emk_gemm_bf16_fused``: the tcgen05 GEMM with an epilogue (``none | residual | bias | swiglu | qknorm_rope``)
-    and an RMSNorm folded around it through per-row partial sum-of-squares buffers ``[dim/128, M]`` fp32 (see
+    and an RMSNorm folded around it through per-row partial sum-of-squares buffers ``[M, dim/128]`` fp32 (see
     ``emk_gemm_desc_t``)."""
     import ctypes as _ct
 
@@ -312,7 +312,7 @@ def sdpa_simt(q, k, v, causal: bool, scale: float | None = None) -> torch.Tensor
 
 
 def embed_gather(table: torch.Tensor, ids: torch.Tensor, out=None, row_sumsq=None) -> torch.Tensor:
-    """GatherOp of the embedding table (bf16 rows) by int64 token ids; ``row_sumsq`` (fp32 ``[hidden/128, tokens]``)
+    """GatherOp of the embedding table (bf16 rows) by int64 token ids; ``row_sumsq`` (fp32 ``[tokens, hidden/128]``)
     optionally receives the sum of squares of every gathered row (slot 0; the other slots are zeroed)."""
     _check_cuda_contig(table, ids, out, row_sumsq)
     if table.dtype != torch.bfloat16 or ids.dtype != torch.int64:

@@ -132,9 +132,9 @@ int emk_linear_bf16_qknorm_rope(emk_handle_t h, const void* x, const void* w, vo
  * Besides the epilogues of emk_linear_bf16 it can fold an RMSNorm across two GEMMs (the reference fuses norm -> linear
  * as k_linear_mean_reduce_* / k_mean_linear_reduce_*, emmy/compiler/pipeline/passes/loop/fusion/010_merge_loop_ops.py:131):
  * the GEMM that PRODUCES a hidden state writes partial sums of squares of every stored row to row_sumsq_out, fp32
- * [ceil(N/128)][M], one slot per 128 output columns (plain stores by the thread that owns the columns: no atomics, no
- * clearing, the same bits on every run); the GEMM that CONSUMES the hidden state reads row_sumsq_in [norm_dim/128][M]
- * and scales its accumulator rows by rsqrt(sum_s row_sumsq_in[s][m] / norm_dim + norm_eps) before its epilogue, with
+ * [M][ceil(N/128)], one slot per 128 output columns (plain stores by the thread that owns the columns: no atomics, no
+ * clearing, the same bits on every run); the GEMM that CONSUMES the hidden state reads row_sumsq_in [M][norm_dim/128]
+ * and scales its accumulator rows by rsqrt(sum_s row_sumsq_in[m][s] / norm_dim + norm_eps) before its epilogue, with
  * the norm weight folded into W by the caller (W' = W * diag(w_norm)). The sum-of-squares buffers are scratch memory
  * owned by the caller. */
 typedef struct {
@@ -144,10 +144,10 @@ typedef struct {
   void* y;              /* [M,N] bf16, [M,N/2] for EMK_EPI_SWIGLU */
   int64_t M, N, K;
   int wlayout, epilogue;
-  const float* row_sumsq_in; /* fp32 [norm_dim/128][M] */
+  const float* row_sumsq_in; /* fp32 [M][norm_dim/128] */
   int64_t norm_dim;          /* multiple of 128 */
   float norm_eps;
-  float* row_sumsq_out;      /* fp32 [ceil(N/128)][M], overwritten */
+  float* row_sumsq_out;      /* fp32 [M][ceil(N/128)], overwritten */
   /* EMK_EPI_QKNORM_ROPE (see emk_linear_bf16_qknorm_rope) */
   const void* q_norm_weight;
   const void* k_norm_weight;
@@ -174,7 +174,7 @@ int emk_linear_residual_rmsnorm_bf16_noalloc(emk_handle_t h, const void* x, cons
 int emk_embed_gather(emk_handle_t h, const void* table, const int64_t* ids, void* out, int64_t tokens,
                      int64_t hidden, int64_t vocab, emk_stream_t stream);
 /* Same gather that also writes the sum of squares of every gathered row in the partial layout of emk_gemm_desc_t
- * (fp32 [hidden/128][tokens]: slot 0 holds the row's total, the other slots zero): the statistic the first folded
+ * (fp32 [tokens][hidden/128]: slot 0 holds the row's total, the other slots zero): the statistic the first folded
  * RMSNorm of the trunk needs. hidden must be a multiple of 128. */
 int emk_embed_gather_sumsq(emk_handle_t h, const void* table, const int64_t* ids, void* out, float* row_sumsq,
                            int64_t tokens, int64_t hidden, int64_t vocab, emk_stream_t stream);

@@ -388,12 +388,12 @@ def test_gemm_fused_row_sumsq_protocol(ops):
     wn = (1 + 0.1 * torch.randn(H, generator=g)).bfloat16()
     w2 = (0.05 * torch.randn(N2, H, generator=g)).bfloat16()
     xd, w1d, w2d, wnd = _dev(x), _dev(w1), _dev(w2), _dev(wn)
-    ss = torch.full((H // 128, M), 123.0, dtype=torch.float32, device="cuda")  # stale contents must not matter
+    ss = torch.full((M, H // 128), 123.0, dtype=torch.float32, device="cuda")  # stale contents must not matter
     h = torch.empty(M, H, dtype=torch.bfloat16, device="cuda")
     ops.gemm_fused(xd, w1d, h, epilogue="residual", residual=_dev(res), row_sumsq_out=ss)
     ops.device_status()
     want_ss = h.float().pow(2).sum(-1)
-    assert torch.allclose(ss.sum(0), want_ss, rtol=1e-4, atol=1e-3)
+    assert torch.allclose(ss.sum(1), want_ss, rtol=1e-4, atol=1e-3)
     metrics.assert_bf16_tensor_path(h.cpu(), cpu_ref.linear(x, w1) + res, what="producer output")
     w2_folded = (w2d.float() * wnd.float()[None, :]).bfloat16().contiguous()
     y = torch.empty(M, N2, dtype=torch.bfloat16, device="cuda")
@@ -412,6 +412,6 @@ def test_gemm_fused_row_sumsq_protocol(ops):
     # the gather writes the same layout
     table = torch.randn(64, H, generator=g).bfloat16()
     ids = inputs.token_ids(2, 9, 64)
-    ssg = torch.full((H // 128, 18), -1.0, dtype=torch.float32, device="cuda")
+    ssg = torch.full((18, H // 128), -1.0, dtype=torch.float32, device="cuda")
     rows = ops.embed_gather(_dev(table), _dev(ids), row_sumsq=ssg)
-    assert torch.allclose(ssg.sum(0), rows.float().pow(2).sum(-1), rtol=1e-5) and float(ssg[1:].abs().max()) == 0.0
+    assert torch.allclose(ssg.sum(1), rows.float().pow(2).sum(-1), rtol=1e-5) and float(ssg[:, 1:].abs().max()) == 0.0
