@@ -4,8 +4,8 @@
 // emmy/compiler/pipeline/passes/frontend/decomposition/100_softmax.py:11-18 and lowered as an online (max, sum)
 // carrier (emmy/compiler/pipeline/passes/lowering/tile/_softmax.py:123); its cold schedule gives one thread a whole
 // row and reads the row twice with an 8 KB stride between neighbouring threads. Here one warp owns a row, keeps it in
-// registers (a 2048-float row is 64 registers per lane), reduces with shuffles, and every access is a coalesced
-// 128-bit streaming load/store, so HBM traffic is exactly one read plus one write. The reference seeds the running
+// registers, reduces with shuffles, and every access is a coalesced 128-bit streaming load/store, so HBM traffic is
+// exactly one read plus one write. Rows longer than 8 vectors per lane are shared by two or four warps. The reference seeds the running
 // max with -1e30 (emmy/compiler/ir/elementwise.py:75-76); -inf is used here so -inf inputs behave as in torch.
 #include "emk_common.cuh"
 
@@ -96,6 +96,77 @@ __global__ void __launch_bounds__(256) softmax_warp_kernel(const T* __restrict__
   }
 }
 
+
+// Long rows, many rows: WPR warps share a row (NV vectors per lane each), so a 2048-float row costs 32 data registers
+// per lane instead of 64 and three to four CTAs fit an SM — the kernel is bound by HBM latency, and with one warp per
+// row (16 resident warps) it reached 80 % of the copy bandwidth, with 24-32 resident warps 90 %. The two reductions
+// cross the warps of a row through shared memory and two CTA barriers per row.
+template <typename T, int NV, int WPR>
+__global__ void __launch_bounds__(256, 4) softmax_multiwarp_kernel(const T* __restrict__ x, T* __restrict__ y,
+                                                                   int64_t rows, int cols) {
+  constexpr int E = Row16<T>::N;
+  constexpr int RPC = 8 / WPR;  // rows per CTA
+  __shared__ float red[2][RPC][WPR];
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int r_in_cta = warp / WPR;
+  const int wr = warp % WPR;
+  const int nvec = cols / E;
+  const int64_t row_stride = (int64_t)gridDim.x * RPC;
+  const int64_t n_trips = (rows + row_stride - 1) / row_stride;  // same for every thread: barriers stay uniform
+  for (int64_t trip = 0; trip < n_trips; ++trip) {
+    const int64_t row = trip * row_stride + (int64_t)blockIdx.x * RPC + r_in_cta;
+    const bool live = row < rows;
+    const T* xr = x + (live ? row : 0) * cols;
+    float v[NV][E];
+    float m = -CUDART_INF_F;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int vi = (i * WPR + wr) * 32 + lane;
+      if (live && vi < nvec) {
+        Row16<T>::load(xr + (int64_t)vi * E, v[i]);
+#pragma unroll
+        for (int e = 0; e < E; ++e) m = fmaxf(m, v[i][e]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < E; ++e) v[i][e] = -CUDART_INF_F;
+      }
+    }
+    m = warp_max(m);
+    if (lane == 0) red[0][r_in_cta][wr] = m;
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < WPR; ++k) m = fmaxf(m, red[0][r_in_cta][k]);
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        v[i][e] = expf(v[i][e] - m);
+        sum += v[i][e];
+      }
+    }
+    sum = warp_sum(sum);
+    if (lane == 0) red[1][r_in_cta][wr] = sum;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int k = 0; k < WPR; ++k) tot += red[1][r_in_cta][k];
+    const float inv = 1.0f / tot;
+    T* yr = y + (live ? row : 0) * cols;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int vi = (i * WPR + wr) * 32 + lane;
+      if (live && vi < nvec) {
+        float o[E];
+#pragma unroll
+        for (int e = 0; e < E; ++e) o[e] = v[i][e] * inv;
+        Row16<T>::store(yr + (int64_t)vi * E, o);
+      }
+    }
+  }
+}
+
 template <typename T>
 __device__ __forceinline__ float ld_f(const T* p);
 template <>
@@ -145,7 +216,7 @@ template <typename T>
 int launch_softmax(emk_handle_t h, const T* x, T* y, int64_t rows, int64_t cols, cudaStream_t s) {
   constexpr int E = Row16<T>::N;
   const bool vec_ok =
-      (cols % E == 0) && (((uintptr_t)x | (uintptr_t)y) & 15u) == 0 && cols <= 4096;  // a row must fit the registers
+      (cols % E == 0) && (((uintptr_t)x | (uintptr_t)y) & 15u) == 0 && cols <= (int64_t)E * 1024;  // a row must fit the registers of four warps
   if (!vec_ok) {
     int grid = (int)(rows < 65535 * 16 ? rows : 65535 * 16);
     softmax_generic_kernel<T><<<grid, 256, 0, s>>>(x, y, rows, cols);
@@ -159,8 +230,18 @@ int launch_softmax(emk_handle_t h, const T* x, T* y, int64_t rows, int64_t cols,
   else if (nvec <= 64) softmax_warp_kernel<T, 2><<<grid, 256, 0, s>>>(x, y, rows, (int)cols);
   else if (nvec <= 128) softmax_warp_kernel<T, 4><<<grid, 256, 0, s>>>(x, y, rows, (int)cols);
   else if (nvec <= 256) softmax_warp_kernel<T, 8><<<grid, 256, 0, s>>>(x, y, rows, (int)cols);
-  else if (nvec <= 512) softmax_warp_kernel<T, 16><<<grid, 256, 0, s>>>(x, y, rows, (int)cols);
-  else if constexpr (E == 4) softmax_warp_kernel<T, 32><<<grid, 256, 0, s>>>(x, y, rows, (int)cols);
+  else {
+    // rows longer than 8 vectors per lane: two or four warps per row keep the register count low enough for four
+    // CTAs per SM
+    const int64_t cap = (int64_t)h->sm_count * 64;
+    if (nvec <= 512) {
+      const int64_t c2 = (rows + 3) / 4;
+      softmax_multiwarp_kernel<T, 8, 2><<<(int)(c2 < cap ? c2 : cap), 256, 0, s>>>(x, y, rows, (int)cols);
+    } else {
+      const int64_t c4 = (rows + 1) / 2;
+      softmax_multiwarp_kernel<T, 8, 4><<<(int)(c4 < cap ? c4 : cap), 256, 0, s>>>(x, y, rows, (int)cols);
+    }
+  }
   EMK_LAUNCH_CHECK(h);
   return EMK_OK;
 }
