@@ -97,6 +97,12 @@ class Graph:
             return cls.from_dict(obj.to_dict())
         raise TypeError(f"cannot build a Graph from {type(obj).__name__}")
 
+    def to_dict(self) -> dict:
+        return {"inputs": list(self.inputs), "outputs": list(self.outputs),
+                "nodes": {nid: {"op": n.op, "op_fields": dict(n.op_fields), "inputs": list(n.inputs),
+                                "output": {"name": n.output.name, "shape": list(n.output.shape),
+                                           "dtype": n.output.dtype}} for nid, n in self.nodes.items()}}
+
     # -- queries -----------------------------------------------------------------------------------------------
     def topological_order(self) -> list[str]:
         order: list[str] = []
