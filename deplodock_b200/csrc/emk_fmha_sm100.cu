@@ -28,10 +28,12 @@ using namespace emk;
 constexpr int FM = 128;   // query rows per tile
 constexpr int FN = 128;   // keys per KV block
 constexpr int HD = 128;   // head dim
-constexpr int FMHA_THREADS = 320;
+constexpr int FMHA_THREADS = 512;  // four warpgroups: softmax tile 0, softmax tile 1, epilogue, {TMA, MMA, 2 idle}
+constexpr int EPI_WARP0 = 8, TMA_WARP = 12, MMA_WARP = 13;
 constexpr int TILE_BYTES = FM * HD * 2;   // 32 KB: two 64-column halves of 16 KB
 constexpr int HALF_BYTES = FM * 64 * 2;   // 16 KB
 constexpr int KV_STAGES = 2;
+constexpr int OSTAGE_BYTES = 32 * 64 * 2;  // per softmax warp: 32 rows x 64 bf16 columns, 128-byte swizzled rows
 constexpr uint32_t IDESC_S = make_idesc_bf16(FM, FN, 0, 0);
 constexpr uint32_t IDESC_PV = make_idesc_bf16(FM, HD, 0, 1);
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
@@ -41,6 +43,7 @@ struct FmhaArgs {
   int B, Hq, Hkv, S, group, pairs;
   int nqblk;
   int n_items, n_rounds;
+  int gp;  // (batch, KV head, head pair) triples per scheduling group
   // coordinates: x = h * cs + 64 * half, y = b * rb + h * rh + s  (q side indexed by query head, kv side by KV head)
   int q_cs, q_rb, q_rh;
   int kv_cs, kv_rb, kv_rh;
@@ -52,12 +55,13 @@ struct FmhaArgs {
 };
 
 struct __align__(8) FmhaBarriers {
-  uint64_t q_full, q_empty;
+  uint64_t q_full[2], q_empty[2];   // one Q tile per query head of the item
   uint64_t k_full[KV_STAGES], v_full[KV_STAGES];
   uint64_t kv_empty[KV_STAGES];  // one K tile and one V tile per stage, released together
-  uint64_t s_full[2], p_full[2], o_done[2], o_empty[2];
+  uint64_t s_full[2], p_full[2], l_ready[2], o_done[2], o_empty[2];
   uint32_t tmem_base;
   int abort_flag;
+  float row_l[2][FM];   // row sums of the finished item, softmax warps -> epilogue warps
 };
 
 __device__ __forceinline__ float ex2_approx(float x) {
@@ -91,6 +95,14 @@ __device__ __forceinline__ unsigned long long add_f32x2(unsigned long long a, un
   return d;
 }
 
+__device__ unsigned long long g_trace[13][4096];
+template <bool TRACE>
+__device__ __forceinline__ void trace_ev(int role, uint32_t& n, int code) {
+  if constexpr (TRACE) {
+    if (blockIdx.x == 0 && n < 4096) g_trace[role][n++] = ((unsigned long long)code << 56) | (clock64() & 0xffffffffffffffull);
+  }
+}
+
 // One unit of work: 128 query rows of the (up to) two query heads `hq0`, `hq0 + 1` that share KV head `hkv`.
 struct WorkItem {
   int b, hkv, hq0, q0, nblk;
@@ -105,9 +117,15 @@ __device__ __forceinline__ int item_of_round(int round, int cta, int grid) {
 
 __device__ __forceinline__ WorkItem decode_item(const FmhaArgs& a, int w) {
   WorkItem it;
+  // (batch, KV head, head pair) triples are taken `a.gp` at a time; within such a group the query blocks go heaviest
+  // first. Items that read the same K/V blocks then run at about the same time on different SMs, so all but the
+  // first read hit in L2; with one group (small K/V) this is plain heaviest-first order.
   const int per_qblk = a.B * a.Hkv * a.pairs;
-  const int qblk = a.nqblk - 1 - w / per_qblk;
-  int rem = w % per_qblk;
+  const int g = w / (a.gp * a.nqblk);
+  const int r = w - g * a.gp * a.nqblk;
+  const int gl = min(a.gp, per_qblk - g * a.gp);
+  const int qblk = a.nqblk - 1 - r / gl;
+  int rem = g * a.gp + r % gl;
   const int pair = rem % a.pairs;
   rem /= a.pairs;
   it.hkv = rem % a.Hkv;
@@ -119,40 +137,66 @@ __device__ __forceinline__ WorkItem decode_item(const FmhaArgs& a, int w) {
   return it;
 }
 
+template <int N>
+__device__ __forceinline__ void reg_grow() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void reg_shrink() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+
+// Work items of this CTA in order: the item of the first round >= `rnd` that exists; returns false past the end.
+__device__ __forceinline__ bool next_item(const FmhaArgs& a, int& rnd, WorkItem& it) {
+  for (; rnd < a.n_rounds; ++rnd) {
+    const int w = item_of_round(rnd, (int)blockIdx.x, (int)gridDim.x);
+    if (w < a.n_items) {
+      it = decode_item(a, w);
+      return true;
+    }
+  }
+  return false;
+}
+
+template <bool TRACE>
 __global__ void __launch_bounds__(FMHA_THREADS, 1)
 fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
-                   const __grid_constant__ CUtensorMap tma_v, const FmhaArgs a) {
+                   const __grid_constant__ CUtensorMap tma_v, const __grid_constant__ CUtensorMap tma_o,
+                   const FmhaArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sQ = smem;                               // 2 tiles
   uint8_t* sK = sQ + 2 * TILE_BYTES;                // KV_STAGES tiles
   uint8_t* sV = sK + KV_STAGES * TILE_BYTES;        // KV_STAGES tiles
-  FmhaBarriers* bars = reinterpret_cast<FmhaBarriers*>(sV + KV_STAGES * TILE_BYTES);
+  uint8_t* sO = sV + KV_STAGES * TILE_BYTES;        // output staging: two 4 KB halves per epilogue warp
+  FmhaBarriers* bars = reinterpret_cast<FmhaBarriers*>(sO + 8 * OSTAGE_BYTES);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    mbar_init(&bars->q_full, 1);
-    mbar_init(&bars->q_empty, 1);
     for (int i = 0; i < KV_STAGES; ++i) {
       mbar_init(&bars->k_full[i], 1);
       mbar_init(&bars->v_full[i], 1);
       mbar_init(&bars->kv_empty[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->q_full[i], 1);
+      mbar_init(&bars->q_empty[i], 1);
       mbar_init(&bars->s_full[i], 1);
-      mbar_init(&bars->p_full[i], 4);   // one arrival per softmax warp
+      mbar_init(&bars->p_full[i], 4);   // one arrival per softmax warp of the tile
+      mbar_init(&bars->l_ready[i], 4);  // one arrival per softmax warp of the tile
       mbar_init(&bars->o_done[i], 1);
-      mbar_init(&bars->o_empty[i], 4);  // one arrival per softmax warp
+      mbar_init(&bars->o_empty[i], 4);  // one arrival per epilogue warp
     }
     bars->abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 8 && lane == 0) {
+  if (warp == TMA_WARP && lane == 0) {
     tma_prefetch_desc(&tma_q);
     tma_prefetch_desc(&tma_k);
     tma_prefetch_desc(&tma_v);
+    tma_prefetch_desc(&tma_o);
   }
   if (warp == 0) {
     tmem_alloc(&bars->tmem_base, 512);
@@ -164,35 +208,36 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
   const WaitCtx wc{&bars->abort_flag, a.status, a.limit_ns};
 
-  // The CTA is persistent: it walks its work items in a loop, and every role keeps running counters for the barrier
-  // phases, so the loads of the next item start while the current one is still in its last softmax / epilogue.
-  if (warp == 8) {
-    // ---------------- TMA producer ----------------
-    if (lane == 0) {
-      uint32_t kv_count = 0, item_i = 0;
+  // The CTA is persistent: every role walks the same list of work items with running counters for the barrier
+  // phases. Nothing drains between items: the first S of the next item is issued right behind the last PV of the
+  // current one, the softmax warps go straight on to it, and the epilogue warps write the finished O meanwhile.
+  if (warp >= TMA_WARP) {
+    reg_shrink<48>();
+    if (warp == TMA_WARP && lane == 0) {
+      // ---------------- TMA producer ----------------
+      uint32_t kv_count = 0;
+      uint32_t qn[2] = {0, 0};   // Q tiles loaded per tile slot
       bool ok = true;
-      for (int rnd = 0; rnd < a.n_rounds && ok; ++rnd) {
-        const int w = item_of_round(rnd, (int)blockIdx.x, (int)gridDim.x);
-        if (w >= a.n_items) continue;
-        const WorkItem it = decode_item(a, w);
+      WorkItem it;
+      for (int rnd = 0; ok && next_item(a, rnd, it); ++rnd) {
         const int ntile = it.two ? 2 : 1;
-        if (!mbar_wait(&bars->q_empty, (item_i & 1u) ^ 1u, wc, EMK_DEV_TIMEOUT_PRODUCER)) break;
-        mbar_arrive_expect_tx(&bars->q_full, (uint32_t)(ntile * TILE_BYTES));
-        for (int t = 0; t < ntile; ++t) {
+        for (int t = 0; t < ntile && ok; ++t) {
+          ok = mbar_wait(&bars->q_empty[t], (qn[t] & 1u) ^ 1u, wc, EMK_DEV_TIMEOUT_PRODUCER);
+          if (!ok) break;
+          ++qn[t];
           const int hq = it.hq0 + t;
           const int y = it.b * a.q_rb + hq * a.q_rh + it.q0;
-          tma_load_2d(sQ + t * TILE_BYTES, &tma_q, &bars->q_full, hq * a.q_cs, y);
-          tma_load_2d(sQ + t * TILE_BYTES + HALF_BYTES, &tma_q, &bars->q_full, hq * a.q_cs + 64, y);
+          mbar_arrive_expect_tx(&bars->q_full[t], TILE_BYTES);
+          tma_load_2d(sQ + t * TILE_BYTES, &tma_q, &bars->q_full[t], hq * a.q_cs, y);
+          tma_load_2d(sQ + t * TILE_BYTES + HALF_BYTES, &tma_q, &bars->q_full[t], hq * a.q_cs + 64, y);
         }
         const int ykv = it.b * a.kv_rb + it.hkv * a.kv_rh;
         const int xkv = it.hkv * a.kv_cs;
-        for (int j = 0; j < it.nblk; ++j, ++kv_count) {
+        for (int j = 0; j < it.nblk && ok; ++j, ++kv_count) {
           const int st = (int)(kv_count % KV_STAGES);
           const uint32_t ph = (kv_count / KV_STAGES) & 1u;
-          if (!mbar_wait(&bars->kv_empty[st], ph ^ 1u, wc, EMK_DEV_TIMEOUT_PRODUCER)) {
-            ok = false;
-            break;
-          }
+          ok = mbar_wait(&bars->kv_empty[st], ph ^ 1u, wc, EMK_DEV_TIMEOUT_PRODUCER);
+          if (!ok) break;
           mbar_arrive_expect_tx(&bars->k_full[st], TILE_BYTES);
           tma_load_2d(sK + st * TILE_BYTES, &tma_k, &bars->k_full[st], xkv, ykv + j * FN);
           tma_load_2d(sK + st * TILE_BYTES + HALF_BYTES, &tma_k, &bars->k_full[st], xkv + 64, ykv + j * FN);
@@ -200,12 +245,9 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
           tma_load_2d(sV + st * TILE_BYTES, &tma_v, &bars->v_full[st], xkv, ykv + j * FN);
           tma_load_2d(sV + st * TILE_BYTES + HALF_BYTES, &tma_v, &bars->v_full[st], xkv + 64, ykv + j * FN);
         }
-        ++item_i;
       }
-    }
-  } else if (warp == 9) {
-    // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+    } else if (warp == MMA_WARP && lane == 0) {
+      // ---------------- MMA issuer ----------------
       const uint32_t hi = smem_desc_hi(1024);
       const uint32_t q_lo = smem_desc_lo(smem_u32(sQ), 0);
       const uint32_t k_lo = smem_desc_lo(smem_u32(sK), 0);
@@ -229,32 +271,42 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
         for (int ks = 1; ks < FN / 16; ++ks)
           umma_ts_lohi(d, pa + (uint32_t)(ks * 8), va + (uint32_t)((ks * 16 * 128) >> 4), hi, IDESC_PV, 1u);
       };
-      // A tcgen05.commit stalls this thread for a few hundred cycles, so only the commits the softmax warps cannot
-      // do without are issued: one per S tile and one after the last PV of an item. "PV of block j-1 is done" is
-      // implied by the S commit of block j (a commit covers every earlier MMA of this thread); the K/V stage and the
-      // Q buffer are handed back by a softmax thread that has seen that commit.
-      uint32_t kv_count = 0, item_i = 0;
-      uint32_t iters[2] = {0, 0};   // softmax round trips per tile (parity of s_full / p_full)
-      uint32_t items[2] = {0, 0};   // items per tile (parity of o_done / o_empty)
+      // A tcgen05.commit costs this thread about a hundred cycles, so only the commits another role cannot do without
+      // are issued: one per S tile and one after the last PV of an item. "PV of block j-1 is done" is implied by the
+      // S commit of block j (a commit covers every earlier MMA of this thread).
+      uint32_t kv_count = 0;
+      uint32_t trn = 0;
+      uint32_t iters[2] = {0, 0};   // softmax round trips per tile (parity of p_full)
+      uint32_t items[2] = {0, 0};   // items per tile (parity of o_done / o_empty / q_full)
       bool ok = true;
-      for (int rnd = 0; rnd < a.n_rounds && ok; ++rnd) {
-        const int w = item_of_round(rnd, (int)blockIdx.x, (int)gridDim.x);
-        if (w >= a.n_items) continue;
-        const WorkItem it = decode_item(a, w);
+      // first S of an item for tile t: its Q tile and the K block of stage `st` must have landed
+      auto first_s = [&](int t, int st, uint32_t ph, bool wait_k) {
+        ok = mbar_wait(&bars->q_full[t], items[t] & 1u, wc, EMK_DEV_TIMEOUT_MMA);
+        if (ok && wait_k) ok = mbar_wait(&bars->k_full[st], ph, wc, EMK_DEV_TIMEOUT_MMA);
+        if (!ok) return;
+        tc_fence_after();
+        issue_s(t, st);
+        tc_commit(&bars->s_full[t]);
+        trace_ev<TRACE>(0, trn, 3);
+      };
+      WorkItem it, nx;
+      int rnd = 0;
+      bool have = next_item(a, rnd, it);
+      if (have) {
+        trace_ev<TRACE>(0, trn, 1);
+        for (int t = 0; t < (it.two ? 2 : 1) && ok; ++t) first_s(t, 0, 0u, t == 0);
+      }
+      while (have && ok) {
+        int rn = rnd + 1;
+        const bool have_next = next_item(a, rn, nx);
         const int ntile = it.two ? 2 : 1;
-        ok = mbar_wait(&bars->q_full, item_i & 1u, wc, EMK_DEV_TIMEOUT_MMA);
-        if (ok) ok = mbar_wait(&bars->k_full[kv_count % KV_STAGES], (kv_count / KV_STAGES) & 1u, wc, EMK_DEV_TIMEOUT_MMA);
-        if (!ok) break;
-        for (int t = 0; t < ntile; ++t) {
-          issue_s(t, (int)(kv_count % KV_STAGES));
-          tc_commit(&bars->s_full[t]);
-        }
+        const int ntile_next = have_next ? (nx.two ? 2 : 1) : 0;
         for (int j = 0; j < it.nblk && ok; ++j, ++kv_count) {
           const int st = (int)(kv_count % KV_STAGES);
           const uint32_t ph = (kv_count / KV_STAGES) & 1u;
           const int stn = (int)((kv_count + 1) % KV_STAGES);
           const uint32_t phn = ((kv_count + 1) / KV_STAGES) & 1u;
-          const bool has_next = (j + 1) < it.nblk;
+          const bool last = (j + 1) == it.nblk;
           for (int t = 0; t < ntile && ok; ++t) {
             ok = mbar_wait(&bars->p_full[t], iters[t] & 1u, wc, EMK_DEV_TIMEOUT_MMA);
             if (ok && t == 0) ok = mbar_wait(&bars->v_full[st], ph, wc, EMK_DEV_TIMEOUT_MMA);
@@ -262,26 +314,121 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
             if (ok && j == 0) ok = mbar_wait(&bars->o_empty[t], (items[t] & 1u) ^ 1u, wc, EMK_DEV_TIMEOUT_MMA);
             if (!ok) break;
             tc_fence_after();
+            trace_ev<TRACE>(0, trn, 4 + t * 16);
             issue_pv(t, st, j > 0);
             ++iters[t];
-            if (has_next) {
+            trace_ev<TRACE>(0, trn, 6 + t * 16);
+            if (!last) {
               if (t == 0) {
                 ok = mbar_wait(&bars->k_full[stn], phn, wc, EMK_DEV_TIMEOUT_MMA);
                 if (!ok) break;
               }
               issue_s(t, stn);
               tc_commit(&bars->s_full[t]);
+              trace_ev<TRACE>(0, trn, 8 + t * 16);
             } else {
               tc_commit(&bars->o_done[t]);
               ++items[t];
+              trace_ev<TRACE>(0, trn, 9 + t * 16);
+              // the next item starts on this tile right away (its K block sits in the other stage of the ring)
+              if (t < ntile_next) first_s(t, stn, phn, t == 0);
             }
           }
         }
-        ++item_i;
+        // a tile that sat the current item out but takes part in the next one
+        for (int t = ntile; t < ntile_next && ok; ++t)
+          first_s(t, (int)(kv_count % KV_STAGES), (kv_count / KV_STAGES) & 1u, false);
+        have = have_next;
+        it = nx;
+        rnd = rn;
+        if (have) trace_ev<TRACE>(0, trn, 1);
       }
     }
+  } else if (warp >= EPI_WARP0) {
+    // ---------------- epilogue: warp e owns rows 32e..32e+31 of both tiles ----------------
+    reg_shrink<80>();
+    const int quarter = warp & 3;
+    const int r_in_tile = quarter * 32 + lane;
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    uint8_t* stage = sO + quarter * 2 * OSTAGE_BYTES;   // two halves of 64 columns
+    const uint32_t stage_row = smem_u32(stage) + (uint32_t)(lane * 128);
+    uint32_t kv_base = 0;
+    uint32_t items[2] = {0, 0};
+    uint32_t trn = 0;
+    bool ok = true;
+    WorkItem it;
+    for (int rnd = 0; ok && next_item(a, rnd, it); ++rnd) {
+      const int ntile = it.two ? 2 : 1;
+      for (int t = 0; t < ntile && ok; ++t) {
+        const uint32_t tO = tmem_base + lane_base + 256u + (uint32_t)(t * HD);
+        ok = mbar_wait_warp(&bars->o_done[t], items[t] & 1u, wc, EMK_DEV_TIMEOUT_SOFTMAX);
+        if (ok) ok = mbar_wait_warp(&bars->l_ready[t], items[t] & 1u, wc, EMK_DEV_TIMEOUT_SOFTMAX);
+        if (!ok) break;
+        ++items[t];
+        tc_fence_after();
+        if (lane == 0) trace_ev<TRACE>(9 + quarter, trn, 6);
+        // every MMA of the item is done: the last K/V stage goes back to the producer
+        if (t == ntile - 1 && quarter == 0 && lane == 0)
+          mbar_arrive(&bars->kv_empty[(kv_base + (uint32_t)it.nblk - 1u) % KV_STAGES]);
+        const float inv = __fdividef(1.0f, bars->row_l[t][r_in_tile]);
+        const int hq = it.hq0 + t;
+        const bool full = it.q0 + FM <= a.S;
+        const int q_row = it.q0 + r_in_tile;
+        __nv_bfloat16* orow =
+            a.o + ((int64_t)it.b * a.o_rb + (int64_t)hq * a.o_rh + q_row) * a.ld_o + (int64_t)hq * a.o_cs;
+        // the stores of the previous tile out of the staging buffers must have read them
+        if (lane == 0) tma_store_wait_read();
+        __syncwarp();
+        uint32_t o[2][32];
+        tmem_ld_x32(tO, o[0]);
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {
+          tmem_ld_wait_regs(o[c & 1]);
+          if (c + 1 < HD / 32) tmem_ld_x32(tO + (uint32_t)((c + 1) * 32), o[(c + 1) & 1]);
+          if (c + 1 == HD / 32) {
+            // O is in registers: the MMA thread may overwrite it with the next item's first PV
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->o_empty[t]);
+          }
+          uint32_t v[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            v[i] = pack_bf16x2(__uint_as_float(o[c & 1][2 * i]) * inv, __uint_as_float(o[c & 1][2 * i + 1]) * inv);
+          if (full) {
+            // Full tile: 64 columns at a time leave through a 128-byte-swizzled staging buffer and one TMA store
+            // (a direct store touches 32 different lines per instruction: one row per lane).
+            const uint32_t half_base = stage_row + (uint32_t)((c >> 1) * OSTAGE_BYTES);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const uint32_t addr = half_base + (uint32_t)((((c & 1) * 4 + q) ^ (lane & 7)) * 16);
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v[4 * q]), "r"(v[4 * q + 1]),
+                           "r"(v[4 * q + 2]), "r"(v[4 * q + 3])
+                           : "memory");
+            }
+            if (c & 1) {
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                tma_store_2d(&tma_o, stage + (c >> 1) * OSTAGE_BYTES, hq * a.o_cs + (c >> 1) * 64,
+                             it.b * a.o_rb + hq * a.o_rh + it.q0 + quarter * 32);
+                tma_store_commit();
+              }
+            }
+          } else if (q_row < a.S) {
+            // ragged last tile of a sequence: rows past the end are not stored
+            st_global_v8(orow + c * 32, v);
+            st_global_v8(orow + c * 32 + 16, v + 8);
+          }
+        }
+        if (lane == 0) trace_ev<TRACE>(9 + quarter, trn, 7);
+      }
+      kv_base += (uint32_t)it.nblk;
+    }
+    if (lane == 0) tma_store_wait_all();   // output tiles still in flight
   } else {
-    // ---------------- softmax / correction / epilogue: warps 0..3 tile 0, warps 4..7 tile 1 ----------------
+    // ---------------- softmax (and the rare rescale of O): warps 0..3 tile 0, warps 4..7 tile 1 ----------------
+    reg_grow<192>();
     const int t = warp >> 2;
     const int quarter = warp & 3;
     const int r_in_tile = quarter * 32 + lane;
@@ -292,18 +439,17 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     uint32_t kv_base = 0;   // KV blocks consumed by the CTA before the current item
     uint32_t iter = 0;      // softmax round trips of this tile
     uint32_t item_n = 0;    // items this tile took part in
+    uint32_t trn = 0;
+    const bool tracer = TRACE && lane == 0;
     bool ok = true;
-    for (int rnd = 0; rnd < a.n_rounds && ok; ++rnd) {
-      const int w = item_of_round(rnd, (int)blockIdx.x, (int)gridDim.x);
-      if (w >= a.n_items) continue;
-      const WorkItem it = decode_item(a, w);
+    WorkItem it;
+    for (int rnd = 0; ok && next_item(a, rnd, it); ++rnd) {
       const int nblk = it.nblk;
       if (t == 1 && !it.two) {  // this tile sits the item out
         kv_base += (uint32_t)nblk;
         continue;
       }
       const bool last_tile = t == (it.two ? 1 : 0);  // its commits come last in the MMA thread's order
-      const int q_row = it.q0 + r_in_tile;           // position in the sequence
       float m_used = -CUDART_INF_F;
       float l = 0.f;
       for (int j = 0; j < nblk; ++j, ++iter) {
@@ -312,16 +458,18 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
           break;
         }
         tc_fence_after();
-        if (last_tile && elected) {
-          // this S commit covers the PV of block j-1 of both tiles: hand that K/V stage back; after the last S of
-          // the item the Q tiles are free as well
-          if (j > 0) mbar_arrive(&bars->kv_empty[(kv_base + (uint32_t)j - 1u) % KV_STAGES]);
-          if (j == nblk - 1) mbar_arrive(&bars->q_empty);
+        if (tracer) trace_ev<TRACE>(1 + warp, trn, 1);
+        if (elected) {
+          // the S commit of the last tile covers the PV of block j-1 of both tiles: hand that K/V stage back;
+          // after the last S of the item this tile's Q buffer is free as well
+          if (last_tile && j > 0) mbar_arrive(&bars->kv_empty[(kv_base + (uint32_t)j - 1u) % KV_STAGES]);
+          if (j == nblk - 1) mbar_arrive(&bars->q_empty[t]);
         }
         uint32_t s[FN];
 #pragma unroll
         for (int c = 0; c < FN / 32; ++c) tmem_ld_x32(tS + (uint32_t)(c * 32), s + c * 32);
         tmem_ld_wait();
+        if (tracer) trace_ev<TRACE>(1 + warp, trn, 2);
         if (j == nblk - 1) {
           // diagonal block: key index k0 + i is visible to query q_row iff k0 + i <= q_row, k0 == q0 here
 #pragma unroll
@@ -357,6 +505,7 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
           }
           m_used = m_new;
         }
+        if (tracer) trace_ev<TRACE>(1 + warp, trn, 3);
         const unsigned long long neg_m2 = pack_f32x2(-m_used, -m_used);
         const unsigned long long scale2 = pack_f32x2(a.scale_log2, a.scale_log2);
         unsigned long long sum_a = 0ull, sum_b = 0ull;  // two independent packed accumulators (4 partial sums)
@@ -384,42 +533,22 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
         tmem_st_x32(tS, p);
         tmem_st_x32(tS + 32u, p + 32);
         tmem_st_wait();
+        if (j == nblk - 1) {
+          // The row sums go to the epilogue warps. They must have finished with the previous item of this tile
+          // (its row sums and its l_ready phase), which their o_empty arrival says; it is almost always long past.
+          if (item_n > 0 && !mbar_wait_warp(&bars->o_empty[t], (item_n - 1u) & 1u, wc, EMK_DEV_TIMEOUT_SOFTMAX)) {
+            ok = false;
+            break;
+          }
+          bars->row_l[t][r_in_tile] = l;
+        }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&bars->p_full[t]);
-      }
-      if (!ok) break;
-      if (!mbar_wait_warp(&bars->o_done[t], item_n & 1u, wc, EMK_DEV_TIMEOUT_SOFTMAX)) {
-        ok = false;
-        break;
-      }
-      tc_fence_after();
-      // every MMA of the item is done: the last K/V stage goes back to the producer
-      if (last_tile && elected) mbar_arrive(&bars->kv_empty[(kv_base + (uint32_t)nblk - 1u) % KV_STAGES]);
-      const float inv = 1.0f / l;
-      const int hq = it.hq0 + t;
-      __nv_bfloat16* orow =
-          a.o + ((int64_t)it.b * a.o_rb + (int64_t)hq * a.o_rh + q_row) * a.ld_o + (int64_t)hq * a.o_cs;
-      uint32_t o[2][32];
-      tmem_ld_x32(tO, o[0]);
-#pragma unroll
-      for (int c = 0; c < HD / 32; ++c) {
-        tmem_ld_wait_regs(o[c & 1]);
-        if (c + 1 < HD / 32) tmem_ld_x32(tO + (uint32_t)((c + 1) * 32), o[(c + 1) & 1]);
-        if (c + 1 == HD / 32) {
-          // O is in registers: the MMA thread may overwrite it with the next item's first PV
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&bars->o_empty[t]);
+        if (lane == 0) {
+          mbar_arrive(&bars->p_full[t]);
+          if (j == nblk - 1) mbar_arrive(&bars->l_ready[t]);
         }
-        if (q_row < a.S) {
-          uint32_t v[16];
-#pragma unroll
-          for (int i = 0; i < 16; ++i)
-            v[i] = pack_bf16x2(__uint_as_float(o[c & 1][2 * i]) * inv, __uint_as_float(o[c & 1][2 * i + 1]) * inv);
-          st_global_v8(orow + c * 32, v);
-          st_global_v8(orow + c * 32 + 16, v + 8);
-        }
+        if (tracer) trace_ev<TRACE>(1 + warp, trn, 5);
       }
       ++item_n;
       kv_base += (uint32_t)nblk;
@@ -433,7 +562,8 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   if (warp == 0) tmem_dealloc(tmem_base, 512);
 }
 
-constexpr int FMHA_SMEM = (2 + 2 * KV_STAGES) * TILE_BYTES + 1024 + (int)sizeof(FmhaBarriers);
+constexpr int FMHA_SMEM = (2 + 2 * KV_STAGES) * TILE_BYTES + 8 * OSTAGE_BYTES + 1024 + (int)sizeof(FmhaBarriers);
+static_assert(FMHA_SMEM <= 232448, "shared memory budget");
 
 int fmha_launch(emk_handle_t h, const void* q, const void* k, const void* v, void* o, int64_t B, int64_t Hq,
                 int64_t Hkv, int64_t S, int64_t D, bool token_major, int64_t ld_q, int64_t ld_k, int64_t ld_v,
@@ -466,7 +596,7 @@ int fmha_launch(emk_handle_t h, const void* q, const void* k, const void* v, voi
   a.status = h->status_dev;
   a.limit_ns = h->wait_limit_ns;
 
-  CUtensorMap tq, tk, tv;
+  CUtensorMap tq, tk, tv, to;
   int rc;
   if (!token_major) {
     a.q_cs = 0; a.q_rb = (int)(Hq * S); a.q_rh = (int)S;
@@ -480,6 +610,9 @@ int fmha_launch(emk_handle_t h, const void* q, const void* k, const void* v, voi
                           CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
     rc = emk_make_tmap_2d(h, &tv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, v, HD, (uint64_t)(B * Hkv * S), HD * 2, 64, FN,
+                          CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    rc = emk_make_tmap_2d(h, &to, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, o, HD, (uint64_t)(B * Hq * S), HD * 2, 64, 32,
                           CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
   } else {
@@ -497,19 +630,39 @@ int fmha_launch(emk_handle_t h, const void* q, const void* k, const void* v, voi
     rc = emk_make_tmap_2d(h, &tv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, v, (uint64_t)(Hkv * HD), (uint64_t)(B * S),
                           (uint64_t)ld_v * 2, 64, FN, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
+    rc = emk_make_tmap_2d(h, &to, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, o, (uint64_t)(Hq * HD), (uint64_t)(B * S),
+                          (uint64_t)ld_o * 2, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
   }
 
   static bool configured[64] = {false};
   if (h->device < 64 && !configured[h->device]) {
-    EMK_CUDA_TRY(h, cudaFuncSetAttribute(fmha_causal_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FMHA_SMEM));
+    EMK_CUDA_TRY(h, cudaFuncSetAttribute(fmha_causal_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         FMHA_SMEM));
+    EMK_CUDA_TRY(h, cudaFuncSetAttribute(fmha_causal_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         FMHA_SMEM));
     configured[h->device] = true;
   }
+  const bool trace = getenv("EMK_FMHA_TRACE") != nullptr;
   const int64_t n_items = (int64_t)a.nqblk * B * Hkv * a.pairs;
   if (n_items > 0x7fffffffLL) return EMK_ERR_SHAPE;
   a.n_items = (int)n_items;
   const int grid = a.n_items < h->sm_count ? a.n_items : h->sm_count;  // persistent: one CTA per SM
   a.n_rounds = (a.n_items + grid - 1) / grid;
-  fmha_causal_kernel<<<(unsigned)grid, FMHA_THREADS, FMHA_SMEM, s>>>(tq, tk, tv, a);
+  {
+    // K/V that fits comfortably in L2 stays there whatever the order; otherwise about two rounds of items per group
+    const int64_t per_qblk = B * Hkv * a.pairs;
+    const int64_t kv_bytes = B * Hkv * S * HD * 2 * 2;
+    int64_t gp = per_qblk;
+    if (kv_bytes > (48ll << 20)) gp = (2ll * grid + a.nqblk - 1) / a.nqblk;
+    if (gp < 1) gp = 1;
+    if (gp > per_qblk) gp = per_qblk;
+    a.gp = (int)gp;
+  }
+  if (trace)
+    fmha_causal_kernel<true><<<(unsigned)grid, FMHA_THREADS, FMHA_SMEM, s>>>(tq, tk, tv, to, a);
+  else
+    fmha_causal_kernel<false><<<(unsigned)grid, FMHA_THREADS, FMHA_SMEM, s>>>(tq, tk, tv, to, a);
   EMK_LAUNCH_CHECK(h);
   return EMK_OK;
 }
@@ -527,4 +680,8 @@ extern "C" int emk_sdpa_causal_gqa_bf16_tok(emk_handle_t h, const void* q, const
                                             int64_t ld_k, int64_t ld_v, int64_t ld_o, float scale,
                                             emk_stream_t stream) {
   return fmha_launch(h, q, k, v, o, B, Hq, Hkv, S, D, true, ld_q, ld_k, ld_v, ld_o, scale, (cudaStream_t)stream);
+}
+
+extern "C" int emk_debug_fmha_trace(void* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, g_trace, sizeof(g_trace));
 }
