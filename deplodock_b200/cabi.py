@@ -74,7 +74,9 @@ _SIGNATURES: dict[str, list] = {
     "emk_gemm_bf16_fused": [c_void_p, c_void_p, c_void_p],
     "emk_linear_residual_rmsnorm_bf16_noalloc": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                  c_int64, c_int64, c_int64, c_float, c_void_p],
-    "emk_linear_bf16_w8": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p],
+    "emk_linear_bf16_w8": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64,
+                           c_void_p],
+    "emk_linear_bf16_w8_workspace_bytes": [c_int64, c_int64],
     "emk_sdpa_causal_gqa_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                  c_int64, c_int64, c_float, c_void_p],
     "emk_sdpa_causal_gqa_bf16_tok": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
@@ -88,7 +90,8 @@ _SIGNATURES: dict[str, list] = {
     "emk_pool_norm_l2": [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_float, c_void_p],
     "emk_selftest_wait_expiry": [c_void_p, c_int, c_void_p],
 }
-_RESTYPES = {"emk_status_string": c_char_p, "emk_last_error": c_char_p}
+_RESTYPES = {"emk_status_string": c_char_p, "emk_last_error": c_char_p,
+             "emk_linear_bf16_w8_workspace_bytes": c_int64}
 
 #: every symbol ``include/emk.h`` declares; ``tests/test_cabi_symbols.py`` checks the header against this list
 EXPORTED_SYMBOLS = tuple(_SIGNATURES)

@@ -282,6 +282,13 @@ int gemm_dispatch(emk_handle_t h, const void* x, const void* w, const void* resi
 
 }  // namespace
 
+// y = bf16(scale[n] * x·Wᵀ) with bf16 W [N,K]: the second step of the expand-then-multiply path of the e4m3 linear.
+int emk_gemm_bf16_colscale_launch(emk_handle_t h, const void* x, const void* w, const float* scale, void* y, int64_t M,
+                                  int64_t N, int64_t K, cudaStream_t s) {
+  return gemm_dispatch(h, x, w, nullptr, scale, y, M, N, K, EMK_W_NK, EMK_EPI_NONE, s);
+}
+
+
 extern "C" int emk_linear_bf16(emk_handle_t h, const void* x, const void* w, const void* residual, void* y, int64_t M,
                                int64_t N, int64_t K, int wlayout, int epilogue, emk_stream_t stream) {
   return gemm_dispatch(h, x, w, residual, nullptr, y, M, N, K, wlayout, epilogue, (cudaStream_t)stream);

@@ -46,6 +46,8 @@ __device__ __forceinline__ void cvt_e4m3x4_bf16(uint32_t w, uint32_t& lo, uint32
   hi = pack_bf16x2(f23.x, f23.y);
 }
 
+constexpr int W8_EXPAND_MIN_M = 256;  // above this many rows the weight is expanded once instead of per row tile
+
 __global__ void __launch_bounds__(W8_THREADS, 1)
 gemm_w8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_w,
                const GemmArgs g) {
@@ -213,12 +215,32 @@ epilogue_drain<W8_BN / 32>(g, taddr, row, n0);
   if (warp == 0) tmem_dealloc(tmem_base, W8_TMEM_COLS);
 }
 
+// e4m3 [rows of 16 bytes] -> bf16, exact (every e4m3 value is a bf16 value). One 16-byte load and one 32-byte store
+// per thread and step; the grid covers the SMs a few times over and strides.
+__global__ void __launch_bounds__(256) expand_e4m3_bf16_kernel(const uint4* __restrict__ src, uint32_t* __restrict__ dst,
+                                                               int64_t n16) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (int64_t)gridDim.x * blockDim.x) {
+    const uint4 v = __ldg(src + i);
+    uint32_t o[8];
+    cvt_e4m3x4_bf16(v.x, o[0], o[1]);
+    cvt_e4m3x4_bf16(v.y, o[2], o[3]);
+    cvt_e4m3x4_bf16(v.z, o[4], o[5]);
+    cvt_e4m3x4_bf16(v.w, o[6], o[7]);
+    st_global_v8(dst + i * 8, o);
+  }
+}
+
 constexpr int W8_SMEM = W8_STAGES * (A_STAGE_BYTES + W8_B_BYTES + W8_RAW_BYTES) + 1024 + (int)sizeof(W8Barriers);
 
 }  // namespace
 
+int emk_gemm_bf16_colscale_launch(emk_handle_t h, const void* x, const void* w, const float* scale, void* y, int64_t M,
+                                  int64_t N, int64_t K, cudaStream_t s);
+
+extern "C" int64_t emk_linear_bf16_w8_workspace_bytes(int64_t N, int64_t K) { return N > 0 && K > 0 ? N * K * 2 : 0; }
+
 extern "C" int emk_linear_bf16_w8(emk_handle_t h, const void* x, const void* w_e4m3, const float* scale, void* y,
-                                  int64_t M, int64_t N, int64_t K, emk_stream_t stream) {
+                                  int64_t M, int64_t N, int64_t K, void* ws, int64_t ws_bytes, emk_stream_t stream) {
   if (!h || !x || !w_e4m3 || !scale || !y) return EMK_ERR_ARG;
   if (M <= 0 || N <= 0 || K <= 0 || M > 0x7fffffff || N > 0x7fffffff || K > 0x7fffffff) return EMK_ERR_SHAPE;
   if ((K % 16) != 0 || (N % 8) != 0) {
@@ -227,6 +249,22 @@ extern "C" int emk_linear_bf16_w8(emk_handle_t h, const void* x, const void* w_e
     return EMK_ERR_ALIGN;
   }
   if ((((uintptr_t)x | (uintptr_t)w_e4m3 | (uintptr_t)y | (uintptr_t)scale) & 15u) != 0) return EMK_ERR_ALIGN;
+  if (ws != nullptr && M > W8_EXPAND_MIN_M) {
+    // Many rows: every 128-row tile would convert the same weight tile again inside its main loop (M/128 times in
+    // all). Expanding the weight once costs one pass over it at memory speed; the multiply then runs at bf16 rate.
+    if (ws_bytes < N * K * 2) {
+      EMK_SET_ERR(h, "emk_linear_bf16_w8: workspace of %lld bytes, %lld needed", (long long)ws_bytes,
+                  (long long)(N * K * 2));
+      return EMK_ERR_WORKSPACE;
+    }
+    if (((uintptr_t)ws & 31u) != 0) return EMK_ERR_ALIGN;
+    const int64_t n16 = N * K / 16;
+    int64_t blocks = (n16 + 255) / 256;
+    if (blocks > (int64_t)h->sm_count * 16) blocks = (int64_t)h->sm_count * 16;
+    expand_e4m3_bf16_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const uint4*)w_e4m3, (uint32_t*)ws, n16);
+    EMK_LAUNCH_CHECK(h);
+    return emk_gemm_bf16_colscale_launch(h, x, ws, scale, y, M, N, K, (cudaStream_t)stream);
+  }
   GemmArgs g = {};
   g.y = (__nv_bfloat16*)y;
   g.residual = nullptr;

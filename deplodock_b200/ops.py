@@ -241,8 +241,24 @@ def linear_f32(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = Non
     return y
 
 
-def linear_w8(x: torch.Tensor, w_e4m3: torch.Tensor, scale: torch.Tensor, out=None) -> torch.Tensor:
-    """bf16 activations times e4m3 weights ``[N,K]`` with one fp32 scale per output channel."""
+_W8_SCRATCH: dict[int, torch.Tensor] = {}
+
+
+def w8_scratch(device: torch.device, nbytes: int) -> torch.Tensor:
+    """One grow-only scratch buffer per device for the expanded weight of :func:`linear_w8`; it holds nothing between
+    calls, so every e4m3 layer of a model shares it (calls on different streams must not overlap)."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    buf = _W8_SCRATCH.get(idx)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _W8_SCRATCH[idx] = buf
+    return buf
+
+
+def linear_w8(x: torch.Tensor, w_e4m3: torch.Tensor, scale: torch.Tensor, out=None, workspace="auto") -> torch.Tensor:
+    """bf16 activations times e4m3 weights ``[N,K]`` with one fp32 scale per output channel. ``workspace``: "auto"
+    (shared scratch when the row count makes expanding the weight once the faster route), ``None`` (always convert
+    inside the main loop, no scratch) or a uint8 CUDA tensor of ``N * K * 2`` bytes."""
     _check_cuda_contig(x, w_e4m3, scale, out)
     if x.dtype != torch.bfloat16 or w_e4m3.dtype != torch.float8_e4m3fn or scale.dtype != torch.float32:
         raise TypeError("linear_w8 expects bfloat16 x, float8_e4m3fn weights and float32 scales")
@@ -253,7 +269,17 @@ def linear_w8(x: torch.Tensor, w_e4m3: torch.Tensor, scale: torch.Tensor, out=No
         raise ValueError("weight/scale shapes do not match x")
     y = torch.empty(*x.shape[:-1], N, dtype=torch.bfloat16, device=x.device) if out is None else out
     h = handle()
-    h.check(h.lib.emk_linear_bf16_w8(h.ptr, _ptr(x), _ptr(w_e4m3), _ptr(scale), _ptr(y), M, N, K, _stream()),
+    ws = None
+    if isinstance(workspace, str):
+        if workspace != "auto":
+            raise ValueError("workspace must be 'auto', None or a uint8 CUDA tensor")
+        if M > 256:
+            ws = w8_scratch(x.device, int(h.lib.emk_linear_bf16_w8_workspace_bytes(N, K)))
+    elif workspace is not None:
+        _check_cuda_contig(workspace)
+        ws = workspace
+    h.check(h.lib.emk_linear_bf16_w8(h.ptr, _ptr(x), _ptr(w_e4m3), _ptr(scale), _ptr(y), M, N, K, _ptr(ws),
+                                     0 if ws is None else ws.numel() * ws.element_size(), _stream()),
             "emk_linear_bf16_w8")
     return y
 

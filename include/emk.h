@@ -105,10 +105,16 @@ int emk_linear_bf16(emk_handle_t h, const void* x, const void* w, const void* re
                     int64_t N, int64_t K, int wlayout, int epilogue, emk_stream_t stream);
 
 /* Same contraction with e4m3 weights [N,K] and one fp32 scale per output channel:
- * y[m,n] = bf16( scale[n] * sum_k x[m,k] * float(Wq[n,k]) ). The weight tile is converted to bf16 inside the
- * tensor-core main loop. No counterpart kernel exists in the reference (it has no fp8 path). */
+ * y[m,n] = bf16( scale[n] * sum_k x[m,k] * float(Wq[n,k]) ). Two routes with identical arithmetic (e4m3 -> bf16 is
+ * exact, the products accumulate in fp32, the scale is applied to the accumulator): with ws == NULL, or for
+ * M <= 256, the weight tile is converted to bf16 inside the tensor-core main loop (no scratch, the weight crosses
+ * HBM as bytes); with a workspace of emk_linear_bf16_w8_workspace_bytes(N, K) bytes (32-byte aligned) and M > 256 the
+ * weight is expanded to bf16 once into ws and the bf16 tensor-core GEMM runs on it. The workspace holds nothing
+ * between calls: one buffer sized for the largest layer serves a whole model. No counterpart kernel exists in the
+ * reference (it has no fp8 path). */
 int emk_linear_bf16_w8(emk_handle_t h, const void* x, const void* w_e4m3, const float* scale, void* y, int64_t M,
-                       int64_t N, int64_t K, emk_stream_t stream);
+                       int64_t N, int64_t K, void* ws, int64_t ws_bytes, emk_stream_t stream);
+int64_t emk_linear_bf16_w8_workspace_bytes(int64_t N, int64_t K);
 
 /* Causal grouped-query attention, bf16, head_dim 128: O = softmax(Q·Kᵀ·scale + causal)·V with fp32 online softmax.
  * Replaces the emitted k_scaled_dot_product_attention kernel (SdpaOp, emmy/compiler/ir/frontend/ir.py:241-275;

@@ -215,6 +215,41 @@ def test_linear_w8_exact_dequant_incl_subnormals(ops):
     assert torch.equal(got, wq.float().t().contiguous())
 
 
+@pytest.mark.parametrize("M,K,N", [(512, 1024, 1024), (1000, 144, 264)])
+def test_linear_w8_routes_agree(ops, M, K, N):
+    """In-loop conversion and expand-once-then-multiply do the same arithmetic (exact e4m3 -> bf16, fp32
+    accumulation over k in 16-wide steps, scale on the accumulator)."""
+    x, wq, s = inputs.linear_w8_inputs(M, K, N)
+    fused = ops.linear_w8(_dev(x), _dev(wq), _dev(s), workspace=None).cpu()
+    ws = torch.empty(N * K * 2, dtype=torch.uint8, device="cuda")
+    expanded = ops.linear_w8(_dev(x), _dev(wq), _dev(s), workspace=ws).cpu()
+    ops.device_status()
+    ref = cpu_ref.linear_w8(x, wq, s)
+    metrics.assert_bf16_tensor_path(fused, ref, what="linear_w8 in-loop")
+    metrics.assert_bf16_tensor_path(expanded, ref, what="linear_w8 expanded")
+    # accumulation order over k differs between the two tensor-core kernels only in how K is chunked: allow one ulp
+    assert (fused.float() - expanded.float()).abs().max().item() <= 2.0 ** -7 * ref.float().abs().max().item()
+
+
+def test_linear_w8_expanded_exact_dequant(ops):
+    K = N = 256
+    codes = torch.arange(256, dtype=torch.uint8)
+    codes = codes[(codes & 0x7F) != 0x7F]
+    wq = codes.repeat((N * K + len(codes) - 1) // len(codes))[: N * K].reshape(N, K).view(torch.float8_e4m3fn)
+    x = torch.zeros(512, K)
+    x[:K] = torch.eye(K)
+    ws = torch.empty(N * K * 2, dtype=torch.uint8, device="cuda")
+    got = ops.linear_w8(_dev(x.bfloat16()), _dev(wq), _dev(torch.ones(N)), workspace=ws).cpu().float()
+    assert torch.equal(got[:K], wq.float().t().contiguous())
+    assert torch.count_nonzero(got[K:]) == 0
+
+
+def test_linear_w8_workspace_too_small(ops):
+    x, wq, s = inputs.linear_w8_inputs(512, 64, 64)
+    with pytest.raises(ValueError, match="workspace"):
+        ops.linear_w8(_dev(x), _dev(wq), _dev(s), workspace=torch.empty(64, dtype=torch.uint8, device="cuda"))
+
+
 # ------------------------------------------------------------------------------------------------------------
 # Attention
 # ------------------------------------------------------------------------------------------------------------
