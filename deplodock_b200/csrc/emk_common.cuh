@@ -191,6 +191,12 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
+// Ask for a 2-D tile to be brought into L2 (no shared-memory destination, nothing to wait for).
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* m, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(reinterpret_cast<uint64_t>(m)), "r"(x),
+               "r"(y)
+               : "memory");
+}
 // 2-D tile store shared -> global (bulk async group of the issuing thread). Rows and columns outside the tensor are
 // clipped by the hardware; x * element size must be a multiple of 16 bytes and no coordinate may be negative.
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, const void* smem_src, int x, int y) {

@@ -6,16 +6,25 @@
 // (emmy/compiler/pipeline/passes/lowering/kernel/_twist.py:229) that re-reads Q and K fragments from global memory
 // every 16 keys, never skips masked tiles and does not share K/V between the query heads of a group.
 //
-// Here one CTA owns 128 query rows of TWO query heads that share a KV head (two 128x128 tiles, "ping-pong"):
-//   warps 0..3  softmax of tile 0 (thread = query row: no shuffles for row max / row sum)
-//   warps 4..7  softmax of tile 1
-//   warp 8      TMA producer: Q once, then a 2-slot ring of K tiles and a 2-slot ring of V tiles
-//   warp 9      MMA issuer: S = Q·Kᵀ (both operands from shared memory) and O += P·V (P from tensor memory,
-//               V from shared memory as an MN-major operand)
+// Here one persistent CTA per SM walks a list of work items; an item is 128 query rows of TWO query heads that share
+// a KV head (two 128x128 tiles, "ping-pong"). Four warpgroups, registers moved between them with setmaxnreg:
+//   warps 0..3   softmax of tile 0 (thread = query row: no shuffles for row max / row sum), 192 registers
+//   warps 4..7   softmax of tile 1
+//   warps 8..11  epilogue of both tiles: O / row sum -> bf16 -> 128-byte-swizzled staging -> TMA store, so the
+//                softmax warps go straight on to the next item
+//   warp 12      TMA producer: one Q tile per head (own barriers, so a head's Q is replaced as soon as its last S is
+//                done), then a 2-slot ring of K tiles and a 2-slot ring of V tiles
+//   warp 13      MMA issuer: S = Q·Kᵀ (both operands from shared memory) and O += P·V (P from tensor memory,
+//                V from shared memory as an MN-major operand); the first S of the next item is issued right behind
+//                the last PV of the current one, so the pipeline does not drain between items
 // Tensor memory (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each; the bf16 probabilities P overwrite the
 // first 64 columns of their S tile. While the tensor core works on one tile the softmax warps work on the other.
-// Only KV blocks at or below the diagonal are visited, heavy query blocks are scheduled first, and O is rescaled
+// Only KV blocks at or below the diagonal are visited; items are ordered so that the query blocks that read the same
+// K/V run at about the same time (L2 reuse) and every CTA gets about the same number of KV blocks; O is rescaled
 // lazily (only when the running max grows by more than 2^8), so most iterations never touch O.
+// Measured dead ends, kept out: two threads per query row (the two warps share a scheduler, 2x slower); blocks of 64
+// keys with two S buffers per tile (N=64 MMAs and the doubled per-block overheads, 1.6x slower); polynomial exp2 on
+// the FMA pipe for part of the row (no gain: issue slots, not the MUFU pipe, bound the row pass).
 // Every mbarrier wait is bounded; after an expiry all roles fall through to the common teardown.
 #include "emk_common.cuh"
 
@@ -95,14 +104,6 @@ __device__ __forceinline__ unsigned long long add_f32x2(unsigned long long a, un
   return d;
 }
 
-__device__ unsigned long long g_trace[13][4096];
-template <bool TRACE>
-__device__ __forceinline__ void trace_ev(int role, uint32_t& n, int code) {
-  if constexpr (TRACE) {
-    if (blockIdx.x == 0 && n < 4096) g_trace[role][n++] = ((unsigned long long)code << 56) | (clock64() & 0xffffffffffffffull);
-  }
-}
-
 // One unit of work: 128 query rows of the (up to) two query heads `hq0`, `hq0 + 1` that share KV head `hkv`.
 struct WorkItem {
   int b, hkv, hq0, q0, nblk;
@@ -158,7 +159,6 @@ __device__ __forceinline__ bool next_item(const FmhaArgs& a, int& rnd, WorkItem&
   return false;
 }
 
-template <bool TRACE>
 __global__ void __launch_bounds__(FMHA_THREADS, 1)
 fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
                    const __grid_constant__ CUtensorMap tma_v, const __grid_constant__ CUtensorMap tma_o,
@@ -275,7 +275,6 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
       // are issued: one per S tile and one after the last PV of an item. "PV of block j-1 is done" is implied by the
       // S commit of block j (a commit covers every earlier MMA of this thread).
       uint32_t kv_count = 0;
-      uint32_t trn = 0;
       uint32_t iters[2] = {0, 0};   // softmax round trips per tile (parity of p_full)
       uint32_t items[2] = {0, 0};   // items per tile (parity of o_done / o_empty / q_full)
       bool ok = true;
@@ -287,13 +286,11 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
         tc_fence_after();
         issue_s(t, st);
         tc_commit(&bars->s_full[t]);
-        trace_ev<TRACE>(0, trn, 3);
       };
       WorkItem it, nx;
       int rnd = 0;
       bool have = next_item(a, rnd, it);
       if (have) {
-        trace_ev<TRACE>(0, trn, 1);
         for (int t = 0; t < (it.two ? 2 : 1) && ok; ++t) first_s(t, 0, 0u, t == 0);
       }
       while (have && ok) {
@@ -314,10 +311,8 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
             if (ok && j == 0) ok = mbar_wait(&bars->o_empty[t], (items[t] & 1u) ^ 1u, wc, EMK_DEV_TIMEOUT_MMA);
             if (!ok) break;
             tc_fence_after();
-            trace_ev<TRACE>(0, trn, 4 + t * 16);
             issue_pv(t, st, j > 0);
             ++iters[t];
-            trace_ev<TRACE>(0, trn, 6 + t * 16);
             if (!last) {
               if (t == 0) {
                 ok = mbar_wait(&bars->k_full[stn], phn, wc, EMK_DEV_TIMEOUT_MMA);
@@ -325,11 +320,9 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
               }
               issue_s(t, stn);
               tc_commit(&bars->s_full[t]);
-              trace_ev<TRACE>(0, trn, 8 + t * 16);
             } else {
               tc_commit(&bars->o_done[t]);
               ++items[t];
-              trace_ev<TRACE>(0, trn, 9 + t * 16);
               // the next item starts on this tile right away (its K block sits in the other stage of the ring)
               if (t < ntile_next) first_s(t, stn, phn, t == 0);
             }
@@ -341,7 +334,6 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
         have = have_next;
         it = nx;
         rnd = rn;
-        if (have) trace_ev<TRACE>(0, trn, 1);
       }
     }
   } else if (warp >= EPI_WARP0) {
@@ -354,7 +346,6 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     const uint32_t stage_row = smem_u32(stage) + (uint32_t)(lane * 128);
     uint32_t kv_base = 0;
     uint32_t items[2] = {0, 0};
-    uint32_t trn = 0;
     bool ok = true;
     WorkItem it;
     for (int rnd = 0; ok && next_item(a, rnd, it); ++rnd) {
@@ -366,7 +357,6 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
         if (!ok) break;
         ++items[t];
         tc_fence_after();
-        if (lane == 0) trace_ev<TRACE>(9 + quarter, trn, 6);
         // every MMA of the item is done: the last K/V stage goes back to the producer
         if (t == ntile - 1 && quarter == 0 && lane == 0)
           mbar_arrive(&bars->kv_empty[(kv_base + (uint32_t)it.nblk - 1u) % KV_STAGES]);
@@ -421,7 +411,6 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
             st_global_v8(orow + c * 32 + 16, v + 8);
           }
         }
-        if (lane == 0) trace_ev<TRACE>(9 + quarter, trn, 7);
       }
       kv_base += (uint32_t)it.nblk;
     }
@@ -439,8 +428,6 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     uint32_t kv_base = 0;   // KV blocks consumed by the CTA before the current item
     uint32_t iter = 0;      // softmax round trips of this tile
     uint32_t item_n = 0;    // items this tile took part in
-    uint32_t trn = 0;
-    const bool tracer = TRACE && lane == 0;
     bool ok = true;
     WorkItem it;
     for (int rnd = 0; ok && next_item(a, rnd, it); ++rnd) {
@@ -458,7 +445,6 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
           break;
         }
         tc_fence_after();
-        if (tracer) trace_ev<TRACE>(1 + warp, trn, 1);
         if (elected) {
           // the S commit of the last tile covers the PV of block j-1 of both tiles: hand that K/V stage back;
           // after the last S of the item this tile's Q buffer is free as well
@@ -469,7 +455,6 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
 #pragma unroll
         for (int c = 0; c < FN / 32; ++c) tmem_ld_x32(tS + (uint32_t)(c * 32), s + c * 32);
         tmem_ld_wait();
-        if (tracer) trace_ev<TRACE>(1 + warp, trn, 2);
         if (j == nblk - 1) {
           // diagonal block: key index k0 + i is visible to query q_row iff k0 + i <= q_row, k0 == q0 here
 #pragma unroll
@@ -505,7 +490,6 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
           }
           m_used = m_new;
         }
-        if (tracer) trace_ev<TRACE>(1 + warp, trn, 3);
         const unsigned long long neg_m2 = pack_f32x2(-m_used, -m_used);
         const unsigned long long scale2 = pack_f32x2(a.scale_log2, a.scale_log2);
         unsigned long long sum_a = 0ull, sum_b = 0ull;  // two independent packed accumulators (4 partial sums)
@@ -548,7 +532,6 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
           mbar_arrive(&bars->p_full[t]);
           if (j == nblk - 1) mbar_arrive(&bars->l_ready[t]);
         }
-        if (tracer) trace_ev<TRACE>(1 + warp, trn, 5);
       }
       ++item_n;
       kv_base += (uint32_t)nblk;
@@ -637,13 +620,9 @@ int fmha_launch(emk_handle_t h, const void* q, const void* k, const void* v, voi
 
   static bool configured[64] = {false};
   if (h->device < 64 && !configured[h->device]) {
-    EMK_CUDA_TRY(h, cudaFuncSetAttribute(fmha_causal_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         FMHA_SMEM));
-    EMK_CUDA_TRY(h, cudaFuncSetAttribute(fmha_causal_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         FMHA_SMEM));
+    EMK_CUDA_TRY(h, cudaFuncSetAttribute(fmha_causal_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FMHA_SMEM));
     configured[h->device] = true;
   }
-  const bool trace = getenv("EMK_FMHA_TRACE") != nullptr;
   const int64_t n_items = (int64_t)a.nqblk * B * Hkv * a.pairs;
   if (n_items > 0x7fffffffLL) return EMK_ERR_SHAPE;
   a.n_items = (int)n_items;
@@ -659,10 +638,7 @@ int fmha_launch(emk_handle_t h, const void* q, const void* k, const void* v, voi
     if (gp > per_qblk) gp = per_qblk;
     a.gp = (int)gp;
   }
-  if (trace)
-    fmha_causal_kernel<true><<<(unsigned)grid, FMHA_THREADS, FMHA_SMEM, s>>>(tq, tk, tv, to, a);
-  else
-    fmha_causal_kernel<false><<<(unsigned)grid, FMHA_THREADS, FMHA_SMEM, s>>>(tq, tk, tv, to, a);
+  fmha_causal_kernel<<<(unsigned)grid, FMHA_THREADS, FMHA_SMEM, s>>>(tq, tk, tv, to, a);
   EMK_LAUNCH_CHECK(h);
   return EMK_OK;
 }
@@ -680,8 +656,4 @@ extern "C" int emk_sdpa_causal_gqa_bf16_tok(emk_handle_t h, const void* q, const
                                             int64_t ld_k, int64_t ld_v, int64_t ld_o, float scale,
                                             emk_stream_t stream) {
   return fmha_launch(h, q, k, v, o, B, Hq, Hkv, S, D, true, ld_q, ld_k, ld_v, ld_o, scale, (cudaStream_t)stream);
-}
-
-extern "C" int emk_debug_fmha_trace(void* host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, g_trace, sizeof(g_trace));
 }
