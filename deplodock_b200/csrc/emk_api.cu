@@ -32,6 +32,8 @@ extern "C" int emk_create(int device, emk_handle_t* out) {
   h->wait_limit_ns = 2000ull * 1000ull * 1000ull;
   const char* impl = getenv("EMK_GEMM_IMPL");
   h->gemm_impl = impl ? atoi(impl) : 0;
+  const char* ovl = getenv("EMK_OVERLAP_LAUNCH");
+  h->overlap_launch = (ovl && atoi(ovl) == 0) ? 0 : 1;
   cudaError_t e = cudaSetDevice(device);
   if (e != cudaSuccess) {
     free(h);

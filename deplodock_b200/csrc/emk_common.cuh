@@ -32,6 +32,8 @@ struct emk_handle_s {
   int* status_dev;      // device alias of status_host
   unsigned long long wait_limit_ns;
   int gemm_impl;        // 0 = choose by shape, 1 = single-CTA tiles, 2 = CTA-pair tiles (env EMK_GEMM_IMPL)
+  int overlap_launch;   // 1 = kernels of the model path start their prologue under the previous kernel's tail
+                        // (programmatic dependent launch; env EMK_OVERLAP_LAUNCH=0 turns it off)
   char last_error[512];
 };
 
@@ -132,6 +134,30 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "r"(smem_u32(bar)), "r"(parity)
       : "memory");
   return ok != 0;
+}
+
+// Programmatic dependent launch. A kernel launched with launch_after_prologue(..., overlap = true) may become
+// resident while the kernel before it in the stream is still draining: its CTAs run their set-up (barrier
+// initialisation, tensor-memory allocation, descriptor prefetch) and then stop in grid_dependency_wait() until the
+// earlier kernel has completed and its writes are visible. Every global read and write of such a kernel comes after
+// that wait. Launched the ordinary way, both calls do nothing.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_after_prologue(void (*kern)(KArgs...), unsigned grid, unsigned block, size_t smem,
+                                         cudaStream_t stream, bool overlap, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(block, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = overlap ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 
 // Shared by all roles of one CTA: where the abort flag lives and how long a wait may last.

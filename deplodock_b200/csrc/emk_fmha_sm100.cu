@@ -207,6 +207,8 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
   const WaitCtx wc{&bars->abort_flag, a.status, a.limit_ns};
+  grid_dependency_wait();      // everything above overlaps the tail of the previous kernel in the stream
+  grid_launch_dependents();
 
   // The CTA is persistent: every role walks the same list of work items with running counters for the barrier
   // phases. Nothing drains between items: the first S of the next item is issued right behind the last PV of the
@@ -638,7 +640,8 @@ int fmha_launch(emk_handle_t h, const void* q, const void* k, const void* v, voi
     if (gp > per_qblk) gp = per_qblk;
     a.gp = (int)gp;
   }
-  fmha_causal_kernel<<<(unsigned)grid, FMHA_THREADS, FMHA_SMEM, s>>>(tq, tk, tv, to, a);
+  EMK_CUDA_TRY(h, launch_after_prologue(fmha_causal_kernel, (unsigned)grid, FMHA_THREADS, FMHA_SMEM, s,
+                                        h->overlap_launch != 0, tq, tk, tv, to, a));
   EMK_LAUNCH_CHECK(h);
   return EMK_OK;
 }

@@ -87,6 +87,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
   __syncthreads();
   cluster_sync_all();
   tc_fence_after();
+  grid_dependency_wait();      // everything above overlaps the tail of the previous kernel in the stream
+  grid_launch_dependents();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
   const WaitCtx wc{&bars->abort_flag, g.status, g.limit_ns};
 
@@ -243,7 +245,7 @@ int launch_gemm2(emk_handle_t h, const CUtensorMap& ta, const CUtensorMap& tb, c
   }
   const int ntiles = g.tiles_m * g.tiles_n;
   const int pairs = ntiles < max_pairs[d] ? ntiles : max_pairs[d];
-  kern<<<2 * pairs, G2_THREADS, G2_SMEM, s>>>(ta, tb, g);
+  EMK_CUDA_TRY(h, launch_after_prologue(kern, 2u * (unsigned)pairs, G2_THREADS, G2_SMEM, s, h->overlap_launch != 0, ta, tb, g));
   EMK_LAUNCH_CHECK(h);
   return EMK_OK;
 }

@@ -22,6 +22,8 @@ __global__ void __launch_bounds__(256) embed_gather_kernel(const uint4* __restri
                                                            int vec_per_row, int64_t vocab) {
   const int lane = threadIdx.x & 31;
   const int64_t warp = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  grid_dependency_wait();
+  grid_launch_dependents();
   if (warp >= tokens) return;
   int64_t id = ids[warp];
   id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);  // clamp instead of reading out of bounds
@@ -124,6 +126,8 @@ __global__ void __launch_bounds__(256) pool_norm_l2_kernel(const __nv_bfloat16* 
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   const int64_t b = blockIdx.x;
   const __nv_bfloat16* row = hs + (b * S + (S - 1)) * (int64_t)hidden;
+  grid_dependency_wait();
+  grid_launch_dependents();
   float ss = 0.f;
   for (int c = threadIdx.x; c < hidden; c += 256) {
     const float f = __bfloat162float(row[c]);
@@ -172,8 +176,9 @@ extern "C" int emk_embed_gather_sumsq(emk_handle_t h, const void* table, const i
   if ((hidden * 2) % 16 != 0 || (((uintptr_t)table | (uintptr_t)out) & 15u)) return EMK_ERR_ALIGN;
   if (row_sumsq != nullptr && hidden % 128 != 0) return EMK_ERR_SHAPE;
   const int64_t grid = (tokens + 7) / 8;
-  embed_gather_kernel<<<(unsigned)grid, 256, 0, (cudaStream_t)stream>>>((const uint4*)table, ids, (uint4*)out, row_sumsq,
-                                                                       tokens, (int)(hidden / 8), vocab);
+  EMK_CUDA_TRY(h, launch_after_prologue(embed_gather_kernel, (unsigned)grid, 256u, 0, (cudaStream_t)stream,
+                                        h->overlap_launch != 0, (const uint4*)table, ids, (uint4*)out, row_sumsq, tokens,
+                                        (int)(hidden / 8), vocab));
   EMK_LAUNCH_CHECK(h);
   return EMK_OK;
 }
@@ -198,9 +203,9 @@ extern "C" int emk_pool_norm_l2(emk_handle_t h, const void* hidden_states, const
                                 int64_t S, int64_t hidden, float eps, emk_stream_t stream) {
   if (!h || !hidden_states || !w || !out) return EMK_ERR_ARG;
   if (B <= 0 || S <= 0 || hidden <= 0) return EMK_ERR_SHAPE;
-  pool_norm_l2_kernel<<<(unsigned)B, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)hidden_states,
-                                                                    (const __nv_bfloat16*)w, out, (int)S, (int)hidden,
-                                                                    eps);
+  EMK_CUDA_TRY(h, launch_after_prologue(pool_norm_l2_kernel, (unsigned)B, 256u, 0, (cudaStream_t)stream,
+                                        h->overlap_launch != 0, (const __nv_bfloat16*)hidden_states,
+                                        (const __nv_bfloat16*)w, out, (int)S, (int)hidden, eps));
   EMK_LAUNCH_CHECK(h);
   return EMK_OK;
 }
