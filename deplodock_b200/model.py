@@ -71,28 +71,17 @@ class _LayerWeights:
     __slots__ = ("ln1", "wqkv", "qn", "kn", "wo", "ln2", "wgu", "wdown")
 
 
-class EmbedForward:
-    """Batch forward of the trunk on one GPU. ``state_dict`` uses the HF ``Qwen3Model`` parameter names."""
+class EmbedWeights:
+    """The trunk's weights in the layout the kernels read, prepared once and shared by every plan: q/k/v projections
+    concatenated, gate/up rows interleaved, and (``fold_rmsnorm``) the two per-layer RMSNorm weights multiplied into
+    the projection that follows them. ``state_dict`` uses the HF ``Qwen3Model`` parameter names."""
 
-    #: kernel launches per layer / outside the layers, for launch accounting in the bench
-    LAUNCHES_FIXED = 2
-
-    @property
-    def LAUNCHES_PER_LAYER(self) -> int:
-        return 5 if self.fold_rmsnorm else 7
-
-    def __init__(self, cfg, state_dict: dict[str, torch.Tensor], *, batch: int, seq: int, device=None,
-                 chunk_seqs: int | None = None, fold_rmsnorm: bool = True) -> None:
-        self.cfg = EmbedConfig.from_any(cfg)
+    def __init__(self, cfg, state_dict: dict[str, torch.Tensor], *, device=None, fold_rmsnorm: bool = True) -> None:
+        self.cfg = c = EmbedConfig.from_any(cfg)
         self.fold_rmsnorm = bool(fold_rmsnorm)
-        c = self.cfg
         if c.head_dim != 128:
             raise ValueError("the attention kernel is built for head_dim 128")
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-        self.batch, self.seq = int(batch), int(seq)
-        self.chunk_seqs = self.batch if not chunk_seqs else min(int(chunk_seqs), self.batch)
-        if self.batch % self.chunk_seqs != 0:
-            raise ValueError("chunk_seqs must divide the batch")
         dev, bf = self.device, torch.bfloat16
 
         def w(name: str) -> torch.Tensor:
@@ -121,22 +110,83 @@ class EmbedForward:
                 lw.wqkv = (lw.wqkv.float() * lw.ln1.float()[None, :]).to(bf).contiguous()
                 lw.wgu = (lw.wgu.float() * lw.ln2.float()[None, :]).to(bf).contiguous()
             self.layers.append(lw)
-        self.cos, self.sin = rope_tables(self.seq, c.head_dim, c.rope_theta, dev)
-        self.rope_cm = ops.rope_chunk_major(self.cos, self.sin)
 
-        T = self.chunk_seqs * self.seq
+
+class EmbedWorkspace:
+    """Activation buffers sized for ``max_tokens`` tokens / ``max_batch`` sequences. Plans of different (batch, seq)
+    take prefixes of the same buffers, so each captured CUDA graph replays over memory that stays put — the scheme of
+    the reference's shared buffer set sized at ``max_seq_len`` (``emmy/serving/runner.py:160-170``)."""
+
+    def __init__(self, cfg, max_tokens: int, max_batch: int, device) -> None:
+        c = EmbedConfig.from_any(cfg)
         nq, nkv, D = c.num_attention_heads, c.num_key_value_heads, c.head_dim
-        self.ids = torch.zeros(self.batch, self.seq, dtype=torch.int64, device=dev)
+        dev, bf = torch.device(device), torch.bfloat16
+        self.max_tokens, self.max_batch = int(max_tokens), int(max_batch)
+        T = self.max_tokens
+        self.ids = torch.zeros(T, dtype=torch.int64, device=dev)
         self.h = torch.empty(T, c.hidden_size, dtype=bf, device=dev)
         self.x = torch.empty(T, c.hidden_size, dtype=bf, device=dev)
+        self.hs = torch.empty(T, c.hidden_size, dtype=bf, device=dev)
         self.qkv = torch.empty(T, (nq + 2 * nkv) * D, dtype=bf, device=dev)
         self.attn = torch.empty(T, nq * D, dtype=bf, device=dev)
         self.mlp = torch.empty(T, c.intermediate_size, dtype=bf, device=dev)
-        self.out = torch.empty(self.batch, c.hidden_size, dtype=torch.float32, device=dev)
+        self.out = torch.empty(self.max_batch, c.hidden_size, dtype=torch.float32, device=dev)
         # scratch of the two folded RMSNorms: partial row sums of squares, one slot per 128 hidden columns, fully
         # overwritten by every producer (no clearing, no atomics)
         self.ss1 = torch.zeros(T, c.hidden_size // 128, dtype=torch.float32, device=dev)
         self.ss2 = torch.zeros(T, c.hidden_size // 128, dtype=torch.float32, device=dev)
+
+
+class EmbedForward:
+    """Batch forward of the trunk on one GPU. ``state_dict`` uses the HF ``Qwen3Model`` parameter names; pass
+    ``weights=`` (an :class:`EmbedWeights`) and ``workspace=`` to share them between plans of different shapes.
+    With ``hidden_states=True`` the plan also writes the final-norm hidden states of every token to ``self.hs``
+    (``[batch * seq, hidden]`` bf16), which is what the reference's runner returns."""
+
+    #: kernel launches per layer / outside the layers, for launch accounting in the bench
+    @property
+    def LAUNCHES_FIXED(self) -> int:
+        return 3 if self.hidden_states else 2
+
+    @property
+    def LAUNCHES_PER_LAYER(self) -> int:
+        return 5 if self.fold_rmsnorm else 7
+
+    def __init__(self, cfg, state_dict: dict[str, torch.Tensor] | None = None, *, batch: int, seq: int, device=None,
+                 chunk_seqs: int | None = None, fold_rmsnorm: bool = True, weights: EmbedWeights | None = None,
+                 workspace: EmbedWorkspace | None = None, hidden_states: bool = False) -> None:
+        if weights is None:
+            if state_dict is None:
+                raise ValueError("give a state_dict or prepared weights")
+            weights = EmbedWeights(cfg, state_dict, device=device, fold_rmsnorm=fold_rmsnorm)
+        self.weights = weights
+        self.cfg = c = weights.cfg
+        self.fold_rmsnorm = weights.fold_rmsnorm
+        self.device = dev = weights.device
+        self.batch, self.seq = int(batch), int(seq)
+        self.chunk_seqs = self.batch if not chunk_seqs else min(int(chunk_seqs), self.batch)
+        if self.batch % self.chunk_seqs != 0:
+            raise ValueError("chunk_seqs must divide the batch")
+        self.hidden_states = bool(hidden_states)
+        if self.hidden_states and self.chunk_seqs != self.batch:
+            raise ValueError("hidden_states=True needs the whole batch in one chunk")
+        self.embed, self.final_norm, self.layers = weights.embed, weights.final_norm, weights.layers
+        self.cos, self.sin = rope_tables(self.seq, c.head_dim, c.rope_theta, dev)
+        self.rope_cm = ops.rope_chunk_major(self.cos, self.sin)
+
+        T = self.chunk_seqs * self.seq
+        if workspace is None:
+            workspace = EmbedWorkspace(c, T, self.batch, dev)
+            if self.batch * self.seq > T:   # chunked plan: the id buffer still holds the whole batch
+                workspace.ids = torch.zeros(self.batch * self.seq, dtype=torch.int64, device=dev)
+        if workspace.max_tokens < T or workspace.max_batch < self.batch or workspace.ids.numel() < self.batch * self.seq:
+            raise ValueError("workspace too small for this plan")
+        self.workspace = ws = workspace
+        self.ids = ws.ids[: self.batch * self.seq].view(self.batch, self.seq)
+        self.h, self.x, self.hs = ws.h[:T], ws.x[:T], ws.hs[:T]
+        self.qkv, self.attn, self.mlp = ws.qkv[:T], ws.attn[:T], ws.mlp[:T]
+        self.out = ws.out[: self.batch]
+        self.ss1, self.ss2 = ws.ss1[:T], ws.ss2[:T]
         self._graph: torch.cuda.CUDAGraph | None = None
 
     # -----------------------------------------------------------------------------------------------------------
@@ -169,6 +219,8 @@ class EmbedForward:
                                norm_eps=eps)
                 ops.gemm_fused(self.mlp, lw.wdown, self.h, epilogue="residual", residual=self.h,
                                row_sumsq_out=self.ss1)
+            if self.hidden_states:
+                ops.rmsnorm(self.h, self.final_norm, eps, out=self.hs)
             ops.pool_norm_l2(self.h, self.final_norm, B, S, eps, out=out)
             return
         ops.embed_gather(self.embed, ids, out=self.h)
@@ -180,6 +232,8 @@ class EmbedForward:
             ops.rmsnorm(self.h, lw.ln2, eps, out=self.x)
             ops.linear(self.x, lw.wgu, swiglu=True, out=self.mlp)
             ops.linear(self.mlp, lw.wdown, residual=self.h, out=self.h)
+        if self.hidden_states:
+            ops.rmsnorm(self.h, self.final_norm, eps, out=self.hs)
         ops.pool_norm_l2(self.h, self.final_norm, B, S, eps, out=out)
 
     def forward_eager(self) -> torch.Tensor:

@@ -111,9 +111,15 @@ def embed_forward_hf(ids: torch.Tensor, cfg: EmbedModelConfig, sd: dict[str, tor
 
 
 def embed_forward(ids: torch.Tensor, cfg: EmbedModelConfig, sd: dict[str, torch.Tensor]) -> torch.Tensor:
-    """The same trunk written out with torch functional ops in the module's own dtype and rounding order — the
-    dataflow of the traced graph (GatherOp, RMSNorm chains, 7 LinearOps, RoPE chain, SdpaOp, SwiGLU per layer).
-    Checked against :func:`embed_forward_hf` in the tests; used where transformers is slow to build."""
+    """Last-token pooling + L2 normalisation of :func:`trunk_hidden_states`; fp32 ``[B, hidden]``."""
+    return F.normalize(trunk_hidden_states(ids, cfg, sd)[:, -1].float(), p=2, dim=-1)
+
+
+def trunk_hidden_states(ids: torch.Tensor, cfg: EmbedModelConfig, sd: dict[str, torch.Tensor]) -> torch.Tensor:
+    """The trunk written out with torch functional ops in the module's own dtype and rounding order — the
+    dataflow of the traced graph (GatherOp, RMSNorm chains, 7 LinearOps, RoPE chain, SdpaOp, SwiGLU per layer) — up to
+    and including the final norm: ``[B, S, hidden]`` in the weights' dtype, i.e. what the reference's runner returns
+    per sequence (``emmy/serving/runner.py:204-236``). Checked against :func:`embed_forward_hf` in the tests."""
     B, S = ids.shape
     D, nq, nkv = cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads
     dt = sd["embed_tokens.weight"].dtype
@@ -143,5 +149,4 @@ def embed_forward(ids: torch.Tensor, cfg: EmbedModelConfig, sd: dict[str, torch.
             x = rmsnorm_hf(h, sd[p + "post_attention_layernorm.weight"], cfg.rms_norm_eps)
             m = F.silu(F.linear(x, sd[p + "mlp.gate_proj.weight"])) * F.linear(x, sd[p + "mlp.up_proj.weight"])
             h = h + F.linear(m, sd[p + "mlp.down_proj.weight"])
-        h = rmsnorm_hf(h, sd["norm.weight"], cfg.rms_norm_eps)
-        return F.normalize(h[:, -1].float(), p=2, dim=-1)
+        return rmsnorm_hf(h, sd["norm.weight"], cfg.rms_norm_eps)

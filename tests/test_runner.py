@@ -1,0 +1,141 @@
+"""The serving-side runner: span splitting (CPU) and per-sequence hidden states against the eager CPU trunk (GPU)."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+from deplodock_b200.runner import split_spans
+from oracle import cpu_ref, inputs
+
+
+# ------------------------------------------------------------------------------------------------------------
+# packed-batch span splitting (contract of emmy/serving/packed.py:6-34)
+# ------------------------------------------------------------------------------------------------------------
+def test_split_spans_at_position_zero():
+    assert split_spans([0, 1, 2, 0, 1, 0], 16) == [(0, 3), (3, 5), (5, 6)]
+    assert split_spans([], 16) == []
+    assert split_spans([0], 16) == [(0, 1)]
+
+
+def test_split_spans_garbage_first_position_and_chopping():
+    # dummy-run batches: positions[0] != 0 still starts a span; over-long spans are cut into max_seq_len pieces
+    assert split_spans([5, 6, 7, 8, 9], 2) == [(0, 2), (2, 4), (4, 5)]
+    assert split_spans([3, 4, 0, 1, 2, 3, 4], 3) == [(0, 2), (2, 5), (5, 7)]
+
+
+def test_split_spans_covers_every_token_once():
+    import random
+
+    rng = random.Random(0)
+    for _ in range(50):
+        lens = [rng.randint(1, 9) for _ in range(rng.randint(1, 8))]
+        pos = [p for n in lens for p in range(n)]
+        spans = split_spans(pos, 4)
+        assert spans[0][0] == 0 and spans[-1][1] == len(pos)
+        assert all(a < b and b - a <= 4 for a, b in spans)
+        assert all(spans[i][1] == spans[i + 1][0] for i in range(len(spans) - 1))
+
+
+def test_create_rejects_other_dtypes():
+    from deplodock_b200.runner import EmbedForwardRunner
+
+    with pytest.raises(ValueError, match="bf16"):
+        EmbedForwardRunner.create({}, 128, dtype_str="float16", cfg=inputs.EmbedModelConfig())
+
+
+# ------------------------------------------------------------------------------------------------------------
+# GPU
+# ------------------------------------------------------------------------------------------------------------
+def _cos(a, b):
+    return torch.nn.functional.cosine_similarity(a.double(), b.double(), dim=-1)
+
+
+@pytest.fixture(scope="module")
+def small_runner(libemk):
+    from deplodock_b200.runner import EmbedForwardRunner
+
+    cfg = inputs.EmbedModelConfig().small(layers=2, vocab=500)
+    sd = inputs.perturb_norm_weights(inputs.embed_model_weights(cfg))
+    return cfg, sd, EmbedForwardRunner.create(sd, 384, batch=4, cfg=cfg)
+
+
+def _assert_hidden(got: torch.Tensor, ref: torch.Tensor, what: str):
+    got, ref = got.float().cpu(), ref.float()
+    assert got.shape == ref.shape, what
+    assert torch.isfinite(got).all(), what
+    # bf16 trunk output of O(1) magnitude after the final norm: one bf16 ulp at 4 is 2^-5
+    assert _cos(got, ref).min().item() >= 0.998, what
+    assert (got - ref).abs().max().item() <= 2.0 ** -4 * max(1.0, ref.abs().max().item()), what
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("S", [1, 40, 128, 200, 384])
+def test_single_sequence_hidden_states(small_runner, S):
+    cfg, sd, runner = small_runner
+    ids = inputs.token_ids(1, S, cfg.vocab_size, seed=S)
+    got = runner.forward_hidden_states(ids[0].cuda())
+    assert got.dtype == torch.bfloat16 and tuple(got.shape) == (S, cfg.hidden_size)
+    _assert_hidden(got, cpu_ref.trunk_hidden_states(ids, cfg, sd)[0], f"S={S}")
+
+
+@pytest.mark.gpu
+def test_one_graph_per_sequence_length(small_runner):
+    cfg, _, runner = small_runner
+    a = inputs.token_ids(1, 77, cfg.vocab_size, seed=1)[0].cuda()
+    b = inputs.token_ids(1, 77, cfg.vocab_size, seed=2)[0].cuda()
+    before = runner.captures
+    ra = runner.forward_hidden_states(a)
+    assert runner.captures == before + 1
+    rb = runner.forward_hidden_states(b)
+    assert runner.captures == before + 1, "same S must reuse the captured graph"
+    assert not torch.equal(ra, rb)
+    assert torch.equal(runner.forward_hidden_states(a), ra), "replay over the shared buffers is deterministic"
+    runner.forward_hidden_states(a[:50])
+    assert runner.captures == before + 2
+
+
+@pytest.mark.gpu
+def test_batched_ragged_equals_per_sequence(small_runner):
+    """Right padding is exact under the causal mask: every sequence of a padded group gets the result it gets alone."""
+    cfg, sd, runner = small_runner
+    lens = [40, 130, 7, 256, 384, 1, 90]
+    seqs = [inputs.token_ids(1, n, cfg.vocab_size, seed=10 + i)[0].cuda() for i, n in enumerate(lens)]
+    batched = runner.forward_hidden_states_batched(seqs)
+    assert [tuple(t.shape) for t in batched] == [(n, cfg.hidden_size) for n in lens]
+    for t, s, n in zip(batched, seqs, lens):
+        alone = runner.forward_hidden_states(s)
+        # same kernels, same per-row arithmetic; only the tile a row falls in differs
+        assert _cos(t.float(), alone.float()).min().item() >= 0.9999
+        _assert_hidden(t, cpu_ref.trunk_hidden_states(s.cpu()[None], cfg, sd)[0], f"len {n}")
+
+
+@pytest.mark.gpu
+def test_packed_forward_and_pooling(small_runner):
+    cfg, sd, runner = small_runner
+    lens = [33, 128, 5]
+    seqs = [inputs.token_ids(1, n, cfg.vocab_size, seed=30 + i)[0] for i, n in enumerate(lens)]
+    packed = torch.cat(seqs + [torch.zeros(6, dtype=torch.int64)]).cuda()     # vLLM pads num_tokens
+    positions = torch.cat([torch.arange(n) for n in lens] + [torch.arange(6)]).cuda()
+    out = runner.forward_packed(packed, positions)
+    assert tuple(out.shape) == (sum(lens) + 6, cfg.hidden_size)
+    off = 0
+    for s, n in zip(seqs, lens):
+        _assert_hidden(out[off:off + n], cpu_ref.trunk_hidden_states(s[None], cfg, sd)[0], f"span at {off}")
+        off += n
+    emb = runner.embed_packed(torch.cat(seqs).cuda(), torch.cat([torch.arange(n) for n in lens]).cuda()).cpu()
+    assert tuple(emb.shape) == (3, cfg.hidden_size)
+    for i, s in enumerate(seqs):
+        ref = cpu_ref.embed_forward(s[None], cfg, sd)[0]
+        assert _cos(emb[i], ref).item() >= 0.999 and (emb[i] - ref).abs().max().item() <= 2e-2
+
+
+@pytest.mark.gpu
+def test_limits(small_runner):
+    cfg, _, runner = small_runner
+    with pytest.raises(ValueError, match="exceeds max_seq_len"):
+        runner.forward_hidden_states(torch.zeros(385, dtype=torch.int64, device="cuda"))
+    assert runner.forward_hidden_states(torch.zeros(0, dtype=torch.int64, device="cuda")).shape == (0, cfg.hidden_size)
+    # out-of-vocabulary ids of a dummy run are clamped, not read out of bounds
+    out = runner.forward_packed(torch.full((9,), 10 ** 9, dtype=torch.int64, device="cuda"), list(range(9)))
+    assert torch.isfinite(out.float()).all()
