@@ -123,7 +123,7 @@ def cmd_compile(args) -> int:
     if args.ir == "torch":
         text = json.dumps(graph.to_dict(), indent=2)
     else:
-        text = B200Backend().compile(graph).describe()
+        text = B200Backend(dump=args.dump_dir or os.environ.get("EMMY_DUMP_DIR")).compile(graph).describe()
     if args.output:
         Path(args.output).write_text(text + "\n")
     else:

@@ -207,6 +207,30 @@ def lower(graph: Graph) -> CompiledPlan:
     return CompiledPlan(graph, steps, aliases)
 
 
+def dump_plan(plan: CompiledPlan, dump_dir) -> None:
+    """Write the compilation artefacts the reference's dumper writes for the stages this backend has
+    (``emmy/compiler/pipeline/dump.py:125-206``): ``00_torch.json`` (the input graph), ``50_cuda.kernels.txt`` (the
+    launch plan) and per launch ``50_cuda.kernels/<kname>.torch.json`` — the Torch op behind that launch as a
+    stand-alone sub-graph that ``python -m deplodock_b200 run --ir <file> --bench`` re-runs — with a
+    ``<kname>.torch.txt`` header giving its origin node and ``i/N`` coverage (always ``1/1 — full`` here: one launch
+    per Torch op, nothing is split or fused at this level)."""
+    import json
+    from pathlib import Path
+
+    d = Path(dump_dir)
+    (d / "50_cuda.kernels").mkdir(parents=True, exist_ok=True)
+    (d / "00_torch.json").write_text(json.dumps(plan.graph.to_dict(), indent=1))
+    (d / "50_cuda.kernels.txt").write_text(plan.describe() + "\n")
+    for s in plan.steps:
+        node = plan.graph.nodes[s.out]
+        sub = plan.graph.single_node_graph(s.out, operands=list(s.args) + [i for i in node.inputs[len(s.args):]
+                                                                          if plan.graph.nodes[i].op == "ConstantOp"])
+        (d / "50_cuda.kernels" / f"{s.kernel_name}.torch.json").write_text(json.dumps(sub.to_dict(), indent=1))
+        (d / "50_cuda.kernels" / f"{s.kernel_name}.torch.txt").write_text(
+            f"# matching torch ops for kernel '{s.kernel_name}' ({s.entry})\n"
+            f"#   {s.out} ({node.op}): 1/1 — full\n")
+
+
 # ------------------------------------------------------------------------------------------------------------
 # Backend
 # ------------------------------------------------------------------------------------------------------------
@@ -239,7 +263,10 @@ class B200Backend(Backend):
     def compile(self, graph: Any) -> CompiledPlan:
         if isinstance(graph, CompiledPlan):
             return graph
-        return lower(Graph.coerce(graph))
+        plan = lower(Graph.coerce(graph))
+        if self.dump:
+            dump_plan(plan, self.dump)
+        return plan
 
     # -- run ---------------------------------------------------------------------------------------------------
     def _device(self):

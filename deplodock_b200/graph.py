@@ -142,6 +142,26 @@ class Graph:
         return [self.nodes[n] for n in self.topological_order()
                 if self.nodes[n].op not in ("InputOp", "ConstantOp")]
 
+    def single_node_graph(self, nid: str, operands: list[str] | None = None) -> "Graph":
+        """The node ``nid`` as a stand-alone graph: the node itself, its scalar / weight ``ConstantOp`` producers as
+        they are, and every other operand turned into an ``InputOp`` of the same name, shape and dtype — the
+        per-kernel reproducer sub-graph of the reference (``emmy/compiler/pipeline/dump.py:135-180``). ``operands``
+        replaces the node's own input ids (a plan step reads through views and casts)."""
+        node = self.nodes[nid]
+        ins = list(node.inputs if operands is None else operands)
+        nodes: dict[str, Node] = {}
+        inputs: list[str] = []
+        for i in ins:
+            src = self.nodes[i]
+            if src.op == "ConstantOp":
+                nodes[i] = Node(i, src.op, dict(src.op_fields), [], src.output)
+            else:
+                nodes[i] = Node(i, "InputOp", {}, [], src.output)
+                if i not in inputs:
+                    inputs.append(i)
+        nodes[nid] = Node(nid, node.op, dict(node.op_fields), ins, node.output)
+        return Graph(inputs, [nid], nodes)
+
     def op_histogram(self) -> dict[str, int]:
         h: dict[str, int] = {}
         for n in self.nodes.values():

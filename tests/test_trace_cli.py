@@ -105,6 +105,28 @@ def test_compile_cli_prints_plan(capsys):
     assert rec["nodes"]["softmax"]["op"] == "SoftmaxOp"
 
 
+def test_dump_dir_writes_rerunnable_per_kernel_records(tmp_path, capsys):
+    """``compile --dump-dir`` leaves one stand-alone Torch-IR record per launch; each compiles back to the same entry."""
+    from deplodock_b200.graph import Graph
+
+    code = "m = nn.Linear(64, 96, bias=True); torch.softmax(m(torch.randn(8, 64)), dim=-1)"
+    assert main(["compile", "-c", code, "--dump-dir", str(tmp_path)]) == 0
+    plan_text = capsys.readouterr().out
+    assert (tmp_path / "00_torch.json").exists() and (tmp_path / "50_cuda.kernels.txt").read_text().strip() == plan_text.strip()
+    whole = B200Backend().compile(Graph.from_json(tmp_path / "00_torch.json"))
+    assert [s.entry for s in whole.steps] == ["emk_linear_f32_simt", "emk_softmax_lastdim"]
+    for step in whole.steps:
+        rec = tmp_path / "50_cuda.kernels" / f"{step.kernel_name}.torch.json"
+        sub = B200Backend().compile(Graph.from_json(rec))
+        assert [s.entry for s in sub.steps] == [step.entry]
+        assert sub.steps[0].attrs == step.attrs
+        head = (tmp_path / "50_cuda.kernels" / f"{step.kernel_name}.torch.txt").read_text()
+        assert "1/1" in head and step.out in head
+    # the softmax record reads the linear's output as a plain input of the same shape
+    soft = Graph.from_json(tmp_path / "50_cuda.kernels" / f"{whole.steps[1].kernel_name}.torch.json")
+    assert soft.inputs == ["linear"] and soft.nodes["linear"].output.shape == (8, 96)
+
+
 def test_compile_cli_unsupported_op_exit_code(capsys):
     assert main(["compile", "-c", "torch.relu(torch.randn(4, 4))"]) == 1
     assert "LoweringError" in capsys.readouterr().err
@@ -156,6 +178,18 @@ def test_run_cli_bf16_and_bench(tmp_path, capsys):
     assert rec["warmup"] == 2 and rec["iters"] == 5
     assert set(rec["backends"]) == {"Eager PyTorch", "Emmy"}
     assert rec["backends"]["Emmy"]["latency_us"] > 0 and "speedup_vs_eager" in rec["backends"]["Emmy"]
+
+
+@pytest.mark.gpu
+def test_run_cli_reruns_dumped_kernel_records(tmp_path, capsys):
+    code = "q=torch.randn(1,4,160,128); k=torch.randn(1,2,160,128); F.scaled_dot_product_attention(q,k,k,is_causal=True,enable_gqa=True)"
+    assert main(["run", "-c", code, "--dump-dir", str(tmp_path)]) == 0
+    capsys.readouterr()
+    recs = sorted((tmp_path / "50_cuda.kernels").glob("*.torch.json"))
+    assert len(recs) == 1
+    assert main(["run", "--ir", str(recs[0]), "--bench", "--warmup", "1", "--iters", "3"]) == 0
+    out = capsys.readouterr().out
+    assert "Emmy" in out and "k_scaled_dot_product_attention" in out
 
 
 @pytest.mark.gpu
