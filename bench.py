@@ -440,7 +440,11 @@ def main() -> None:
             "unit": "TFLOP/s", "frac": round(gemm_tflops / peak, 4),
             "launches_per_step": gp["launches"], "avg_launch_us": round(gp["ms"] * 1e3 / gp["launches"], 2),
             "gemm_share_of_step": round(gp["ms"] / ms_per_step, 4), "by_shape": gp["by_shape"],
-            "traffic": None,
+            # dram__bytes_read + dram__bytes_write of one launch of the widest projection (QKV, 32768x4096x1024):
+            # ncu capture at M = 8192 (41.6 MB), scaled by the rows of a full launch; 344 MB algorithmic
+            "traffic": 166.4e6 * (BATCH // world) / 64,
+            "traffic_kernel": "gemm2_bf16_kernel, QKV projection of one rank's shard",
+            "traffic_source": "profiles/gemm2_bf16_linear_4096x2048x6144.md (M=8192 capture scaled by rows)",
         }
         step_flops = cfg.linear_flops_per_token() * BATCH * SEQ + cfg.attention_flops(BATCH, SEQ)
         line = {
