@@ -150,7 +150,45 @@ def run_reference_arm(args) -> None:
                                    "reference traces and checks against)"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
+    emitted = reference_emitted_kernels()
+    if emitted is not None:
+        line["emitted_kernels_on_this_gpu"] = emitted
     print(json.dumps(line), flush=True)
+
+
+def reference_emitted_kernels():
+    """The reference compiler's own emitted kernels for the four kernel configurations (``oracle/_ref``, lowered for
+    sm_100 by its pipeline and compiled with its nvcc flags), timed on this GPU on the seeded inputs with the protocol
+    used for the hand-written kernels (CUDA graph of back-to-back launches). ``None`` without a GPU or without the
+    prebuilt files."""
+    try:
+        import torch
+
+        from oracle import inputs, ref_kernels
+
+        if not torch.cuda.is_available() or not ref_kernels.available():
+            return None
+        rows = []
+        for name in ("rmsnorm", "softmax", "linear", "sdpa"):
+            k = ref_kernels.RefKernel(name)
+            if name == "rmsnorm":
+                x, w = inputs.rmsnorm_inputs()
+                k.bind(x=x, p_weight=w)
+            elif name == "softmax":
+                k.bind(input=inputs.softmax_inputs((1, 28, 2048, 2048)))
+            elif name == "linear":
+                x, w = inputs.linear_inputs()
+                k.bind(input=x, linear_wt=w.t().contiguous())
+            else:
+                q, kk, v = inputs.sdpa_inputs()
+                k.bind(q=q, k=kk, v=v)
+            rows.append({"config": name, "kernel": k.meta["kernel_name"], "grid": k.meta["grid"][0],
+                         "block": k.meta["block"][0], "us": round(k.time_us(10 if name == "rmsnorm" else 3, 3), 1)})
+            del k
+            torch.cuda.empty_cache()
+        return rows
+    except Exception as exc:  # noqa: BLE001 - an informational table must not fail the arm
+        return {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
 
 
 # ------------------------------------------------------------------------------------------------------------
