@@ -272,7 +272,11 @@ def kernel_table(peaks: dict) -> list[dict]:
     s = (w32.abs().amax(1) / 448.0).contiguous()
     wq = (w32 / s[:, None]).to(torch.float8_e4m3fn)
     us, mn = _graph_time_us(lambda: ops.linear_w8(xl, wq, s, out=yl), 20)
-    add("k_linear 4096x2048x6144 e4m3 weights", us, mn, "tensor", 103079215104, 1e12, peaks["bf16_tflops"], "burst peak")
+    add("k_linear 4096x2048x6144 e4m3 weights", us, mn, "tensor", 103079215104, 1e12, peaks["bf16_tflops"],
+        "burst peak; weight expanded to bf16 once into a 25 MB scratch, then the bf16 CTA-pair GEMM (M > 256 route)")
+    us, mn = _graph_time_us(lambda: ops.linear_w8(xl, wq, s, out=yl, workspace=None), 20)
+    add("k_linear 4096x2048x6144 e4m3 weights, converted inside the main loop", us, mn, "tensor", 103079215104, 1e12,
+        peaks["bf16_tflops"], "burst peak; no scratch: every 128-row tile converts its weight tiles again")
     del xl, wl, w32, wq, yl
     # 4. SDPA B4 Hq16 Hkv8 S2048 D128
     q = torch.randn(4, 16, 2048, 128, device=dev, generator=g).bfloat16()

@@ -6,16 +6,20 @@ a captured CUDA graph per sequence (``emmy/serving/runner.py:204-236``); vLLM th
 (``emmy/serving/vllm_model.py:50-58``). The traced layer is GatherOp, five RMSNorm chains, seven LinearOps, a RoPE
 chain, repeat_kv, SdpaOp with an additive causal mask, and a SwiGLU — 18 generated kernels per layer.
 
-Here the same dataflow is a fixed plan of seven launches per layer over a whole batch of sequences:
+Here the same dataflow is a fixed plan of five launches per layer over a whole batch of sequences, with the two
+RMSNorms of a layer folded around the GEMMs (the producer's epilogue writes partial row sums of squares, the consumer
+scales its accumulator rows; the norm weight is folded into the projection):
 
-    rmsnorm -> GEMM(Wqkv) + q/k-norm + RoPE (epilogue) -> causal GQA flash attention (token-major, no transposes)
-            -> GEMM(Wo) + residual -> rmsnorm -> GEMM(Wgate|Wup interleaved) + SwiGLU -> GEMM(Wdown) + residual
+    GEMM(Wqkv * ln1) + rmsnorm-in + q/k-norm + RoPE (epilogue) -> causal GQA flash attention (token-major, no transposes)
+        -> GEMM(Wo) + residual + row sums of squares -> GEMM((Wgate|Wup interleaved) * ln2) + rmsnorm-in + SwiGLU
+        -> GEMM(Wdown) + residual + row sums of squares
 
-
-and a last-token RMSNorm + L2 kernel. The whole forward is captured once in a CUDA graph and replayed. Sequences are
-independent, so a batch can be processed in chunks (``chunk_seqs``) whose activations stay resident in the 126 MB L2.
-Weights are prepared once: q/k/v projections concatenated, gate/up rows interleaved, cos/sin tables rounded to bf16
-as the eager module does.
+preceded by the embedding gather (which also writes the first row sums of squares) and followed by a last-token
+RMSNorm + L2 kernel (``fold_rmsnorm=False`` keeps the two stand-alone RMSNorm kernels: seven launches per layer). The
+whole forward is captured once in a CUDA graph and replayed. Sequences are independent, so a batch can be processed in
+chunks (``chunk_seqs``). Weights are prepared once (:class:`EmbedWeights`) and shared by plans of different shapes,
+which take prefixes of one activation workspace (:class:`EmbedWorkspace`): q/k/v projections concatenated, gate/up
+rows interleaved, cos/sin tables rounded to bf16 as the eager module does.
 """
 
 from __future__ import annotations
