@@ -185,6 +185,31 @@ def lower(graph: Graph) -> CompiledPlan:
                 raise LoweringError(f"{node.id}: {op} in {dt} has no kernel")
             steps.append(PlanStep(_name("linear", node), entry, node.id, ins[: 3 if has_bias else 2],
                                   {"kn": kn, "has_bias": has_bias}))
+        elif op == "LoopOp":
+            # a Loop-IR kernel record of the reference (kernels/*.json): recognise the loop nest
+            from deplodock_b200 import loopir
+
+            try:
+                m = loopir.verify(graph, node.id, loopir.classify(graph, node.id))
+            except loopir.LoopRecordError as exc:
+                raise LoweringError(str(exc)) from exc
+            kname = f"k_{node.output.name}"
+            p = m.params
+            if m.kind == "rmsnorm":
+                steps.append(PlanStep(kname, "emk_rmsnorm", node.id, [src(p["x"]), src(p["weight"])],
+                                      {"eps": float(p["eps"])}))
+            elif m.kind in ("linear", "linear_residual", "silu_gate_linear"):
+                extra = [src(p[k]) for k in ("residual", "gate") if p[k] is not None]
+                steps.append(PlanStep(kname, "emk_loop_linear_f32", node.id, [src(p["x"]), src(p["w"]), *extra],
+                                      {"kind": m.kind, "M": p["M"], "N": p["N"], "K": p["K"], "x_inner": p["x_inner"],
+                                       "x_stride_outer": p["x_stride_outer"], "x_stride_m": p["x_stride_m"]}))
+            elif m.kind == "rope_scores":
+                steps.append(PlanStep(kname, "emk_loop_rope_scores_f32", node.id,
+                                      [src(p["q"]), src(p["k"]), src(p["cos"]), src(p["sin"])],
+                                      {k: p[k] for k in ("S", "H", "Hkv", "D", "scale", "mask_zero", "mask_fill")}))
+            else:  # softmax_pv
+                steps.append(PlanStep(kname, "emk_loop_softmax_pv_f32", node.id, [src(p["scores"]), src(p["v"])],
+                                      {k: p[k] for k in ("S", "H", "Hkv", "D")}))
         elif op == "SdpaOp":
             causal = bool(f.get("is_causal"))
             if len(ins) > 3:
@@ -327,6 +352,20 @@ class B200Backend(Backend):
                 y = fn(a[0], a[1], bias=a[2].reshape(-1) if s.attrs["has_bias"] else None, w_is_kn=s.attrs["kn"])
             elif s.entry == "emk_linear_f32_simt":
                 y = ops.linear_f32(a[0], a[1], a[2].reshape(-1) if s.attrs["has_bias"] else None, s.attrs["kn"])
+            elif s.entry == "emk_loop_linear_f32":
+                at = s.attrs
+                extra = a[2] if len(a) > 2 else None
+                y = ops.loop_linear_f32(a[0].reshape(-1), a[1], at["M"], at["N"], at["K"], x_inner=at["x_inner"],
+                                        x_stride_outer=at["x_stride_outer"], x_stride_m=at["x_stride_m"],
+                                        residual=extra if at["kind"] == "linear_residual" else None,
+                                        gate=extra if at["kind"] == "silu_gate_linear" else None)
+            elif s.entry == "emk_loop_rope_scores_f32":
+                at = s.attrs
+                y = ops.loop_rope_scores_f32(a[0], a[1], a[2], a[3], at["S"], at["H"], at["Hkv"], at["D"], at["scale"],
+                                             at["mask_zero"], at["mask_fill"])
+            elif s.entry == "emk_loop_softmax_pv_f32":
+                at = s.attrs
+                y = ops.loop_softmax_pv_f32(a[0], a[1], at["S"], at["H"], at["Hkv"], at["D"])
             elif s.entry == "emk_sdpa_causal_gqa_bf16":
                 y = ops.sdpa_causal_gqa(a[0], a[1], a[2])
             elif s.entry == "emk_sdpa_simt":

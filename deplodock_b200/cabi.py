@@ -77,6 +77,11 @@ _SIGNATURES: dict[str, list] = {
     "emk_linear_bf16_w8": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64,
                            c_void_p],
     "emk_linear_bf16_w8_workspace_bytes": [c_int64, c_int64],
+    "emk_loop_rope_scores_f32": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
+                                 c_int64, c_float, c_float, c_float, c_void_p],
+    "emk_loop_softmax_pv_f32": [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p],
+    "emk_loop_linear_f32": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
+                            c_int64, c_int64, c_int64, c_void_p],
     "emk_sdpa_causal_gqa_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                  c_int64, c_int64, c_float, c_void_p],
     "emk_sdpa_causal_gqa_bf16_tok": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,

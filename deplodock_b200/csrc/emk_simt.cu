@@ -4,6 +4,8 @@
 // tests/compiler/e2e/test_matmul_coverage.py:300,938-1068).
 #include "emk_common.cuh"
 
+#include <math_constants.h>
+
 namespace {
 
 using namespace emk;
@@ -134,7 +136,165 @@ __global__ void __launch_bounds__(256) gemm_f32_simt_kernel(const float* __restr
   }
 }
 
+// fp32 contraction of the Loop-IR kernel records (one LoopOp of the reference = one launch here):
+//   y[m,n] = epilogue( sum_k x[m,k] * W[n,k] ),  epilogue = identity | + r[m,n] | * silu(g[m,n]).
+// x[m,k] lives at (k / x_inner) * x_stride_outer + m * x_stride_m + k % x_inner, which covers the plain row-major
+// activation (x_inner = K) and the [K/D, M, D] head-major attention output the o_proj record reads through a
+// div/mod index. 32x32 output tile per CTA, K in steps of 32 through shared memory (coalesced loads of both operands),
+// accumulation in k order like the reference's serial reduce loop.
+__global__ void __launch_bounds__(1024) loop_linear_f32_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                               const float* __restrict__ residual,
+                                                               const float* __restrict__ gate, float* __restrict__ y,
+                                                               int64_t M, int64_t N, int64_t K, int64_t x_inner,
+                                                               int64_t x_stride_outer, int64_t x_stride_m) {
+  __shared__ float sx[32][33];
+  __shared__ float sw[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int64_t m0 = (int64_t)blockIdx.y * 32, n0 = (int64_t)blockIdx.x * 32;
+  float acc = 0.f;
+  for (int64_t k0 = 0; k0 < K; k0 += 32) {
+    const int64_t k = k0 + tx;
+    const int64_t m = m0 + ty, n = n0 + ty;
+    sx[ty][tx] = (m < M && k < K) ? x[(k / x_inner) * x_stride_outer + m * x_stride_m + k % x_inner] : 0.f;
+    sw[ty][tx] = (n < N && k < K) ? w[n * K + k] : 0.f;
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < 32; ++kk) acc = fmaf(sx[ty][kk], sw[tx][kk], acc);
+    __syncthreads();
+  }
+  const int64_t m = m0 + ty, n = n0 + tx;
+  if (m < M && n < N) {
+    const int64_t i = m * N + n;
+    if (residual != nullptr) acc = residual[i] + acc;
+    if (gate != nullptr) {
+      const float gv = gate[i];
+      acc = (gv * (1.0f / (1.0f + expf(-gv)))) * acc;   // x * reciprocal(1 + exp(-x)), as the record spells silu
+    }
+    y[i] = acc;
+  }
+}
+
+// The reference's unfused attention, first half (kernels/k_scaled_dot_product_attention_masked_reduce.json):
+//   s[h,i,j] = scale * sum_d rope(q)[i,h,d] * rope(k)[j,h/g,d] + (j <= i ? mask_zero : mask_fill),
+//   rope(x)[d] = x[d] * cos[pos,d] + (d < D/2 ? -x[d + D/2] : x[d - D/2]) * sin[pos,d].
+// q [S, H*D], k [S, Hkv*D], cos/sin [S, D], s [H, S, S]. One CTA per 32x32 tile of (i, j) and head: the rotated rows
+// are built once in shared memory, then every thread takes one dot product over d in ascending order.
+__global__ void __launch_bounds__(1024) loop_rope_scores_f32_kernel(const float* __restrict__ q, const float* __restrict__ k,
+                                                                   const float* __restrict__ cosb,
+                                                                   const float* __restrict__ sinb, float* __restrict__ y,
+                                                                   int S, int H, int Hkv, int D, float scale,
+                                                                   float mask_zero, float mask_fill) {
+  extern __shared__ float rs_smem[];
+  float* rq = rs_smem;                    // [32][D + 1]
+  float* rk = rs_smem + 32 * (D + 1);     // [32][D + 1]
+  const int h = blockIdx.z, hk = h / (H / Hkv);
+  const int i0 = blockIdx.y * 32, j0 = blockIdx.x * 32;
+  const int half = D / 2;
+  for (int e = threadIdx.x; e < 32 * D; e += blockDim.x) {
+    const int row = e / D, d = e % D;
+    const int dr = d < half ? d + half : d - half;
+    const int i = i0 + row, j = j0 + row;
+    float vq = 0.f, vk = 0.f;
+    if (i < S) {
+      const float* qr = q + (int64_t)i * H * D + (int64_t)h * D;
+      const float rot = d < half ? -qr[dr] : qr[dr];
+      vq = qr[d] * cosb[(int64_t)i * D + d] + rot * sinb[(int64_t)i * D + d];
+    }
+    if (j < S) {
+      const float* kr = k + (int64_t)j * Hkv * D + (int64_t)hk * D;
+      const float rot = d < half ? -kr[dr] : kr[dr];
+      vk = kr[d] * cosb[(int64_t)j * D + d] + rot * sinb[(int64_t)j * D + d];
+    }
+    rq[row * (D + 1) + d] = vq;
+    rk[row * (D + 1) + d] = vk;
+  }
+  __syncthreads();
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int i = i0 + ty, j = j0 + tx;
+  if (i < S && j < S) {
+    float acc = 0.f;
+    for (int d = 0; d < D; ++d) acc += rq[ty * (D + 1) + d] * rk[tx * (D + 1) + d];
+    y[((int64_t)h * S + i) * S + j] = acc * scale + (j <= i ? mask_zero : mask_fill);
+  }
+}
+
+// Second half (kernels/k_scaled_dot_product_attention_reduce_reduce.json):
+//   o[h,i,d] = sum_j (exp(s[h,i,j] - max_j s) / sum_j exp(s[h,i,j] - max_j s)) * v[j,h/g,d].
+// s [H, S, S], v [S, Hkv*D], o [H, S, D]. One warp per (h, i) row; the row's weights go through shared memory.
+__global__ void __launch_bounds__(256) loop_softmax_pv_f32_kernel(const float* __restrict__ sc, const float* __restrict__ v,
+                                                                 float* __restrict__ o, int S, int H, int Hkv, int D) {
+  extern __shared__ float pv_smem[];
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  float* p = pv_smem + wid * S;
+  const int64_t row = (int64_t)blockIdx.x * 8 + wid;
+  if (row >= (int64_t)H * S) return;
+  const int h = (int)(row / S), hk = h / (H / Hkv);
+  const float* srow = sc + row * S;
+  float mx = -CUDART_INF_F;
+  for (int j = lane; j < S; j += 32) mx = fmaxf(mx, srow[j]);
+  mx = warp_max(mx);
+  float sum = 0.f;
+  for (int j = lane; j < S; j += 32) {
+    const float e = expf(srow[j] - mx);
+    p[j] = e;
+    sum += e;
+  }
+  sum = warp_sum(sum);
+  __syncwarp();
+  for (int d = lane; d < D; d += 32) {
+    float acc = 0.f;
+    for (int j = 0; j < S; ++j) acc += (p[j] / sum) * v[(int64_t)j * Hkv * D + (int64_t)hk * D + d];
+    o[row * D + d] = acc;
+  }
+}
+
 }  // namespace
+
+extern "C" int emk_loop_rope_scores_f32(emk_handle_t h, const float* q, const float* k, const float* cosb,
+                                        const float* sinb, float* y, int64_t S, int64_t H, int64_t Hkv, int64_t D,
+                                        float scale, float mask_zero, float mask_fill, emk_stream_t stream) {
+  if (!h || !q || !k || !cosb || !sinb || !y) return EMK_ERR_ARG;
+  if (S <= 0 || H <= 0 || Hkv <= 0 || D <= 0 || (D % 2) != 0 || H % Hkv != 0) return EMK_ERR_SHAPE;
+  if (D > 128 || H > 65535 || S > 65535 * 32) return EMK_ERR_LIMIT;
+  const unsigned t = (unsigned)((S + 31) / 32);
+  const size_t smem = (size_t)2 * 32 * (D + 1) * sizeof(float);
+  loop_rope_scores_f32_kernel<<<dim3(t, t, (unsigned)H), 1024, smem, (cudaStream_t)stream>>>(
+      q, k, cosb, sinb, y, (int)S, (int)H, (int)Hkv, (int)D, scale, mask_zero, mask_fill);
+  EMK_LAUNCH_CHECK(h);
+  return EMK_OK;
+}
+
+extern "C" int emk_loop_softmax_pv_f32(emk_handle_t h, const float* scores, const float* v, float* o, int64_t S,
+                                       int64_t H, int64_t Hkv, int64_t D, emk_stream_t stream) {
+  if (!h || !scores || !v || !o) return EMK_ERR_ARG;
+  if (S <= 0 || H <= 0 || Hkv <= 0 || D <= 0 || H % Hkv != 0) return EMK_ERR_SHAPE;
+  if (S > 1536) {
+    EMK_SET_ERR(h, "emk_loop_softmax_pv_f32: row length %lld exceeds the 1536 floats per warp of shared memory",
+                (long long)S);
+    return EMK_ERR_LIMIT;
+  }
+  const int64_t blocks = (H * S + 7) / 8;
+  if (blocks > 0x7fffffffLL) return EMK_ERR_SHAPE;
+  loop_softmax_pv_f32_kernel<<<(unsigned)blocks, 256, (size_t)8 * S * sizeof(float), (cudaStream_t)stream>>>(
+      scores, v, o, (int)S, (int)H, (int)Hkv, (int)D);
+  EMK_LAUNCH_CHECK(h);
+  return EMK_OK;
+}
+
+extern "C" int emk_loop_linear_f32(emk_handle_t h, const float* x, const float* w, const float* residual,
+                                   const float* gate, float* y, int64_t M, int64_t N, int64_t K, int64_t x_inner,
+                                   int64_t x_stride_outer, int64_t x_stride_m, emk_stream_t stream) {
+  if (!h || !x || !w || !y) return EMK_ERR_ARG;
+  if (M <= 0 || N <= 0 || K <= 0 || x_inner <= 0 || K % x_inner != 0 || x_stride_m <= 0 || x_stride_outer < 0)
+    return EMK_ERR_SHAPE;
+  if (residual != nullptr && gate != nullptr) return EMK_ERR_ARG;
+  const int64_t gx = (N + 31) / 32, gy = (M + 31) / 32;
+  if (gx > 0x7fffffffLL || gy > 65535) return EMK_ERR_SHAPE;
+  loop_linear_f32_kernel<<<dim3((unsigned)gx, (unsigned)gy), 1024, 0, (cudaStream_t)stream>>>(
+      x, w, residual, gate, y, M, N, K, x_inner, x_stride_outer, x_stride_m);
+  EMK_LAUNCH_CHECK(h);
+  return EMK_OK;
+}
 
 extern "C" int emk_linear_bf16_simt(emk_handle_t h, const void* x, const void* w, const void* residual, void* y,
                                     int64_t M, int64_t N, int64_t K, int wlayout, int epilogue, emk_stream_t stream) {

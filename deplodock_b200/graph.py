@@ -28,6 +28,9 @@ DTYPES: dict[str, tuple[np.dtype, int]] = {
 }
 
 
+_DTYPE_ALIASES = {"float32": "f32", "float16": "f16", "bfloat16": "bf16", "int64": "i64", "int32": "i32"}
+
+
 @dataclass(frozen=True)
 class TensorInfo:
     name: str
@@ -65,10 +68,14 @@ class Graph:
                 if not isinstance(dim, int):
                     raise ValueError(f"node {nid!r}: symbolic dimension {dim!r} is not supported by this backend")
                 shape.append(int(dim))
-            dtype = out["dtype"]
+            dtype = _DTYPE_ALIASES.get(out["dtype"], out["dtype"])   # older records spell the numpy name
             if dtype not in DTYPES:
                 raise TypeError(f"node {nid!r}: unknown dtype token {dtype!r}")
-            nodes[nid] = Node(nid, nd["op"], dict(nd.get("op_fields") or {}), list(nd.get("inputs") or []),
+            fields = dict(nd.get("op_fields") or {})
+            if nd["op"] == "ConstantOp" and isinstance(fields.get("value"), str):
+                # Loop-IR records carry constant values as strings ('None', '1e-05')
+                fields["value"] = None if fields["value"] == "None" else float(fields["value"])
+            nodes[nid] = Node(nid, nd["op"], fields, list(nd.get("inputs") or []),
                               TensorInfo(out.get("name", nid), tuple(shape), dtype))
         g = cls(list(d["inputs"]), list(d["outputs"]), nodes)
         for nid in g.inputs + g.outputs:

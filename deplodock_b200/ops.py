@@ -241,6 +241,62 @@ def linear_f32(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = Non
     return y
 
 
+def loop_linear_f32(x: torch.Tensor, w: torch.Tensor, M: int, N: int, K: int, *, x_inner: int | None = None,
+                    x_stride_outer: int = 0, x_stride_m: int | None = None, residual=None, gate=None,
+                    out=None) -> torch.Tensor:
+    """The fp32 contraction of the Loop-IR kernel records: ``y[m,n] = e(sum_k x[m,k] * w[n,k])`` with the blocked
+    activation addressing ``(k // x_inner) * x_stride_outer + m * x_stride_m + k % x_inner`` and the epilogue
+    ``+ residual`` or ``* silu(gate)`` (see ``emk_loop_linear_f32``). ``x`` is taken as a flat buffer."""
+    _check_cuda_contig(x, w, residual, gate, out)
+    for t in (x, w, residual, gate):
+        if t is not None and t.dtype != torch.float32:
+            raise TypeError("loop_linear_f32 expects float32 tensors")
+    x_inner = K if x_inner is None else int(x_inner)
+    x_stride_m = K if x_stride_m is None else int(x_stride_m)
+    need = (K // x_inner - 1) * x_stride_outer + (M - 1) * x_stride_m + x_inner
+    if x.numel() < need or tuple(w.shape) != (N, K):
+        raise ValueError("operand sizes do not match the addressing")
+    for t in (residual, gate):
+        if t is not None and t.numel() != M * N:
+            raise ValueError("epilogue operand must hold M * N elements")
+    y = torch.empty(M, N, dtype=torch.float32, device=x.device) if out is None else out
+    h = handle()
+    h.check(h.lib.emk_loop_linear_f32(h.ptr, _ptr(x), _ptr(w), _ptr(residual), _ptr(gate), _ptr(y), M, N, K, x_inner,
+                                      int(x_stride_outer), x_stride_m, _stream()), "emk_loop_linear_f32")
+    return y
+
+
+def loop_rope_scores_f32(q, k, cos, sin, S: int, H: int, Hkv: int, D: int, scale: float, mask_zero: float,
+                         mask_fill: float) -> torch.Tensor:
+    """First half of the reference's unfused attention record: RoPE on q and k, scaled dot products, causal fill;
+    ``[H, S, S]`` fp32 (see ``emk_loop_rope_scores_f32``)."""
+    _check_cuda_contig(q, k, cos, sin)
+    if any(t.dtype != torch.float32 for t in (q, k, cos, sin)):
+        raise TypeError("loop_rope_scores_f32 expects float32 tensors")
+    if q.numel() != S * H * D or k.numel() != S * Hkv * D or cos.numel() != S * D or sin.numel() != S * D:
+        raise ValueError("operand sizes do not match S, H, Hkv, D")
+    y = torch.empty(H, S, S, dtype=torch.float32, device=q.device)
+    h = handle()
+    h.check(h.lib.emk_loop_rope_scores_f32(h.ptr, _ptr(q), _ptr(k), _ptr(cos), _ptr(sin), _ptr(y), S, H, Hkv, D,
+                                           float(scale), float(mask_zero), float(mask_fill), _stream()),
+            "emk_loop_rope_scores_f32")
+    return y
+
+
+def loop_softmax_pv_f32(scores, v, S: int, H: int, Hkv: int, D: int) -> torch.Tensor:
+    """Second half: row softmax of ``[H, S, S]`` scores times ``v [S, Hkv*D]`` -> ``[H, S, D]`` fp32."""
+    _check_cuda_contig(scores, v)
+    if scores.dtype != torch.float32 or v.dtype != torch.float32:
+        raise TypeError("loop_softmax_pv_f32 expects float32 tensors")
+    if scores.numel() != H * S * S or v.numel() != S * Hkv * D:
+        raise ValueError("operand sizes do not match S, H, Hkv, D")
+    o = torch.empty(H, S, D, dtype=torch.float32, device=scores.device)
+    h = handle()
+    h.check(h.lib.emk_loop_softmax_pv_f32(h.ptr, _ptr(scores), _ptr(v), _ptr(o), S, H, Hkv, D, _stream()),
+            "emk_loop_softmax_pv_f32")
+    return o
+
+
 _W8_SCRATCH: dict[int, torch.Tensor] = {}
 
 

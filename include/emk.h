@@ -218,6 +218,29 @@ int emk_linear_bf16_simt(emk_handle_t h, const void* x, const void* w, const voi
 int emk_linear_f32_simt(emk_handle_t h, const float* x, const float* w, const float* bias, float* y, int64_t M,
                         int64_t N, int64_t K, int wlayout, emk_stream_t stream);
 
+/* The fp32 contraction behind the reference's Loop-IR kernel records (kernels/k_linear_*_reduce*.json,
+ * k_add_3_reduce.json, k_add_5_reduce.json, k_mul_8_reduce.json; LoopOp bodies as in
+ * emmy/compiler/ir/stmt/leaves.py:96-469): y[m,n] = e(sum_k x[m,k] * W[n,k]) with W [N,K] row-major, y and the
+ * optional epilogue operand [M,N] row-major, e = identity, "+ residual[m,n]" or "* silu(gate[m,n])" (at most one of
+ * residual / gate non-NULL). x[m,k] is read at (k / x_inner) * x_stride_outer + m * x_stride_m + k % x_inner:
+ * (K, 0, K) for a row-major activation, (D, M*D, D) for the [heads, M, D] attention output the o_proj record reads. */
+int emk_loop_linear_f32(emk_handle_t h, const float* x, const float* w, const float* residual, const float* gate,
+                        float* y, int64_t M, int64_t N, int64_t K, int64_t x_inner, int64_t x_stride_outer,
+                        int64_t x_stride_m, emk_stream_t stream);
+
+/* The two halves of the reference's unfused attention lowering, as its Loop-IR records state them
+ * (kernels/k_scaled_dot_product_attention_masked_reduce.json, ..._reduce_reduce.json), fp32:
+ *   scores[h,i,j] = scale * sum_d rope(q)[i,h,d] * rope(k)[j,h/g,d] + (j <= i ? mask_zero : mask_fill),
+ *   rope(x)[d] = x[d] * cos[pos,d] + (d < D/2 ? -x[d+D/2] : x[d-D/2]) * sin[pos,d];
+ *   o[h,i,d] = sum_j softmax_j(scores[h,i,:])[j] * v[j,h/g,d].
+ * q [S,H*D], k and v [S,Hkv*D], cos/sin [S,D], scores [H,S,S], o [H,S,D]; g = H/Hkv; D even and <= 128 for the
+ * scores, S <= 1536 for the second half (EMK_ERR_LIMIT beyond). */
+int emk_loop_rope_scores_f32(emk_handle_t h, const float* q, const float* k, const float* cos_table,
+                             const float* sin_table, float* scores, int64_t S, int64_t H, int64_t Hkv, int64_t D,
+                             float scale, float mask_zero, float mask_fill, emk_stream_t stream);
+int emk_loop_softmax_pv_f32(emk_handle_t h, const float* scores, const float* v, float* o, int64_t S, int64_t H,
+                            int64_t Hkv, int64_t D, emk_stream_t stream);
+
 /* Generic attention on CUDA cores (one warp per query row, fp32 online softmax): any head_dim <= 256, causal or
  * full, EMK_F32 or EMK_BF16, q/o [B,Hq,Sq,D], k/v [B,Hkv,Skv,D] contiguous. Takes the SdpaOp shapes the tensor-core
  * kernel rejects (fp32 inputs, head_dim != 128, non-causal: the reference's scalar flash tier,

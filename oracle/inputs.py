@@ -138,3 +138,28 @@ def rope_tables(seq: int, head_dim: int = 128, theta: float = 1e6):
 
 def sdpa_scale(head_dim: int) -> float:
     return 1.0 / math.sqrt(head_dim)
+
+
+def loop_record_inputs(record: dict, seed: int = 0) -> dict[str, "np.ndarray"]:
+    """Seeded fp32 inputs for a Loop-IR kernel record (``kernels/*.json`` of the reference): scalar constants take their
+    recorded value, weight constants (``value`` None) are N(0, 0.02) (1 + N(0, 0.02) for 1-D norm weights), rotary
+    tables are uniform in [-1, 1], every other input is N(0, 1). One generator, node order of the record."""
+    import numpy as np
+
+    rng = np.random.default_rng(seed)
+    out = {}
+    for nid, node in record["nodes"].items():
+        if node["op"] not in ("InputOp", "ConstantOp"):
+            continue
+        shape = tuple(int(d) for d in node["output"]["shape"])
+        value = node.get("op_fields", {}).get("value")
+        if node["op"] == "ConstantOp" and value not in (None, "None"):
+            out[nid] = np.full(shape, float(value), dtype=np.float32)
+        elif node["op"] == "ConstantOp":
+            w = rng.standard_normal(shape).astype(np.float32) * np.float32(0.02)
+            out[nid] = (w + np.float32(1.0)) if len(shape) == 1 else w
+        elif "position_embeddings" in nid:
+            out[nid] = rng.uniform(-1.0, 1.0, shape).astype(np.float32)
+        else:
+            out[nid] = rng.standard_normal(shape).astype(np.float32)
+    return out

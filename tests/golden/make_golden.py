@@ -120,6 +120,11 @@ def main() -> None:
     if "--only-qwen3" in sys.argv:
         _qwen3_layer_case()
         return
+    if "--only-loop-records" in sys.argv:
+        import emmy
+
+        _loop_records(Path(emmy.__file__).resolve().parent.parent)
+        return
     for name, code in CASES.items():
         graph, input_data, outputs = _trace_and_run(code)
         arrays = {f"in__{k}": _to_np(v) for k, v in input_data.items()}
@@ -135,6 +140,53 @@ def main() -> None:
         (HERE / "graphs" / f"{name}.json").write_text(json.dumps(graph.to_dict(), indent=1))
         print(name, "record only")
     _qwen3_layer_case()
+    import emmy
+
+    _loop_records(Path(emmy.__file__).resolve().parent.parent)
+
+
+def _loop_records(reference_root: Path):
+    """The reference's shipped Loop-IR kernel records (``kernels/*.json``): copied as fixtures, and for each one the
+    output of the reference's own LoopOp -> C++ renderer (``emmy/compiler/ir/loop/runner.py:56-78``) compiled with g++
+    on the seeded inputs of ``oracle.inputs.loop_record_inputs``. The outputs are up to 2 MB each, so a strided sample
+    (every ``stride``-th element) and two checksums are stored."""
+    import ctypes
+    import shutil
+    import subprocess
+    import tempfile
+
+    from emmy.compiler.graph import Graph
+    from emmy.compiler.ir.loop.runner import PRELUDE, render_loopop_cpp
+
+    sys.path.insert(0, str(HERE.parent.parent))
+    from oracle.inputs import loop_record_inputs
+
+    dst = HERE / "loop_records"
+    dst.mkdir(exist_ok=True)
+    for i, path in enumerate(sorted((reference_root / "kernels").glob("*.json"))):
+        shutil.copyfile(path, dst / path.name)
+        record = json.loads(path.read_text())
+        graph = Graph.from_dict(record)
+        nid, node = next((n, v) for n, v in graph.nodes.items() if type(v.op).__name__ == "LoopOp")
+        loop = node.op
+        shapes = {name: tuple(int(d.as_static()) for d in graph.nodes[name].output.shape) for name in loop.inputs}
+        out_shape = tuple(int(d.as_static()) for d in node.output.shape)
+        text = PRELUDE + render_loopop_cpp(loop, "k", shapes, out_shape)
+        data = loop_record_inputs(record, seed=i)
+        with tempfile.TemporaryDirectory() as td:
+            src, lib = Path(td) / "k.cpp", Path(td) / "k.so"
+            src.write_text(text)
+            subprocess.run(["g++", "-O2", "-shared", "-fPIC", "-o", str(lib), str(src)], check=True)
+            fn = ctypes.CDLL(str(lib)).k
+            out = np.zeros(out_shape, dtype=np.float32)
+            args = [np.ascontiguousarray(data[name]) for name in loop.inputs]
+            fn(*[a.ctypes.data_as(ctypes.c_void_p) for a in args], out.ctypes.data_as(ctypes.c_void_p))
+        flat = out.ravel()
+        stride = max(1, flat.size // 4096)
+        np.savez_compressed(dst / f"{path.stem}.npz", sample=flat[::stride], stride=np.int64(stride), seed=np.int64(i),
+                            sum=np.float64(flat.astype(np.float64).sum()),
+                            abs_sum=np.float64(np.abs(flat.astype(np.float64)).sum()))
+        print(path.stem, out_shape, "stride", stride, "sum", float(flat.astype(np.float64).sum()))
 
 
 if __name__ == "__main__":
