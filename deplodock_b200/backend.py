@@ -143,10 +143,24 @@ def _is_causal_mask_const(g: Graph, nid: str) -> bool:
     return n.op == "ConstantOp" and "causal_mask" in str(n.op_fields.get("source_path") or n.id)
 
 
+def _consumers(g: Graph, nid: str) -> list[str]:
+    return [n.id for n in g.nodes.values() if nid in n.inputs]
+
+
+def _sole_consumer_is_multiply(g: Graph, nid: str) -> bool:
+    cons = _consumers(g, nid)
+    if len(cons) != 1 or nid in g.outputs:
+        return False
+    c = g.nodes[cons[0]]
+    return c.op == "ElementwiseOp" and c.op_fields.get("op") == "multiply" and all(
+        g.nodes[i].output.shape == c.output.shape for i in c.inputs)
+
+
 def lower(graph: Graph) -> CompiledPlan:
     """Op-by-op dispatch of a Torch-IR graph onto C-ABI entry points."""
     steps: list[PlanStep] = []
     aliases: dict[str, str] = {}
+    silu_of: dict[str, str] = {}   # silu nodes folded into their consuming multiply -> their operand
 
     def src(nid: str) -> str:
         while nid in aliases:
@@ -185,6 +199,35 @@ def lower(graph: Graph) -> CompiledPlan:
                 raise LoweringError(f"{node.id}: {op} in {dt} has no kernel")
             steps.append(PlanStep(_name("linear", node), entry, node.id, ins[: 3 if has_bias else 2],
                                   {"kn": kn, "has_bias": has_bias}))
+        elif op == "ElementwiseOp":
+            name = str(f.get("op"))
+            shapes = [graph.nodes[i].output.shape for i in ins]
+            if dt not in ("f32", "bf16") or name not in ("add", "multiply", "silu") or any(
+                    sh != node.output.shape for sh in shapes):
+                raise LoweringError(f"{node.id}: ElementwiseOp {name!r} on shapes {shapes} ({dt}) has no kernel "
+                                    "(same-shape add / multiply / silu only)")
+            if name == "silu" and _sole_consumer_is_multiply(graph, node.id):
+                silu_of[node.id] = ins[0]   # folded into the multiply that consumes it
+                continue
+            if name == "multiply" and any(graph.nodes[i].id in silu_of for i in node.inputs):
+                si = next(i for i in node.inputs if i in silu_of)
+                other = next(i for i in node.inputs if i != si)
+                steps.append(PlanStep(_name("silu_mul", node), "emk_elementwise", node.id, [silu_of[si], src(other)],
+                                      {"op": "silu_multiply"}))
+                continue
+            # y = matmul(...) + r in bf16: the add becomes the GEMM's residual epilogue when it is the product's only use
+            if name == "add" and dt == "bf16":
+                prod = next((st for st in steps if st.out in ins and st.entry == "emk_linear_bf16"
+                             and not st.attrs["has_bias"] and "residual" not in st.attrs
+                             and _consumers(graph, st.out) == [node.id]), None)
+                if prod is not None:
+                    other = next(i for i in ins if i != prod.out)
+                    prod.args.append(other)
+                    prod.attrs["residual"] = True
+                    aliases[node.id] = prod.out
+                    continue
+            steps.append(PlanStep(_name(name, node), "emk_elementwise", node.id, ins[: 1 if name == "silu" else 2],
+                                  {"op": name}))
         elif op == "LoopOp":
             # a Loop-IR kernel record of the reference (kernels/*.json): recognise the loop nest
             from deplodock_b200 import loopir
@@ -349,7 +392,11 @@ class B200Backend(Backend):
                 y = ops.softmax_lastdim(a[0])
             elif s.entry in ("emk_linear_bf16", "emk_linear_bf16_simt"):
                 fn = ops.linear if s.entry == "emk_linear_bf16" else ops.linear_simt
-                y = fn(a[0], a[1], bias=a[2].reshape(-1) if s.attrs["has_bias"] else None, w_is_kn=s.attrs["kn"])
+                if s.attrs.get("residual"):
+                    y = fn(a[0], a[1], residual=a[2].reshape(-1, a[1].shape[1 if s.attrs["kn"] else 0]).contiguous(),
+                           w_is_kn=s.attrs["kn"])
+                else:
+                    y = fn(a[0], a[1], bias=a[2].reshape(-1) if s.attrs["has_bias"] else None, w_is_kn=s.attrs["kn"])
             elif s.entry == "emk_linear_f32_simt":
                 y = ops.linear_f32(a[0], a[1], a[2].reshape(-1) if s.attrs["has_bias"] else None, s.attrs["kn"])
             elif s.entry == "emk_loop_linear_f32":
@@ -359,6 +406,8 @@ class B200Backend(Backend):
                                         x_stride_outer=at["x_stride_outer"], x_stride_m=at["x_stride_m"],
                                         residual=extra if at["kind"] == "linear_residual" else None,
                                         gate=extra if at["kind"] == "silu_gate_linear" else None)
+            elif s.entry == "emk_elementwise":
+                y = ops.elementwise(s.attrs["op"], a[0].contiguous(), a[1].contiguous() if len(a) > 1 else None)
             elif s.entry == "emk_loop_rope_scores_f32":
                 at = s.attrs
                 y = ops.loop_rope_scores_f32(a[0], a[1], a[2], a[3], at["S"], at["H"], at["Hkv"], at["D"], at["scale"],

@@ -26,6 +26,7 @@ EMK_ERR_ARG = 7
 EMK_ERR_LIMIT = 8
 
 EMK_F32, EMK_BF16, EMK_F16 = 0, 1, 2
+EMK_EW_ADD, EMK_EW_MUL, EMK_EW_SILU, EMK_EW_SILU_MUL = 0, 1, 2, 3
 EMK_W_NK, EMK_W_KN = 0, 1
 EMK_EPI_NONE, EMK_EPI_RESIDUAL, EMK_EPI_SWIGLU, EMK_EPI_BIAS, EMK_EPI_QKNORM_ROPE = 0, 1, 2, 3, 4
 
@@ -77,6 +78,7 @@ _SIGNATURES: dict[str, list] = {
     "emk_linear_bf16_w8": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64,
                            c_void_p],
     "emk_linear_bf16_w8_workspace_bytes": [c_int64, c_int64],
+    "emk_elementwise": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p],
     "emk_loop_rope_scores_f32": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                  c_int64, c_float, c_float, c_float, c_void_p],
     "emk_loop_softmax_pv_f32": [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p],

@@ -159,6 +159,57 @@ __global__ void __launch_bounds__(256) pool_norm_l2_kernel(const __nv_bfloat16* 
   }
 }
 
+// Same-shape pointwise ops of the frontend IR (ElementwiseOp add / multiply / silu, emmy/compiler/ir/tensor/ir.py;
+// silu decomposed by the reference as x * reciprocal(1 + exp(-x)), .../decomposition/020_silu.py:11-36), with
+// silu(a) * b as one fused form. 16 bytes per thread and step; fp32 math; bf16 results rounded once.
+template <typename T, int OP>
+__device__ __forceinline__ float ew_apply(float a, float b) {
+  if (OP == EMK_EW_ADD) return a + b;
+  if (OP == EMK_EW_MUL) return a * b;
+  const float sa = a * (1.0f / (1.0f + expf(-a)));
+  return OP == EMK_EW_SILU ? sa : sa * b;
+}
+
+template <typename T, int OP>
+__global__ void __launch_bounds__(256) elementwise_kernel(const T* __restrict__ a, const T* __restrict__ b,
+                                                          T* __restrict__ y, int64_t n) {
+  constexpr int V = 16 / (int)sizeof(T);
+  const int64_t nvec = n / V;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+    const uint4 va = reinterpret_cast<const uint4*>(a)[i];
+    uint4 vb = va;
+    if (OP != EMK_EW_SILU) vb = reinterpret_cast<const uint4*>(b)[i];
+    uint4 vy;
+    const T* pa = reinterpret_cast<const T*>(&va);
+    const T* pb = reinterpret_cast<const T*>(&vb);
+    T* py = reinterpret_cast<T*>(&vy);
+#pragma unroll
+    for (int e = 0; e < V; ++e) py[e] = (T)ew_apply<T, OP>((float)pa[e], (float)pb[e]);
+    reinterpret_cast<uint4*>(y)[i] = vy;
+  }
+  for (int64_t i = nvec * V + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+    y[i] = (T)ew_apply<T, OP>((float)a[i], OP != EMK_EW_SILU ? (float)b[i] : 0.f);
+}
+
+template <typename T>
+int elementwise_launch(emk_handle_t h, int op, const void* a, const void* b, void* y, int64_t n, cudaStream_t s) {
+  int64_t blocks = (n / (16 / (int64_t)sizeof(T)) + 255) / 256;
+  if (blocks < 1) blocks = 1;
+  if (blocks > (int64_t)h->sm_count * 16) blocks = (int64_t)h->sm_count * 16;
+  const T *pa = (const T*)a, *pb = (const T*)b;
+  T* py = (T*)y;
+  switch (op) {
+    case EMK_EW_ADD: elementwise_kernel<T, EMK_EW_ADD><<<(unsigned)blocks, 256, 0, s>>>(pa, pb, py, n); break;
+    case EMK_EW_MUL: elementwise_kernel<T, EMK_EW_MUL><<<(unsigned)blocks, 256, 0, s>>>(pa, pb, py, n); break;
+    case EMK_EW_SILU: elementwise_kernel<T, EMK_EW_SILU><<<(unsigned)blocks, 256, 0, s>>>(pa, pb, py, n); break;
+    case EMK_EW_SILU_MUL: elementwise_kernel<T, EMK_EW_SILU_MUL><<<(unsigned)blocks, 256, 0, s>>>(pa, pb, py, n); break;
+    default: return EMK_ERR_ARG;
+  }
+  EMK_LAUNCH_CHECK(h);
+  return EMK_OK;
+}
+
 }  // namespace
 
 extern "C" int emk_embed_gather_sumsq(emk_handle_t h, const void* table, const int64_t* ids, void* out, float* row_sumsq,
@@ -208,4 +259,14 @@ extern "C" int emk_pool_norm_l2(emk_handle_t h, const void* hidden_states, const
                                         (const __nv_bfloat16*)w, out, (int)S, (int)hidden, eps));
   EMK_LAUNCH_CHECK(h);
   return EMK_OK;
+}
+
+extern "C" int emk_elementwise(emk_handle_t h, int op, const void* a, const void* b, void* y, int64_t n, int dtype,
+                               emk_stream_t stream) {
+  if (!h || !a || !y || (op != EMK_EW_SILU && !b)) return EMK_ERR_ARG;
+  if (n <= 0) return EMK_ERR_SHAPE;
+  if ((((uintptr_t)a | (uintptr_t)b | (uintptr_t)y) & 15u) != 0) return EMK_ERR_ALIGN;
+  if (dtype == EMK_F32) return elementwise_launch<float>(h, op, a, b, y, n, (cudaStream_t)stream);
+  if (dtype == EMK_BF16) return elementwise_launch<__nv_bfloat16>(h, op, a, b, y, n, (cudaStream_t)stream);
+  return EMK_ERR_DTYPE;
 }

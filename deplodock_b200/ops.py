@@ -241,6 +241,26 @@ def linear_f32(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = Non
     return y
 
 
+_EW_OPS = {"add": cabi.EMK_EW_ADD, "multiply": cabi.EMK_EW_MUL, "silu": cabi.EMK_EW_SILU, "silu_multiply": cabi.EMK_EW_SILU_MUL}
+
+
+def elementwise(op: str, a: torch.Tensor, b: torch.Tensor | None = None, out=None) -> torch.Tensor:
+    """Same-shape ``add`` / ``multiply`` / ``silu`` / ``silu_multiply`` (= ``silu(a) * b``) in fp32 or bf16."""
+    _check_cuda_contig(a, b, out)
+    if op not in _EW_OPS:
+        raise ValueError(f"unknown elementwise op {op!r}")
+    if a.dtype not in (torch.float32, torch.bfloat16) or (b is not None and b.dtype != a.dtype):
+        raise TypeError("elementwise expects float32 or bfloat16 operands of one dtype")
+    if op != "silu" and (b is None or tuple(b.shape) != tuple(a.shape)):
+        raise ValueError("elementwise operands must have the same shape (no broadcasting)")
+    y = torch.empty_like(a) if out is None else out
+    h = handle()
+    h.check(h.lib.emk_elementwise(h.ptr, _EW_OPS[op], _ptr(a), _ptr(b), _ptr(y), a.numel(),
+                                  cabi.EMK_F32 if a.dtype == torch.float32 else cabi.EMK_BF16, _stream()),
+            "emk_elementwise")
+    return y
+
+
 def loop_linear_f32(x: torch.Tensor, w: torch.Tensor, M: int, N: int, K: int, *, x_inner: int | None = None,
                     x_stride_outer: int = 0, x_stride_m: int | None = None, residual=None, gate=None,
                     out=None) -> torch.Tensor:

@@ -209,6 +209,11 @@ def trace_module(module: torch.nn.Module, args: tuple, kwargs: dict | None = Non
                 ins = [a[0].name, a[1].name, a[2].name] + ([mask.name] if mask is not None else [])
                 const_scalar(node.name, 3, 0.0)
                 add(node.name, "SdpaOp", {"is_causal": is_causal}, ins, shape, dtype)
+            elif target.startswith(("aten.add.Tensor", "aten.mul.Tensor", "aten.silu.")) and all(
+                    hasattr(x, "name") for x in a[:1 if "silu" in target else 2]):
+                # same names as the reference's ElementwiseOp (emmy/compiler/trace/torch.py:506-523)
+                name = "silu" if "silu" in target else ("add" if "add" in target else "multiply")
+                add(node.name, "ElementwiseOp", {"op": name}, tin[:1 if name == "silu" else 2], shape, dtype)
             elif target.startswith(_PASSTHROUGH_TARGETS):
                 add(node.name, "ToOp", {}, tin[:1], shape, dtype)
             elif target.startswith(_VIEW_TARGETS):

@@ -201,6 +201,14 @@ int emk_qknorm_rope(emk_handle_t h, void* qkv, const void* qw, const void* kw, c
                     const void* sin_table, int64_t tokens, int64_t S, int64_t Hq, int64_t Hkv, float eps,
                     emk_stream_t stream);
 
+/* Same-shape pointwise ops that reach the backend as Torch-IR nodes of their own (the reference's perf suite drives
+ * `torch.matmul(x,w)+r` and `F.silu(x@wg)*(x@wu)`, tests/perf/cases.py:60-74; ElementwiseOp add / multiply / silu):
+ * y = a + b, a * b, silu(a), or silu(a) * b; n elements of `dtype` (EMK_F32 or EMK_BF16), no broadcasting.
+ * Inside the model plan these are GEMM epilogues instead. */
+typedef enum { EMK_EW_ADD = 0, EMK_EW_MUL = 1, EMK_EW_SILU = 2, EMK_EW_SILU_MUL = 3 } emk_elementwise_op_t;
+int emk_elementwise(emk_handle_t h, int op, const void* a, const void* b, void* y, int64_t n, int dtype,
+                    emk_stream_t stream);
+
 /* Last-token pooling + final RMSNorm + L2 normalisation: for each sequence b, takes row (b*S + S-1) of hidden
  * [B*S, hidden] (bf16), applies RMSNorm(w, eps) rounding to bf16 as the eager module does, then divides by its L2
  * norm; writes fp32 [B, hidden]. Stands for the final norm of the trunk plus the pooler the reference leaves to

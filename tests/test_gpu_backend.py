@@ -24,7 +24,8 @@ def backend(libemk):
 @pytest.mark.parametrize("case,rtol,atol", [
     ("rmsnorm_f32", 1e-5, 1e-6), ("rmsnorm_readme_shape", 1e-5, 1e-6), ("softmax_f32", 1e-5, 1e-7),
     ("linear_f32", 1e-4, 2e-6), ("linear_bias_f32", 1e-4, 2e-6), ("matmul_f32", 5e-5, 2e-6),
-    ("sdpa_causal_gqa_f32", 5e-5, 2e-6), ("sdpa_full_f32", 5e-5, 2e-6), ("sdpa_causal_gqa_d128_f32", 5e-5, 2e-6)])
+    ("sdpa_causal_gqa_f32", 5e-5, 2e-6), ("sdpa_full_f32", 5e-5, 2e-6), ("sdpa_causal_gqa_d128_f32", 5e-5, 2e-6),
+    ("swiglu_f32", 1e-4, 1e-4)])
 def test_run_matches_reference_fixture(backend, case, rtol, atol):
     """Tolerances are the reference's per-op ones (tests/compiler/e2e/test_ops_vs_torch.py:303-449) or tighter."""
     ins, outs = load_golden(case)

@@ -57,8 +57,9 @@ def test_kernel_names_are_stable_across_processes():
 def test_unsupported_ops_raise_lowering_error():
     from deplodock_b200.backend import B200Backend, LoweringError
 
-    with pytest.raises(LoweringError):
-        B200Backend().compile(GOLDEN / "graphs" / "swiglu_f32.json")  # elementwise chain: no standalone kernel
+    plan = B200Backend().compile(GOLDEN / "graphs" / "swiglu_f32.json")   # silu folded into the multiply
+    assert [s.entry for s in plan.steps] == ["emk_linear_f32_simt", "emk_linear_f32_simt", "emk_elementwise"]
+    assert plan.steps[2].attrs == {"op": "silu_multiply"} and plan.steps[2].args == ["matmul", "matmul_1"]
     rec = {"inputs": ["x"], "outputs": ["s"], "nodes": {
         "x": {"op": "InputOp", "op_fields": {}, "inputs": [], "output": {"name": "x", "shape": [4, 8], "dtype": "f32"}},
         "s": {"op": "SoftmaxOp", "op_fields": {"axis": 0}, "inputs": ["x"],

@@ -34,7 +34,7 @@ CODES = _golden_codes()
 _KERNEL_OPS = {"RmsNormOp", "SoftmaxOp", "LinearOp", "MatmulOp", "SdpaOp"}
 
 
-@pytest.mark.parametrize("name", [n for n in CODES if n != "swiglu_f32"])
+@pytest.mark.parametrize("name", list(CODES))
 def test_tracer_matches_reference_records(name):
     ref = json.loads((GOLDEN / "graphs" / f"{name}.json").read_text())
     got = trace_inline_code(CODES[name]).graph.to_dict()
@@ -44,23 +44,36 @@ def test_tracer_matches_reference_records(name):
     def essentials(d):
         out = {}
         for nid, n in d["nodes"].items():
-            if n["op"] in _KERNEL_OPS or n["op"] == "InputOp" or (n["op"] == "ConstantOp"
-                                                                   and n["op_fields"].get("source_path")):
+            if n["op"] in _KERNEL_OPS or n["op"] in ("InputOp", "ElementwiseOp") or (
+                    n["op"] == "ConstantOp" and n["op_fields"].get("source_path")):
                 fields = {k: v for k, v in n["op_fields"].items() if k in ("eps", "axis", "is_causal", "has_bias",
-                                                                           "source_path")}
+                                                                           "source_path", "op")}
                 out[nid] = (n["op"], fields, n["inputs"], n["output"]["shape"], n["output"]["dtype"])
         return out
 
     assert essentials(got) == essentials(ref)
 
 
-def test_swiglu_expression_is_rejected_at_lowering():
-    """Pointwise ops have no stand-alone kernel here: traced under their ATen name, refused by ``compile``."""
+def test_perf_suite_expressions_lower_to_gemms_and_one_pointwise_launch():
+    """The expressions the reference's perf suite drives (``tests/perf/cases.py:60-74``)."""
     g, _, _ = graph_from_code(CODES["swiglu_f32"])
-    ops = {n.op for n in g.nodes.values()}
-    assert "MatmulOp" in ops and any(o.startswith("Aten:") for o in ops)
+    assert {n.op for n in g.nodes.values()} == {"InputOp", "MatmulOp", "ElementwiseOp"}
+    plan = B200Backend().compile(g)
+    assert [s.entry for s in plan.steps] == ["emk_linear_f32_simt", "emk_linear_f32_simt", "emk_elementwise"]
+    assert plan.steps[2].attrs["op"] == "silu_multiply"
+    # bf16 matmul + residual: the add becomes the GEMM's residual epilogue
+    plan = B200Backend().compile(trace_inline_code(
+        "x=torch.randn(16,64).bfloat16(); w=torch.randn(64,96).bfloat16(); r=torch.randn(16,96).bfloat16(); "
+        "torch.matmul(x,w)+r").graph)
+    assert [s.entry for s in plan.steps] == ["emk_linear_bf16"] and plan.steps[0].attrs["residual"]
+    assert plan.aliases["add"] == "matmul"
+    # fp32: GEMM then a pointwise add
+    plan = B200Backend().compile(trace_inline_code(
+        "x=torch.randn(16,64); w=torch.randn(64,96); r=torch.randn(16,96); torch.matmul(x,w)+r").graph)
+    assert [s.entry for s in plan.steps] == ["emk_linear_f32_simt", "emk_elementwise"]
+    # broadcasting adds have no kernel
     with pytest.raises(LoweringError):
-        B200Backend().compile(g)
+        B200Backend().compile(trace_inline_code("torch.matmul(torch.randn(4,8), torch.randn(8,4)) + torch.randn(4)").graph)
 
 
 def test_grammar_errors():
@@ -162,7 +175,7 @@ def test_table_rows():
 # ------------------------------------------------------------------------------------------------------------
 @pytest.mark.gpu
 @pytest.mark.parametrize("name", ["rmsnorm_readme_shape", "softmax_f32", "linear_bias_f32", "matmul_f32",
-                                  "sdpa_causal_gqa_d128_f32", "sdpa_full_f32"])
+                                  "sdpa_causal_gqa_d128_f32", "sdpa_full_f32", "swiglu_f32"])
 def test_run_cli_passes_on_golden_expressions(name, capsys):
     assert main(["run", "-c", CODES[name]]) == 0
     assert capsys.readouterr().out.strip().endswith("PASS")
@@ -190,6 +203,19 @@ def test_run_cli_reruns_dumped_kernel_records(tmp_path, capsys):
     assert main(["run", "--ir", str(recs[0]), "--bench", "--warmup", "1", "--iters", "3"]) == 0
     out = capsys.readouterr().out
     assert "Emmy" in out and "k_scaled_dot_product_attention" in out
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("code", [
+    "x=torch.randn(512,1024).bfloat16(); w=(0.03*torch.randn(1024,768)).bfloat16(); r=torch.randn(512,768).bfloat16(); "
+    "torch.matmul(x,w)+r",
+    "x=torch.randn(40,64); w=torch.randn(64,96); r=torch.randn(40,96); torch.matmul(x,w)+r",
+    "x=torch.randn(256,512).bfloat16(); wg=(0.05*torch.randn(512,384)).bfloat16(); wu=(0.05*torch.randn(512,384)).bfloat16(); "
+    "F.silu(torch.matmul(x,wg))*torch.matmul(x,wu)",
+])
+def test_run_cli_perf_suite_expressions(code, capsys):
+    assert main(["run", "-c", code]) == 0
+    assert capsys.readouterr().out.strip().endswith("PASS")
 
 
 @pytest.mark.gpu
