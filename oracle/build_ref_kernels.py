@@ -1,6 +1,6 @@
 """Recipe for ``oracle/_ref/``: the reference compiler's own emitted CUDA kernels for the four kernel configurations.
 
-TEST / BASELINE INFRASTRUCTURE, not product code. Run where the reference checkout is importable (it is not on the GPU
+TEST AND REFERENCE-TIMING INFRASTRUCTURE, not product code. Run where the reference checkout is importable (it is not on the GPU
 box; the outputs travel there):
 
     python oracle/build_ref_kernels.py /path/to/reference

@@ -1,6 +1,6 @@
 """Launcher for ``oracle/_ref/``: the reference compiler's own emitted kernels (built by ``build_ref_kernels.py``).
 
-TEST / BASELINE INFRASTRUCTURE, not product code: the product never imports this. It exists so that the parity tests
+TEST AND REFERENCE-TIMING INFRASTRUCTURE, not product code: the product never imports this. It exists so that the parity tests
 can compare the hand-written kernels with what the reference itself emits for the same four configurations, and so
 that ``bench.py --impl reference`` can report the reference's kernels timed on the same GPU.
 
