@@ -206,7 +206,7 @@ int launch_rmsnorm(emk_handle_t h, const T* x, const T* w, T* y, int64_t rows, i
     else rmsnorm_cta_kernel<T, 2, 256><<<grid, 256, 0, s>>>(x, w, y, rows, (int)cols, eps);
   } else {
     const int64_t ctas = (rows + 7) / 8;
-    const int grid = (int)(ctas < (int64_t)h->sm_count * 64 ? ctas : (int64_t)h->sm_count * 64);
+    const int grid = (int)(ctas < (int64_t)h->sm_count * 16 ? ctas : (int64_t)h->sm_count * 16);  // two resident rounds of CTAs, rows dealt evenly
     if (nvec <= 32) rmsnorm_warp_kernel<T, 1><<<grid, 256, 0, s>>>(x, w, y, rows, (int)cols, eps);
     else if (nvec <= 64) rmsnorm_warp_kernel<T, 2><<<grid, 256, 0, s>>>(x, w, y, rows, (int)cols, eps);
     else if (nvec <= 128) rmsnorm_warp_kernel<T, 4><<<grid, 256, 0, s>>>(x, w, y, rows, (int)cols, eps);
