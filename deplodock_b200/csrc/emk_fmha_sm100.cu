@@ -13,7 +13,10 @@
 //   warps 8..11  epilogue of both tiles: O / row sum -> bf16 -> 128-byte-swizzled staging -> TMA store, so the
 //                softmax warps go straight on to the next item
 //   warp 12      TMA producer: one Q tile per head (own barriers, so a head's Q is replaced as soon as its last S is
-//                done), then a 2-slot ring of K tiles and a 2-slot ring of V tiles
+//                done), then a 2-slot ring of K tiles and a 2-slot ring of V tiles with separate release: a K slot
+//                comes free when its S products are done, so the next-but-one K block is on its way a whole block
+//                before it is needed (with a joint release the load latency sat on the critical path whenever K/V
+//                came from DRAM, as with many short sequences)
 //   warp 13      MMA issuer: S = Q·Kᵀ (both operands from shared memory) and O += P·V (P from tensor memory,
 //                V from shared memory as an MN-major operand); the first S of the next item is issued right behind
 //                the last PV of the current one, so the pipeline does not drain between items
@@ -66,7 +69,8 @@ struct FmhaArgs {
 struct __align__(8) FmhaBarriers {
   uint64_t q_full[2], q_empty[2];   // one Q tile per query head of the item
   uint64_t k_full[KV_STAGES], v_full[KV_STAGES];
-  uint64_t kv_empty[KV_STAGES];  // one K tile and one V tile per stage, released together
+  uint64_t k_empty[KV_STAGES], v_empty[KV_STAGES];  // a K tile is free once its S products are done, a block earlier
+                                                    // than the V tile of the same block (free after its PV products)
   uint64_t s_full[2], p_full[2], l_ready[2], o_done[2], o_empty[2];
   uint32_t tmem_base;
   int abort_flag;
@@ -178,7 +182,8 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     for (int i = 0; i < KV_STAGES; ++i) {
       mbar_init(&bars->k_full[i], 1);
       mbar_init(&bars->v_full[i], 1);
-      mbar_init(&bars->kv_empty[i], 1);
+      mbar_init(&bars->k_empty[i], 1);
+      mbar_init(&bars->v_empty[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars->q_full[i], 1);
@@ -238,11 +243,15 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
         for (int j = 0; j < it.nblk && ok; ++j, ++kv_count) {
           const int st = (int)(kv_count % KV_STAGES);
           const uint32_t ph = (kv_count / KV_STAGES) & 1u;
-          ok = mbar_wait(&bars->kv_empty[st], ph ^ 1u, wc, EMK_DEV_TIMEOUT_PRODUCER);
+          // K of this block goes out as soon as the S products of the block two back are done; its V follows when
+          // that block's PV products are done too (the same moment at which the next block's K slot comes free)
+          ok = mbar_wait(&bars->k_empty[st], ph ^ 1u, wc, EMK_DEV_TIMEOUT_PRODUCER);
           if (!ok) break;
           mbar_arrive_expect_tx(&bars->k_full[st], TILE_BYTES);
           tma_load_2d(sK + st * TILE_BYTES, &tma_k, &bars->k_full[st], xkv, ykv + j * FN);
           tma_load_2d(sK + st * TILE_BYTES + HALF_BYTES, &tma_k, &bars->k_full[st], xkv + 64, ykv + j * FN);
+          ok = mbar_wait(&bars->v_empty[st], ph ^ 1u, wc, EMK_DEV_TIMEOUT_PRODUCER);
+          if (!ok) break;
           mbar_arrive_expect_tx(&bars->v_full[st], TILE_BYTES);
           tma_load_2d(sV + st * TILE_BYTES, &tma_v, &bars->v_full[st], xkv, ykv + j * FN);
           tma_load_2d(sV + st * TILE_BYTES + HALF_BYTES, &tma_v, &bars->v_full[st], xkv + 64, ykv + j * FN);
@@ -359,9 +368,9 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
         if (!ok) break;
         ++items[t];
         tc_fence_after();
-        // every MMA of the item is done: the last K/V stage goes back to the producer
+        // every MMA of the item is done: the V slot of its last block goes back to the producer
         if (t == ntile - 1 && quarter == 0 && lane == 0)
-          mbar_arrive(&bars->kv_empty[(kv_base + (uint32_t)it.nblk - 1u) % KV_STAGES]);
+          mbar_arrive(&bars->v_empty[(kv_base + (uint32_t)it.nblk - 1u) % KV_STAGES]);
         const float inv = __fdividef(1.0f, bars->row_l[t][r_in_tile]);
         const int hq = it.hq0 + t;
         const bool full = it.q0 + FM <= a.S;
@@ -448,9 +457,13 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
         }
         tc_fence_after();
         if (elected) {
-          // the S commit of the last tile covers the PV of block j-1 of both tiles: hand that K/V stage back;
-          // after the last S of the item this tile's Q buffer is free as well
-          if (last_tile && j > 0) mbar_arrive(&bars->kv_empty[(kv_base + (uint32_t)j - 1u) % KV_STAGES]);
+          // the S commit of the last tile covers the S products of block j and the PV products of block j-1 of
+          // both tiles: hand back this block's K slot and the previous block's V slot; after the last S of the item
+          // this tile's Q buffer is free as well
+          if (last_tile) {
+            mbar_arrive(&bars->k_empty[(kv_base + (uint32_t)j) % KV_STAGES]);
+            if (j > 0) mbar_arrive(&bars->v_empty[(kv_base + (uint32_t)j - 1u) % KV_STAGES]);
+          }
           if (j == nblk - 1) mbar_arrive(&bars->q_empty[t]);
         }
         uint32_t s[FN];
