@@ -218,6 +218,44 @@ def _graph_time_us(fn, reps: int, iters: int = 5) -> tuple[float, float]:
     return statistics.median(samples), min(samples)
 
 
+def serving_table(weights) -> list[dict]:
+    """Requests per second of the serving-side runner (``deplodock_b200.runner``) on the two workloads the reference
+    quotes for its vLLM plugin (64 requests x 256 tokens; uniform 512 tokens): ids resident on the device, hidden
+    states of every token produced and cloned per request, all requests submitted at once."""
+    import time
+
+    import torch
+
+    from deplodock_b200.runner import EmbedForwardRunner
+
+    rows = []
+    cfg = weights.cfg
+    gen = torch.Generator().manual_seed(0)
+    for tokens, batch_cap in ((256, 1), (256, 8), (256, 32), (512, 32)):
+        runner = EmbedForwardRunner(weights, max_seq_len=tokens, batch_cap=batch_cap)
+        reqs = [torch.randint(0, cfg.vocab_size, (tokens,), generator=gen).cuda() for _ in range(64)]
+
+        def serve():
+            if batch_cap == 1:
+                return [runner.forward_hidden_states(r) for r in reqs]
+            return runner.forward_hidden_states_batched(reqs)
+
+        serve()   # captures the graph(s)
+        torch.cuda.synchronize()
+        best = float("inf")
+        for _ in range(3):
+            t0 = time.perf_counter()
+            out = serve()
+            torch.cuda.synchronize()
+            best = min(best, time.perf_counter() - t0)
+        assert len(out) == 64 and tuple(out[0].shape) == (tokens, cfg.hidden_size)
+        rows.append({"requests": 64, "tokens_per_request": tokens, "batch_cap": batch_cap,
+                     "req_per_s": round(64 / best, 1), "ms_total": round(best * 1e3, 2)})
+        del runner
+        torch.cuda.empty_cache()
+    return rows
+
+
 def kernel_table(peaks: dict) -> list[dict]:
     import torch
 
@@ -507,7 +545,11 @@ def main() -> None:
             "step_breakdown_ms": gp["families"],
         }
         if world == 1 and not args.no_kernels:
+            weights = model.weights
             del model
+            torch.cuda.empty_cache()
+            line["serving"] = serving_table(weights)
+            del weights
             torch.cuda.empty_cache()
             line["kernels"] = kernel_table(peaks)
         if world == 1 and not args.no_cpu:
