@@ -2,7 +2,7 @@
 
 The two verbs of the reference's CLI that sit on the kernel path (``emmy/cli.py:17-47``, ``emmy/commands/run.py:23-140``,
 ``emmy/commands/compile.py:66-290``), with the same input grammar (``-c/--code`` inline expression, ``--ir`` or a
-positional ``.json`` Torch-IR record), the same accuracy rule against eager PyTorch (``run.py:1440-1500``), the same
+positional ``.json`` record: Torch-IR, or one of the reference's Loop-IR kernel records, ``kernels/*.json``), the same accuracy rule against eager PyTorch (``run.py:1440-1500``), the same
 bench table rows (``Eager PyTorch`` / ``Emmy`` / ``vs Eager``, ``run.py:1715-1730``) and the same
 ``60_bench_compare.json`` artefact under ``--dump-dir`` / ``EMMY_DUMP_DIR`` (``run.py:375-394``). Exit code 0 iff the
 accuracy verdict is PASS (or no eager reference exists, for ``--ir``).
