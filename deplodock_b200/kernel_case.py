@@ -14,7 +14,7 @@ import torch
 
 from deplodock_b200 import ops
 
-CASES = ("rmsnorm", "rmsnorm_big", "softmax", "linear", "linear_model", "linear_w8", "sdpa", "qknorm_rope")
+CASES = ("rmsnorm", "rmsnorm_big", "softmax", "linear", "linear_model", "linear_w8", "sdpa", "sdpa_model", "qknorm_rope")
 
 
 def build_case(name: str, scale: float = 1.0):
@@ -56,6 +56,11 @@ def build_case(name: str, scale: float = 1.0):
         q, k, v = rn(B, 16, 2048, 128).bfloat16(), rn(B, 8, 2048, 128).bfloat16(), rn(B, 8, 2048, 128).bfloat16()
         o = torch.empty_like(q)
         return lambda: ops.sdpa_causal_gqa(q, k, v, out=o)
+    if name == "sdpa_model":   # the attention launch of the model plan: token-major fused QKV buffer, 64 x 512 tokens
+        B = max(1, int(64 * scale))
+        qkv = rn(B * 512, 4096).bfloat16()
+        o = torch.empty(B * 512, 2048, device=dev, dtype=torch.bfloat16)
+        return lambda: ops.sdpa_causal_gqa_tok(qkv, B, 512, 16, 8, o)
     if name == "qknorm_rope":
         T, S = int(32768 * scale), 512
         qkv = rn(T, 4096).bfloat16()
