@@ -209,22 +209,40 @@ def lower(graph: Graph) -> CompiledPlan:
             if name == "silu" and _sole_consumer_is_multiply(graph, node.id):
                 silu_of[node.id] = ins[0]   # folded into the multiply that consumes it
                 continue
-            if name == "multiply" and any(graph.nodes[i].id in silu_of for i in node.inputs):
-                si = next(i for i in node.inputs if i in silu_of)
-                other = next(i for i in node.inputs if i != si)
-                steps.append(PlanStep(_name("silu_mul", node), "emk_elementwise", node.id, [silu_of[si], src(other)],
-                                      {"op": "silu_multiply"}))
-                continue
-            # y = matmul(...) + r in bf16: the add becomes the GEMM's residual epilogue when it is the product's only use
-            if name == "add" and dt == "bf16":
-                prod = next((st for st in steps if st.out in ins and st.entry == "emk_linear_bf16"
-                             and not st.attrs["has_bias"] and "residual" not in st.attrs
-                             and _consumers(graph, st.out) == [node.id]), None)
-                if prod is not None:
-                    other = next(i for i in ins if i != prod.out)
-                    prod.args.append(other)
-                    prod.attrs["residual"] = True
-                    aliases[node.id] = prod.out
+            if name == "multiply":
+                folded = [i for i in dict.fromkeys(node.inputs) if i in silu_of]
+                # silu(a) * silu(b) and silu(a) * silu(a): only one silu can ride in the multiply, so every other
+                # folded operand (and a silu that is both operands) gets its own launch first
+                keep = folded[0] if folded and len(set(node.inputs)) == 2 else None
+                for sid in folded:
+                    if sid != keep:
+                        steps.append(PlanStep(_name("silu", graph.nodes[sid]), "emk_elementwise", sid,
+                                              [silu_of.pop(sid)], {"op": "silu"}))
+                if keep is not None:
+                    other = next(i for i in node.inputs if i != keep)
+                    steps.append(PlanStep(_name("silu_mul", node), "emk_elementwise", node.id,
+                                          [silu_of[keep], src(other)], {"op": "silu_multiply"}))
+                    continue
+            # y = matmul(...) + r in bf16: the add becomes the GEMM's residual epilogue when the product has no other
+            # use (not a graph output either) and r already exists when the GEMM runs: a graph input, a constant, or
+            # the output of an earlier launch
+            if name == "add" and dt == "bf16" and ins[0] != ins[1]:
+                produced: dict[str, int] = {st.out: k for k, st in enumerate(steps)}
+                for k, st in enumerate(steps):
+                    if not (st.out in ins and st.entry == "emk_linear_bf16" and not st.attrs["has_bias"]
+                            and "residual" not in st.attrs and _consumers(graph, st.out) == [node.id]
+                            and st.out not in graph.outputs
+                            and all(src(o) != st.out for o in graph.outputs)):
+                        continue
+                    other = next(i for i in ins if i != st.out)
+                    ready = graph.node_role(other) in ("input", "constant") or produced.get(other, len(steps)) < k
+                    if not ready:
+                        continue
+                    st.args.append(other)
+                    st.attrs["residual"] = True
+                    aliases[node.id] = st.out
+                    break
+                if node.id in aliases:
                     continue
             steps.append(PlanStep(_name(name, node), "emk_elementwise", node.id, ins[: 1 if name == "silu" else 2],
                                   {"op": name}))

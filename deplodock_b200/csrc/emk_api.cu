@@ -26,6 +26,16 @@ extern "C" const char* emk_status_string(int s) {
 extern "C" int emk_create(int device, emk_handle_t* out) {
   if (!out) return EMK_ERR_ARG;
   *out = nullptr;
+  if (device < 0 || device >= EMK_MAX_DEVICES) return EMK_ERR_ARG;
+  int caller_device = -1;
+  if (cudaGetDevice(&caller_device) != cudaSuccess) caller_device = -1;
+  // the handle's set-up runs with `device` current; the caller's current device is put back on every way out
+  struct Restore {
+    int dev;
+    ~Restore() {
+      if (dev >= 0) (void)cudaSetDevice(dev);
+    }
+  } restore{caller_device == device ? -1 : caller_device};
   emk_handle_s* h = (emk_handle_s*)calloc(1, sizeof(emk_handle_s));
   if (!h) return EMK_ERR_ARG;
   h->device = device;

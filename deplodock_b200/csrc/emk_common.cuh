@@ -6,6 +6,7 @@
 // Blackwell equivalents, written for hand-scheduled kernels.
 #pragma once
 
+#include <mutex>
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -22,6 +23,15 @@ typedef CUresult (*emk_encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuin
                                         const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
                                         CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
                                         CUtensorMapFloatOOBfill);
+
+// Per-device caches (kernel attributes, occupancy, symbol addresses) are indexed by device ordinal; emk_create
+// refuses ordinals outside [0, EMK_MAX_DEVICES). Their one-time set-up is serialised by a mutex so that handles used
+// from several host threads see a finished set-up.
+#define EMK_MAX_DEVICES 64
+struct emk_device_once {
+  std::mutex mu;
+  bool done[EMK_MAX_DEVICES] = {};
+};
 
 struct emk_handle_s {
   int device;

@@ -633,10 +633,13 @@ int fmha_launch(emk_handle_t h, const void* q, const void* k, const void* v, voi
     if (rc) return rc;
   }
 
-  static bool configured[64] = {false};
-  if (h->device < 64 && !configured[h->device]) {
-    EMK_CUDA_TRY(h, cudaFuncSetAttribute(fmha_causal_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FMHA_SMEM));
-    configured[h->device] = true;
+  static emk_device_once once;
+  {
+    std::lock_guard<std::mutex> lk(once.mu);
+    if (!once.done[h->device]) {
+      EMK_CUDA_TRY(h, cudaFuncSetAttribute(fmha_causal_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FMHA_SMEM));
+      once.done[h->device] = true;
+    }
   }
   const int64_t n_items = (int64_t)a.nqblk * B * Hkv * a.pairs;
   if (n_items > 0x7fffffffLL) return EMK_ERR_SHAPE;

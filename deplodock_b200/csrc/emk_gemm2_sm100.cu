@@ -217,11 +217,12 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
 template <int G2_BN, int G2_STAGES, int WL, int KSUB>
 int launch_gemm2(emk_handle_t h, const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, cudaStream_t s) {
   constexpr int G2_SMEM = G2_STAGES * KSUB * (A_STAGE_BYTES + (G2_BN / 2) * BK * 2) + 1024 + (int)sizeof(G2Barriers);
-  static bool configured[64] = {false};
-  static int max_pairs[64] = {0};
+  static emk_device_once once;
+  static int max_pairs[EMK_MAX_DEVICES] = {0};
   auto kern = gemm2_bf16_kernel<G2_BN, G2_STAGES, WL, KSUB>;
-  const int d = h->device < 64 ? h->device : 0;
-  if (!configured[d]) {
+  const int d = h->device;   // emk_create admits ordinals below EMK_MAX_DEVICES only
+  std::unique_lock<std::mutex> lk(once.mu);
+  if (!once.done[d]) {
     EMK_CUDA_TRY(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(h->sm_count & ~1), 1, 1);
@@ -241,10 +242,12 @@ int launch_gemm2(emk_handle_t h, const CUtensorMap& ta, const CUtensorMap& tb, c
       nclusters = h->sm_count / 2;
     }
     max_pairs[d] = nclusters < h->sm_count / 2 ? nclusters : h->sm_count / 2;
-    configured[d] = true;
+    once.done[d] = true;
   }
+  const int pair_cap = max_pairs[d];
+  lk.unlock();
   const int ntiles = g.tiles_m * g.tiles_n;
-  const int pairs = ntiles < max_pairs[d] ? ntiles : max_pairs[d];
+  const int pairs = ntiles < pair_cap ? ntiles : pair_cap;
   EMK_CUDA_TRY(h, launch_after_prologue(kern, 2u * (unsigned)pairs, G2_THREADS, G2_SMEM, s, h->overlap_launch != 0, ta, tb, g));
   EMK_LAUNCH_CHECK(h);
   return EMK_OK;

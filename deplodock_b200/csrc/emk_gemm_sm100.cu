@@ -179,11 +179,14 @@ epilogue_drain<BN / 32>(g, taddr, row, n0);
 template <int BN, int STAGES, int WL>
 int launch_gemm(emk_handle_t h, const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, cudaStream_t s) {
   constexpr int SMEM = STAGES * (A_STAGE_BYTES + BN * BK * 2) + 1024 + (int)sizeof(GemmBarriers);
-  static bool configured[64] = {false};
+  static emk_device_once once;
   auto kern = gemm_bf16_kernel<BN, STAGES, WL>;
-  if (h->device < 64 && !configured[h->device]) {
-    EMK_CUDA_TRY(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
-    configured[h->device] = true;
+  {
+    std::lock_guard<std::mutex> lk(once.mu);
+    if (!once.done[h->device]) {
+      EMK_CUDA_TRY(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+      once.done[h->device] = true;
+    }
   }
   const int ntiles = g.tiles_m * g.tiles_n;
   const int grid = ntiles < h->sm_count ? ntiles : h->sm_count;
@@ -262,7 +265,10 @@ int gemm_dispatch(emk_handle_t h, const void* x, const void* w, const void* resi
   }
   // CTA-pair tiles (256x256) when the problem has at least one full pair tile; single-CTA tiles otherwise.
   const bool pair_ok = M > BM && N > 128;
-  if (h->gemm_impl == 2 || (h->gemm_impl == 0 && pair_ok)) return emk_gemm2_launch(h, x, w, g, wlayout, s);
+  // The pair kernel's 128-wide tiles give each epilogue thread 64 columns, half of a row_sumsq_out slot: two threads
+  // would write one slot. Such outputs (N <= 128) always take the single-CTA kernel, whose threads own whole slots.
+  const bool pair_forced = h->gemm_impl == 2 && !(g.ss_out != nullptr && N <= 128);
+  if (pair_forced || (h->gemm_impl == 0 && pair_ok)) return emk_gemm2_launch(h, x, w, g, wlayout, s);
 
   CUtensorMap ta, tb;
   int rc = emk_make_tmap_2d(h, &ta, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2,

@@ -287,10 +287,13 @@ extern "C" int emk_linear_bf16_w8(emk_handle_t h, const void* x, const void* w_e
   rc = emk_make_tmap_2d(h, &tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_e4m3, (uint64_t)K, (uint64_t)N, (uint64_t)K, BK,
                         W8_BN, CU_TENSOR_MAP_SWIZZLE_NONE);
   if (rc != EMK_OK) return rc;
-  static bool configured[64] = {false};
-  if (h->device < 64 && !configured[h->device]) {
-    EMK_CUDA_TRY(h, cudaFuncSetAttribute(gemm_w8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, W8_SMEM));
-    configured[h->device] = true;
+  static emk_device_once once;
+  {
+    std::lock_guard<std::mutex> lk(once.mu);
+    if (!once.done[h->device]) {
+      EMK_CUDA_TRY(h, cudaFuncSetAttribute(gemm_w8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, W8_SMEM));
+      once.done[h->device] = true;
+    }
   }
   const int ntiles = g.tiles_m * g.tiles_n;
   const int grid = ntiles < h->sm_count ? ntiles : h->sm_count;

@@ -14,8 +14,9 @@
 //   * all calls on a device share the array: two calls that overlap on the GPU (different streams) race. The array
 //     keeps the last call's contents; nothing in it has to start at zero because the GEMM epilogue overwrites every
 //     slot it later reads;
-//   * the first call on a device looks the array's device address up (cudaGetSymbolAddress) and sets kernel
-//     attributes: make that first call outside of any stream capture.
+//   * the first call on a device looks the array's device address up (cudaGetSymbolAddress), and the first call of
+//     each shape class (M <= 128 or larger, N <= 128 or larger: each selects its own GEMM kernel) sets that kernel's
+//     attributes: make a warm-up call of the same shape class before any stream capture.
 // No counterpart exists in the reference (its runtime allocates through cupy, emmy/compiler/backend/cuda/program.py:340-364).
 #include "emk_common.cuh"
 
@@ -60,9 +61,11 @@ __global__ void __launch_bounds__(256) rmsnorm_from_partials_kernel(const __nv_b
 
 // Device address of the scratch array, looked up once per device with that device current.
 int scratch_address(emk_handle_t h, float** out) {
-  static float* addr[64] = {nullptr};
+  static float* addr[EMK_MAX_DEVICES] = {nullptr};
+  static std::mutex mu;
   const int d = h->device;
-  if (d < 0 || d >= 64) return EMK_ERR_ARG;
+  if (d < 0 || d >= EMK_MAX_DEVICES) return EMK_ERR_ARG;
+  std::lock_guard<std::mutex> lk(mu);
   if (addr[d] == nullptr) {
     int cur = -1;
     EMK_CUDA_TRY(h, cudaGetDevice(&cur));

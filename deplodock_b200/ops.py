@@ -51,6 +51,17 @@ def _check_cuda_contig(*tensors: torch.Tensor) -> None:
             raise ValueError("expected contiguous tensors")
 
 
+def _check_buffer(name: str, t: torch.Tensor | None, numel: int, dtype: torch.dtype) -> None:
+    """A caller-provided buffer the library reads or writes through a raw pointer: its size and dtype are checked here,
+    because the kernels cannot (a short buffer would be an out-of-bounds device access, not a Python error)."""
+    if t is None:
+        return
+    if t.dtype != dtype:
+        raise TypeError(f"{name} must be {dtype}, got {t.dtype}")
+    if t.numel() < numel:
+        raise ValueError(f"{name} holds {t.numel()} elements, the call needs {numel}")
+
+
 _DTYPES = {torch.float32: cabi.EMK_F32, torch.bfloat16: cabi.EMK_BF16}
 
 
@@ -116,6 +127,9 @@ def _linear_common(fn_name: str, x, w, *, residual, bias, swiglu, w_is_kn, out):
         epi, extra = cabi.EMK_EPI_BIAS, bias
     elif swiglu:
         epi, n_out = cabi.EMK_EPI_SWIGLU, N // 2
+    _check_buffer("out", out, M * n_out, torch.bfloat16)
+    _check_buffer("residual", residual, M * N, torch.bfloat16)
+    _check_buffer("bias", bias, N, torch.bfloat16)
     y = torch.empty(*x.shape[:-1], n_out, dtype=torch.bfloat16, device=x.device) if out is None else out
     h = handle()
     fn = getattr(h.lib, fn_name)
@@ -178,12 +192,20 @@ def gemm_fused(x, w, out, *, epilogue: str = "none", residual=None, w_is_kn: boo
     _check_cuda_contig(x, w, out, residual, row_sumsq_in, row_sumsq_out, q_weight, k_weight, rope_cm)
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise TypeError("gemm_fused expects bfloat16 operands")
-    for t in (row_sumsq_in, row_sumsq_out):
-        if t is not None and t.dtype != torch.float32:
-            raise TypeError("row sum-of-squares buffers are float32")
     epi = {"none": cabi.EMK_EPI_NONE, "residual": cabi.EMK_EPI_RESIDUAL, "swiglu": cabi.EMK_EPI_SWIGLU,
            "bias": cabi.EMK_EPI_BIAS, "qknorm_rope": cabi.EMK_EPI_QKNORM_ROPE}[epilogue]
     K = x.shape[-1]
+    M = x.numel() // K
+    N = w.shape[1] if w_is_kn else w.shape[0]
+    if (w.shape[0] if w_is_kn else w.shape[1]) != K:
+        raise ValueError("weight does not match x")
+    _check_buffer("out", out, M * (N // 2 if epilogue == "swiglu" else N), torch.bfloat16)
+    _check_buffer("residual", residual, M * N, torch.bfloat16)
+    _check_buffer("row_sumsq_out", row_sumsq_out, M * ((N + 127) // 128), torch.float32)
+    if row_sumsq_in is not None:
+        if norm_dim <= 0 or norm_dim % 128 != 0:
+            raise ValueError("row_sumsq_in needs norm_dim > 0 and a multiple of 128")
+        _check_buffer("row_sumsq_in", row_sumsq_in, M * (norm_dim // 128), torch.float32)
     d = cabi.GemmDesc()
     d.x, d.w, d.y = x.data_ptr(), w.data_ptr(), out.data_ptr()
     d.residual = residual.data_ptr() if residual is not None else None

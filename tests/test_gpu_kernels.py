@@ -450,3 +450,74 @@ def test_gemm_fused_row_sumsq_protocol(ops):
     ssg = torch.full((18, H // 128), -1.0, dtype=torch.float32, device="cuda")
     rows = ops.embed_gather(_dev(table), _dev(ids), row_sumsq=ssg)
     assert torch.allclose(ssg.sum(1), rows.float().pow(2).sum(-1), rtol=1e-5) and float(ssg[:, 1:].abs().max()) == 0.0
+
+
+# ------------------------------------------------------------------------------------------------------------
+# Whole-tensor comparisons at the benchmark sizes, bf16 softmax, row sums of squares from the single-CTA GEMM
+# ------------------------------------------------------------------------------------------------------------
+def _fp32_rel_err(got: torch.Tensor, ref: torch.Tensor, abs_floor: float) -> float:
+    """max |got - ref| / max(|ref|, abs_floor) in fp32 on the CPU (the float64 route of ``metrics`` would hold three
+    1 GB arrays for the 117 M-element softmax)."""
+    return ((got - ref).abs() / ref.abs().clamp_min(abs_floor)).max().item()
+
+
+def test_softmax_full_config_whole_tensor_vs_oracle(ops):
+    """[1,28,2048,2048] with 1 % of the entries at -inf: every one of the 117 440 512 outputs against the eager CPU
+    module on the same seeded input."""
+    x = inputs.softmax_inputs((1, 28, 2048, 2048))
+    got = ops.softmax_lastdim(_dev(x)).cpu()
+    ops.device_status()
+    ref = cpu_ref.softmax(x)
+    assert torch.equal(got == 0, ref == 0)
+    assert torch.isfinite(got).all()
+    assert _fp32_rel_err(got, ref, 1e-30) <= 1e-5
+
+
+def test_sdpa_full_config_whole_tensor_vs_oracle(ops):
+    """B4 Hq16 Hkv8 S2048 D128: all 64 heads against the eager CPU call (bf16) on the same seeded inputs."""
+    q, k, v = inputs.sdpa_inputs(4, 16, 8, 2048)
+    got = ops.sdpa_causal_gqa(_dev(q), _dev(k), _dev(v)).cpu()
+    ops.device_status()
+    ref = cpu_ref.sdpa_causal_gqa(q, k, v)
+    assert torch.isfinite(got).all()
+    err = (got.float() - ref.float()).abs().max().item()
+    assert err <= max(2e-2, ref.float().abs().max().item() * 2.0 ** -7), err
+    cos = torch.nn.functional.cosine_similarity(got.float(), ref.float(), dim=-1).min().item()
+    assert cos >= 0.999, cos
+
+
+@pytest.mark.parametrize("shape", [(64, 2048), (3, 5, 100), (7, 4096), (33, 1000), (2, 8192)])
+def test_softmax_bf16(ops, shape):
+    """bf16 rows: the eager CPU module computes in fp32 and rounds once; so does the kernel."""
+    x = inputs.softmax_inputs(shape, mask_frac=0.05, seed=7).bfloat16()
+    got = ops.softmax_lastdim(_dev(x)).cpu()
+    ops.device_status()
+    ref = cpu_ref.softmax(x)
+    assert got.dtype == torch.bfloat16 and torch.equal(got == 0, ref == 0)
+    # one rounding of the same fp32 value: at most one bf16 ulp apart
+    assert ((got.float() - ref.float()).abs() <= ref.float().abs() * 2.0 ** -7 + 1e-30).all()
+    assert (got != ref).float().mean().item() < 0.02
+
+
+@pytest.mark.parametrize("M,K,N", [(128, 256, 512), (96, 128, 384), (64, 256, 128), (100, 64, 64), (300, 256, 128),
+                                   (300, 128, 64)])
+def test_row_sumsq_out_small_shapes(ops, M, K, N):
+    """Partial row sums of squares from the shapes that do not take the 256-wide CTA-pair tiles: M <= 128 (single-CTA
+    kernel) and N <= 128 (one slot per row, never split between two epilogue threads)."""
+    g = torch.Generator().manual_seed(41)
+    x = torch.randn(M, K, generator=g).bfloat16()
+    w = (0.06 * torch.randn(N, K, generator=g)).bfloat16()
+    res = torch.randn(M, N, generator=g).bfloat16()
+    slots = (N + 127) // 128
+    ss = torch.full((M, slots), -7.0, dtype=torch.float32, device="cuda")
+    h = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    ops.gemm_fused(_dev(x), _dev(w), h, epilogue="residual", residual=_dev(res), row_sumsq_out=ss)
+    ops.device_status()
+    ref_h = cpu_ref.linear(x, w) + res
+    metrics.assert_bf16_tensor_path(h.cpu(), ref_h, what="producer output")
+    want = h.float().pow(2).view(M, -1)
+    for sl in range(slots):
+        part = want[:, sl * 128:(sl + 1) * 128].sum(-1)
+        assert torch.allclose(ss[:, sl], part, rtol=1e-4, atol=1e-3), f"slot {sl}"
+    # and against the oracle's rows (bf16 rounding of h is the only difference)
+    assert torch.allclose(ss.sum(1).cpu(), ref_h.float().pow(2).sum(-1), rtol=2e-2, atol=1e-2)

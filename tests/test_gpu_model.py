@@ -76,3 +76,21 @@ def test_sequences_are_independent(libemk):
     full = EmbedForward(cfg, sd, batch=4, seq=96)(ids).cpu().clone()
     half = EmbedForward(cfg, sd, batch=2, seq=96)(ids[2:]).cpu().clone()
     assert torch.equal(full[2:], half)
+
+
+def test_full_depth_full_vocab_forward_matches_eager_cpu(libemk):
+    """The benchmark configuration itself: 28 layers, hidden 1024, vocabulary 151 669, 512-token sequences, HF-default
+    initialisation (norm weights 1) — 8 of the 64 sequences against the eager CPU trunk on the same weights and ids.
+    The folded-RMSNorm plan rounds differently from the eager module; this is where 28 layers of that show."""
+    from deplodock_b200.model import EmbedForward
+
+    cfg = inputs.EmbedModelConfig()
+    sd = inputs.embed_model_weights(cfg, seed=0)
+    ids = inputs.token_ids(64, 512, cfg.vocab_size, seed=0)[:8]
+    got = EmbedForward(cfg, sd, batch=8, seq=512)(ids).cpu().clone()
+    ref = cpu_ref.embed_forward(ids, cfg, sd)
+    assert torch.isfinite(got).all()
+    cos = _cos(got, ref).min().item()
+    err = (got - ref).abs().max().item()
+    assert cos >= 0.999, f"min cosine {cos:.6f}"
+    assert err <= 2e-2, f"max abs {err:.3e}"

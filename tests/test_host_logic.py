@@ -259,3 +259,99 @@ def test_bench_reference_arm_prints_contract_line(monkeypatch, capsys):
                 "scaling", "vs_baseline", "dtype", "data", "config", "cpu_baseline", "e2e"):
         assert key in line
     assert line["impl"] == "reference" and line["value"] > 0 and line["e2e"]["h2d_bytes_per_step"] == 0
+
+
+# ------------------------------------------------------------------------------------------- folds keep launch order
+def _rec(nodes: dict, inputs: list[str], outputs: list[str]) -> dict:
+    out = {}
+    for nid, (op, ins, shape, dtype, fields) in nodes.items():
+        out[nid] = {"op": op, "op_fields": dict(fields), "inputs": list(ins),
+                    "output": {"name": nid, "shape": list(shape), "dtype": dtype}}
+    return {"inputs": inputs, "outputs": outputs, "nodes": out}
+
+
+def _assert_args_produced_before_use(plan):
+    ready = {nid for nid in plan.graph.nodes if plan.graph.node_role(nid) in ("input", "constant")}
+    for st in plan.steps:
+        for a in st.args:
+            assert a in ready, f"{st.kernel_name} reads {a!r} before any launch wrote it"
+        ready.add(st.out)
+    for o in plan.outputs:
+        t = o
+        while t in plan.aliases:
+            t = plan.aliases[t]
+        assert t in ready
+
+
+def test_residual_fold_waits_for_its_addend():
+    """``matmul(x, w) + rms_norm(x)``: the addend is computed after the product, so the add cannot ride in the GEMM
+    that was already placed; ``matmul(x, w) + r`` with r a graph input still folds."""
+    from deplodock_b200.backend import lower
+    from deplodock_b200.graph import Graph
+
+    bf = "bf16"
+    late = _rec({
+        "x": ("InputOp", [], [64, 256], bf, {}), "w": ("ConstantOp", [], [256, 256], bf, {}),
+        "g": ("ConstantOp", [], [256], bf, {}),
+        "mm": ("MatmulOp", ["x", "w"], [64, 256], bf, {}),
+        "rn": ("RmsNormOp", ["x", "g"], [64, 256], bf, {"eps": 1e-6}),
+        "add": ("ElementwiseOp", ["mm", "rn"], [64, 256], bf, {"op": "add"})}, ["x"], ["add"])
+    plan = lower(Graph.from_dict(late))
+    _assert_args_produced_before_use(plan)
+    assert [s.entry for s in plan.steps] == ["emk_linear_bf16", "emk_rmsnorm", "emk_elementwise"]
+    early = _rec({
+        "x": ("InputOp", [], [64, 256], bf, {}), "r": ("InputOp", [], [64, 256], bf, {}),
+        "w": ("ConstantOp", [], [256, 256], bf, {}),
+        "mm": ("MatmulOp", ["x", "w"], [64, 256], bf, {}),
+        "add": ("ElementwiseOp", ["mm", "r"], [64, 256], bf, {"op": "add"})}, ["x", "r"], ["add"])
+    plan = lower(Graph.from_dict(early))
+    _assert_args_produced_before_use(plan)
+    assert [s.entry for s in plan.steps] == ["emk_linear_bf16"] and plan.steps[0].attrs["residual"] is True
+    # the bare product is a graph output too: folding would return the sum in its place
+    both = dict(early)
+    both["outputs"] = ["add", "mm"]
+    plan = lower(Graph.from_dict(both))
+    _assert_args_produced_before_use(plan)
+    assert [s.entry for s in plan.steps] == ["emk_linear_bf16", "emk_elementwise"]
+    # p + p
+    twice = _rec({
+        "x": ("InputOp", [], [64, 256], bf, {}), "w": ("ConstantOp", [], [256, 256], bf, {}),
+        "mm": ("MatmulOp", ["x", "w"], [64, 256], bf, {}),
+        "add": ("ElementwiseOp", ["mm", "mm"], [64, 256], bf, {"op": "add"})}, ["x"], ["add"])
+    plan = lower(Graph.from_dict(twice))
+    _assert_args_produced_before_use(plan)
+    assert [s.entry for s in plan.steps] == ["emk_linear_bf16", "emk_elementwise"]
+
+
+def test_silu_fold_with_two_silu_operands():
+    from deplodock_b200.backend import lower
+    from deplodock_b200.graph import Graph
+
+    f = "f32"
+    two = _rec({
+        "a": ("InputOp", [], [8, 32], f, {}), "b": ("InputOp", [], [8, 32], f, {}),
+        "sa": ("ElementwiseOp", ["a"], [8, 32], f, {"op": "silu"}),
+        "sb": ("ElementwiseOp", ["b"], [8, 32], f, {"op": "silu"}),
+        "m": ("ElementwiseOp", ["sa", "sb"], [8, 32], f, {"op": "multiply"})}, ["a", "b"], ["m"])
+    plan = lower(Graph.from_dict(two))
+    _assert_args_produced_before_use(plan)
+    assert [s.attrs["op"] for s in plan.steps] == ["silu", "silu_multiply"]
+    assert plan.steps[1].args == ["a", "sb"]
+    same = _rec({
+        "a": ("InputOp", [], [8, 32], f, {}),
+        "sa": ("ElementwiseOp", ["a"], [8, 32], f, {"op": "silu"}),
+        "m": ("ElementwiseOp", ["sa", "sa"], [8, 32], f, {"op": "multiply"})}, ["a"], ["m"])
+    plan = lower(Graph.from_dict(same))
+    _assert_args_produced_before_use(plan)
+    assert [s.attrs["op"] for s in plan.steps] == ["silu", "multiply"] and plan.steps[1].args == ["sa", "sa"]
+
+
+def test_ops_check_buffer_sizes_before_the_call():
+    """Caller-provided buffers reach the library as raw pointers: a short or mistyped one must be a Python error."""
+    from deplodock_b200 import ops
+
+    with pytest.raises(ValueError, match="holds 8 elements"):
+        ops._check_buffer("row_sumsq_out", torch.zeros(8), 16, torch.float32)
+    with pytest.raises(TypeError):
+        ops._check_buffer("out", torch.zeros(16), 16, torch.bfloat16)
+    ops._check_buffer("out", None, 16, torch.bfloat16)
