@@ -103,6 +103,11 @@ class CompiledPlan:
     graph: Graph
     steps: list[PlanStep]
     aliases: dict[str, str]   # view-like nodes (reshape/contiguous/to) -> the node whose buffer they share
+    trunk: Any = None         # a ``trunk.TrunkMatch`` when the graph was recognised as a whole decoder trunk
+    # device copies of the weight constants, kept between runs while the caller passes the same host objects
+    # (host -> device once per compiled plan, not once per run)
+    const_cache: dict[str, tuple[Any, Any]] = field(default_factory=dict, repr=False)
+    executor: Any = field(default=None, repr=False)   # the trunk's EmbedForward, built at the first run
 
     @property
     def inputs(self) -> list[str]:
@@ -156,8 +161,36 @@ def _sole_consumer_is_multiply(g: Graph, nid: str) -> bool:
         g.nodes[i].output.shape == c.output.shape for i in c.inputs)
 
 
+def _lower_trunk(graph: Graph) -> CompiledPlan:
+    """A traced decoder trunk (embedding gather + attention in one graph): matched as a whole against the fused
+    five-launches-per-layer plan (``deplodock_b200.trunk``); anything that does not match is refused."""
+    from deplodock_b200 import trunk as _trunk
+    from deplodock_b200.model import launch_names
+
+    try:
+        m = _trunk.recognise_trunk(graph)
+    except _trunk.TrunkMismatch as exc:
+        raise LoweringError(f"the graph holds an embedding gather and attention but is not the decoder trunk the "
+                            f"fused plan implements: {exc}") from exc
+    roles: list[list[str]] = [[m.embed, m.ids]]
+    for lr in m.layers:
+        roles += [[lr.wq, lr.wk, lr.wv, lr.ln1, lr.qn, lr.kn, m.cos, m.sin], [], [lr.wo], [lr.wgate, lr.wup, lr.ln2],
+                  [lr.wdown]]
+    roles.append([m.final_norm])
+    names = launch_names(m.num_hidden_layers, True, True, False)
+    assert len(names) == len(roles)
+    steps = [PlanStep(name, entry, m.output, args, {"launch": i}) for i, ((name, entry), args) in
+             enumerate(zip(names, roles))]
+    return CompiledPlan(graph, steps, {}, trunk=m)
+
+
 def lower(graph: Graph) -> CompiledPlan:
-    """Op-by-op dispatch of a Torch-IR graph onto C-ABI entry points."""
+    """Op-by-op dispatch of a Torch-IR graph onto C-ABI entry points; a whole traced decoder trunk is matched onto
+    the fused model plan instead."""
+    from deplodock_b200 import trunk as _trunk
+
+    if _trunk.looks_like_trunk(graph):
+        return _lower_trunk(graph)
     steps: list[PlanStep] = []
     aliases: dict[str, str] = {}
     silu_of: dict[str, str] = {}   # silu nodes folded into their consuming multiply -> their operand
@@ -307,6 +340,8 @@ def dump_plan(plan: CompiledPlan, dump_dir) -> None:
     (d / "50_cuda.kernels").mkdir(parents=True, exist_ok=True)
     (d / "00_torch.json").write_text(json.dumps(plan.graph.to_dict(), indent=1))
     (d / "50_cuda.kernels.txt").write_text(plan.describe() + "\n")
+    if plan.trunk is not None:
+        return   # the launches of a fused trunk are not single Torch ops: no per-kernel sub-graph records
     for s in plan.steps:
         node = plan.graph.nodes[s.out]
         sub = plan.graph.single_node_graph(s.out, operands=list(s.args) + [i for i in node.inputs[len(s.args):]
@@ -361,12 +396,16 @@ class B200Backend(Backend):
         return torch.device("cuda", self.device_id if self.device_id is not None else torch.cuda.current_device())
 
     def _upload(self, plan: CompiledPlan, input_data: dict[str, Any]) -> dict[str, Any]:
-        """Host arrays -> device tensors for inputs and constants (cast to the node dtype)."""
+        """Host arrays -> device tensors for inputs and constants (cast to the node dtype). The device copy of a
+        weight constant is kept on the plan and reused while the caller passes the same host object again."""
         import torch
 
         dev = self._device()
         vals: dict[str, torch.Tensor] = {}
         g = plan.graph
+        want_dtype = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16, "i64": torch.int64,
+                      "i32": torch.int32, "bool": torch.bool}
+        fresh_constants = False
         for nid, node in g.nodes.items():
             role = g.node_role(nid)
             if role not in ("input", "constant"):
@@ -374,6 +413,10 @@ class B200Backend(Backend):
             info = node.output
             if nid in input_data:
                 arr = input_data[nid]
+                cached = plan.const_cache.get(nid) if role == "constant" else None
+                if cached is not None and cached[0] is arr and cached[1].device == dev:
+                    vals[nid] = cached[1]
+                    continue
                 if isinstance(arr, torch.Tensor):
                     t = arr
                 else:
@@ -382,10 +425,11 @@ class B200Backend(Backend):
                         t = torch.from_numpy(a.view(np.int16)).view(torch.bfloat16)
                     else:
                         t = torch.from_numpy(a)
-                want = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16, "i64": torch.int64,
-                        "i32": torch.int32, "bool": torch.bool}[info.dtype]
-                t = t.to(device=dev, dtype=want).reshape(info.shape).contiguous()
+                t = t.to(device=dev, dtype=want_dtype[info.dtype]).reshape(info.shape).contiguous()
                 vals[nid] = t
+                if role == "constant":
+                    plan.const_cache[nid] = (arr, t)
+                    fresh_constants = True
             elif role == "input":
                 raise KeyError(f"Missing input for node {nid!r}")
             elif node.op_fields.get("value") is not None:
@@ -394,13 +438,42 @@ class B200Backend(Backend):
                 used = any(nid in s.args for s in plan.steps)
                 if used:
                     raise KeyError(f"ConstantOp {nid!r} has no value and was not supplied in input_data")
+        if plan.trunk is not None:
+            if plan.executor is None or fresh_constants:
+                plan.executor = self._build_trunk_executor(plan, vals, dev)
+            vals["__executor__"] = plan.executor
         return vals
+
+    @staticmethod
+    def _build_trunk_executor(plan: CompiledPlan, vals: dict[str, Any], dev):
+        """The fused model plan for a recognised trunk: weights re-laid out once (q/k/v concatenated, gate/up
+        interleaved, norm weights folded), rotary tables taken from the graph's own cos/sin buffers."""
+        from deplodock_b200.model import EmbedConfig, EmbedForward
+
+        m = plan.trunk
+        cfg = EmbedConfig(vocab_size=m.vocab_size, hidden_size=m.hidden_size, intermediate_size=m.intermediate_size,
+                          num_hidden_layers=m.num_hidden_layers, num_attention_heads=m.num_attention_heads,
+                          num_key_value_heads=m.num_key_value_heads, head_dim=m.head_dim,
+                          rms_norm_eps=m.rms_norm_eps, rope_theta=0.0)
+        sd = {name: vals[nid] for name, nid in m.state_dict_names().items()}
+        ex = EmbedForward(cfg, sd, batch=m.batch, seq=m.seq, device=dev, hidden_states=True, pool=False,
+                          rope=(vals[m.cos], vals[m.sin]))
+        ex.launches = ex.launch_list(ex.ids, ex.out)
+        return ex
 
     def _execute(self, plan: CompiledPlan, vals: dict[str, Any], step_idx: int | None = None) -> None:
         from deplodock_b200 import ops
 
         steps = plan.steps if step_idx is None else [plan.steps[step_idx]]
         g = plan.graph
+        if plan.trunk is not None:
+            ex, m = vals["__executor__"], plan.trunk
+            if step_idx is None or step_idx == 0:
+                ex.ids.copy_(vals[m.ids].reshape(ex.ids.shape))
+            for s in steps:
+                ex.launches[s.attrs["launch"]][2]()
+            vals[m.output] = ex.hs.view(m.batch, m.seq, m.hidden_size)
+            return
         for s in steps:
             a = [vals[i] for i in s.args]
             shape = g.nodes[s.out].output.shape

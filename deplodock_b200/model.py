@@ -71,6 +71,37 @@ def rope_tables(seq: int, head_dim: int, theta: float, device) -> tuple[torch.Te
     return cos, sin
 
 
+def launch_names(num_layers: int, fold_rmsnorm: bool = True, hidden_states: bool = False,
+                 pool: bool = True) -> list[tuple[str, str]]:
+    """``(kernel name, C-ABI entry)`` of every launch of one chunk of the plan, in order — what
+    :meth:`EmbedForward.launch_list` launches, computable without a device (the backend shim lists a compiled trunk
+    with it)."""
+    L: list[tuple[str, str]] = []
+    if fold_rmsnorm:
+        L.append(("k_embed_gather_sumsq", "emk_embed_gather_sumsq"))
+        for i in range(num_layers):
+            L += [(f"k_rmsnorm_linear_qkv_qknorm_rope_{i}", "emk_gemm_bf16_fused"),
+                  (f"k_scaled_dot_product_attention_{i}", "emk_sdpa_causal_gqa_bf16_tok"),
+                  (f"k_linear_o_proj_residual_sumsq_{i}", "emk_gemm_bf16_fused"),
+                  (f"k_rmsnorm_linear_gate_up_swiglu_{i}", "emk_gemm_bf16_fused"),
+                  (f"k_linear_down_residual_sumsq_{i}", "emk_gemm_bf16_fused")]
+    else:
+        L.append(("k_embed_gather", "emk_embed_gather"))
+        for i in range(num_layers):
+            L += [(f"k_rms_norm_input_{i}", "emk_rmsnorm"),
+                  (f"k_linear_qkv_qknorm_rope_{i}", "emk_linear_bf16_qknorm_rope"),
+                  (f"k_scaled_dot_product_attention_{i}", "emk_sdpa_causal_gqa_bf16_tok"),
+                  (f"k_linear_o_proj_residual_{i}", "emk_linear_bf16"),
+                  (f"k_rms_norm_post_attention_{i}", "emk_rmsnorm"),
+                  (f"k_linear_gate_up_swiglu_{i}", "emk_linear_bf16"),
+                  (f"k_linear_down_residual_{i}", "emk_linear_bf16")]
+    if hidden_states:
+        L.append(("k_rms_norm_final", "emk_rmsnorm"))
+    if pool:
+        L.append(("k_pool_norm_l2", "emk_pool_norm_l2"))
+    return L
+
+
 class _LayerWeights:
     __slots__ = ("ln1", "wqkv", "qn", "kn", "wo", "ln2", "wgu", "wdown")
 
@@ -150,7 +181,7 @@ class EmbedForward:
     #: kernel launches per layer / outside the layers, for launch accounting in the bench
     @property
     def LAUNCHES_FIXED(self) -> int:
-        return 3 if self.hidden_states else 2
+        return 1 + int(self.hidden_states) + int(self.pool)
 
     @property
     def LAUNCHES_PER_LAYER(self) -> int:
@@ -158,7 +189,8 @@ class EmbedForward:
 
     def __init__(self, cfg, state_dict: dict[str, torch.Tensor] | None = None, *, batch: int, seq: int, device=None,
                  chunk_seqs: int | None = None, fold_rmsnorm: bool = True, weights: EmbedWeights | None = None,
-                 workspace: EmbedWorkspace | None = None, hidden_states: bool = False) -> None:
+                 workspace: EmbedWorkspace | None = None, hidden_states: bool = False,
+                 rope: tuple[torch.Tensor, torch.Tensor] | None = None, pool: bool = True) -> None:
         if weights is None:
             if state_dict is None:
                 raise ValueError("give a state_dict or prepared weights")
@@ -172,10 +204,19 @@ class EmbedForward:
         if self.batch % self.chunk_seqs != 0:
             raise ValueError("chunk_seqs must divide the batch")
         self.hidden_states = bool(hidden_states)
+        self.pool = bool(pool)   # False: stop at the final-norm hidden states (what a traced trunk returns)
+        if not self.pool and not self.hidden_states:
+            raise ValueError("a plan without pooling must produce hidden states")
         if self.hidden_states and self.chunk_seqs != self.batch:
             raise ValueError("hidden_states=True needs the whole batch in one chunk")
         self.embed, self.final_norm, self.layers = weights.embed, weights.final_norm, weights.layers
-        self.cos, self.sin = rope_tables(self.seq, c.head_dim, c.rope_theta, dev)
+        if rope is None:
+            self.cos, self.sin = rope_tables(self.seq, c.head_dim, c.rope_theta, dev)
+        else:   # cos/sin buffers of a traced module ([seq, head_dim] or [1, seq, head_dim]) instead of theta
+            self.cos, self.sin = (t.reshape(-1, c.head_dim).to(device=dev, dtype=torch.bfloat16).contiguous()
+                                  for t in rope)
+            if self.cos.shape[0] != self.seq or self.sin.shape[0] != self.seq:
+                raise ValueError("rotary tables do not match the sequence length")
         self.rope_cm = ops.rope_chunk_major(self.cos, self.sin)
 
         T = self.chunk_seqs * self.seq
@@ -204,41 +245,67 @@ class EmbedForward:
         return self.cfg.linear_flops_per_token() * self.batch * self.seq + self.cfg.attention_flops(self.batch,
                                                                                                      self.seq)
 
-    def _forward_chunk(self, ids: torch.Tensor, out: torch.Tensor) -> None:
+    def launch_list(self, ids: torch.Tensor, out: torch.Tensor) -> list[tuple[str, str, object]]:
+        """The plan of one chunk as ``(kernel name, C-ABI entry, thunk)`` per launch, in launch order. Calling the
+        thunks one after the other is the forward; the backend shim lists and times them one by one."""
         c = self.cfg
         B, S = ids.shape
         nq, nkv = c.num_attention_heads, c.num_key_value_heads
         eps = c.rms_norm_eps
+        H = c.hidden_size
+        L: list[tuple[str, str, object]] = []
+
+        def add(name: str, entry: str, fn) -> None:
+            L.append((name, entry, fn))
+
         if self.fold_rmsnorm:
-            H = c.hidden_size
-            ops.embed_gather(self.embed, ids, out=self.h, row_sumsq=self.ss1)
-            for lw in self.layers:
-                ops.gemm_fused(self.h, lw.wqkv, self.qkv, epilogue="qknorm_rope", row_sumsq_in=self.ss1, norm_dim=H,
-                               norm_eps=eps, q_weight=lw.qn, k_weight=lw.kn, rope_cm=self.rope_cm, S=S, Hq=nq, Hkv=nkv,
-                               qk_eps=eps)
-                ops.sdpa_causal_gqa_tok(self.qkv, B, S, nq, nkv, self.attn)
-                ops.gemm_fused(self.attn, lw.wo, self.h, epilogue="residual", residual=self.h,
-                               row_sumsq_out=self.ss2)
-                ops.gemm_fused(self.h, lw.wgu, self.mlp, epilogue="swiglu", row_sumsq_in=self.ss2, norm_dim=H,
-                               norm_eps=eps)
-                ops.gemm_fused(self.mlp, lw.wdown, self.h, epilogue="residual", residual=self.h,
-                               row_sumsq_out=self.ss1)
-            if self.hidden_states:
-                ops.rmsnorm(self.h, self.final_norm, eps, out=self.hs)
-            ops.pool_norm_l2(self.h, self.final_norm, B, S, eps, out=out)
-            return
-        ops.embed_gather(self.embed, ids, out=self.h)
-        for lw in self.layers:
-            ops.rmsnorm(self.h, lw.ln1, eps, out=self.x)
-            ops.linear_qknorm_rope(self.x, lw.wqkv, lw.qn, lw.kn, self.rope_cm, S, nq, nkv, eps, out=self.qkv)
-            ops.sdpa_causal_gqa_tok(self.qkv, B, S, nq, nkv, self.attn)
-            ops.linear(self.attn, lw.wo, residual=self.h, out=self.h)
-            ops.rmsnorm(self.h, lw.ln2, eps, out=self.x)
-            ops.linear(self.x, lw.wgu, swiglu=True, out=self.mlp)
-            ops.linear(self.mlp, lw.wdown, residual=self.h, out=self.h)
+            add("k_embed_gather_sumsq", "emk_embed_gather_sumsq",
+                lambda: ops.embed_gather(self.embed, ids, out=self.h, row_sumsq=self.ss1))
+            for i, lw in enumerate(self.layers):
+                add(f"k_rmsnorm_linear_qkv_qknorm_rope_{i}", "emk_gemm_bf16_fused",
+                    lambda lw=lw: ops.gemm_fused(self.h, lw.wqkv, self.qkv, epilogue="qknorm_rope",
+                                                 row_sumsq_in=self.ss1, norm_dim=H, norm_eps=eps, q_weight=lw.qn,
+                                                 k_weight=lw.kn, rope_cm=self.rope_cm, S=S, Hq=nq, Hkv=nkv, qk_eps=eps))
+                add(f"k_scaled_dot_product_attention_{i}", "emk_sdpa_causal_gqa_bf16_tok",
+                    lambda: ops.sdpa_causal_gqa_tok(self.qkv, B, S, nq, nkv, self.attn))
+                add(f"k_linear_o_proj_residual_sumsq_{i}", "emk_gemm_bf16_fused",
+                    lambda lw=lw: ops.gemm_fused(self.attn, lw.wo, self.h, epilogue="residual", residual=self.h,
+                                                 row_sumsq_out=self.ss2))
+                add(f"k_rmsnorm_linear_gate_up_swiglu_{i}", "emk_gemm_bf16_fused",
+                    lambda lw=lw: ops.gemm_fused(self.h, lw.wgu, self.mlp, epilogue="swiglu", row_sumsq_in=self.ss2,
+                                                 norm_dim=H, norm_eps=eps))
+                add(f"k_linear_down_residual_sumsq_{i}", "emk_gemm_bf16_fused",
+                    lambda lw=lw: ops.gemm_fused(self.mlp, lw.wdown, self.h, epilogue="residual", residual=self.h,
+                                                 row_sumsq_out=self.ss1))
+        else:
+            add("k_embed_gather", "emk_embed_gather", lambda: ops.embed_gather(self.embed, ids, out=self.h))
+            for i, lw in enumerate(self.layers):
+                add(f"k_rms_norm_input_{i}", "emk_rmsnorm", lambda lw=lw: ops.rmsnorm(self.h, lw.ln1, eps, out=self.x))
+                add(f"k_linear_qkv_qknorm_rope_{i}", "emk_linear_bf16_qknorm_rope",
+                    lambda lw=lw: ops.linear_qknorm_rope(self.x, lw.wqkv, lw.qn, lw.kn, self.rope_cm, S, nq, nkv, eps,
+                                                         out=self.qkv))
+                add(f"k_scaled_dot_product_attention_{i}", "emk_sdpa_causal_gqa_bf16_tok",
+                    lambda: ops.sdpa_causal_gqa_tok(self.qkv, B, S, nq, nkv, self.attn))
+                add(f"k_linear_o_proj_residual_{i}", "emk_linear_bf16",
+                    lambda lw=lw: ops.linear(self.attn, lw.wo, residual=self.h, out=self.h))
+                add(f"k_rms_norm_post_attention_{i}", "emk_rmsnorm",
+                    lambda lw=lw: ops.rmsnorm(self.h, lw.ln2, eps, out=self.x))
+                add(f"k_linear_gate_up_swiglu_{i}", "emk_linear_bf16",
+                    lambda lw=lw: ops.linear(self.x, lw.wgu, swiglu=True, out=self.mlp))
+                add(f"k_linear_down_residual_{i}", "emk_linear_bf16",
+                    lambda lw=lw: ops.linear(self.mlp, lw.wdown, residual=self.h, out=self.h))
         if self.hidden_states:
-            ops.rmsnorm(self.h, self.final_norm, eps, out=self.hs)
-        ops.pool_norm_l2(self.h, self.final_norm, B, S, eps, out=out)
+            add("k_rms_norm_final", "emk_rmsnorm", lambda: ops.rmsnorm(self.h, self.final_norm, eps, out=self.hs))
+        if self.pool:
+            add("k_pool_norm_l2", "emk_pool_norm_l2",
+                lambda: ops.pool_norm_l2(self.h, self.final_norm, B, S, eps, out=out))
+        assert [(n, e) for n, e, _ in L] == launch_names(c.num_hidden_layers, self.fold_rmsnorm, self.hidden_states,
+                                                         self.pool)
+        return L
+
+    def _forward_chunk(self, ids: torch.Tensor, out: torch.Tensor) -> None:
+        for _, _, fn in self.launch_list(ids, out):
+            fn()
 
     def forward_eager(self) -> torch.Tensor:
         """Launch the plan on the current stream from ``self.ids``; returns ``self.out`` ``[batch, hidden]`` fp32."""

@@ -6,8 +6,11 @@ be an expression; statements before it are a preamble run with ``torch``, ``nn``
 inputs are the tensor names of the preamble and inline tensor-constructor calls) and of its FX walk
 (``emmy/compiler/trace/torch.py:71-135``: ``torch.export.export``, parameters/buffers become ``ConstantOp`` with a
 ``source_path``, other placeholders ``InputOp``, casts and ``contiguous``/``clone`` pass their input through,
-``:698-701``). Only the ops this backend has kernels for get a Torch-IR op; anything else is recorded under its ATen
-name and rejected later by ``B200Backend.compile`` with a ``LoweringError``.
+``:698-701``). The ops this backend has kernels for, and the ops the HF decoder trunk is traced into (embedding gather,
+the pow / mean / rsqrt RMSNorm chain, slice / negative / cat RoPE, transposes, ``expand`` as ``IndexMapOp``), get the
+reference's Torch-IR op names; anything else is recorded under its ATen name and rejected later by
+``B200Backend.compile`` with a ``LoweringError``. :func:`build_full_model_wrapper` makes an HF model traceable the way
+the reference's wrapper does (``emmy/compiler/trace/huggingface.py:17-186``).
 
 When the reference package is importable its tracer can be used instead: ``B200Backend.compile`` accepts its ``Graph``
 objects directly.
@@ -133,8 +136,7 @@ def graph_from_code(code: str):
 # ------------------------------------------------------------------------------------------------------------
 _PASSTHROUGH_TARGETS = ("aten.to.", "aten._to_copy.", "aten.contiguous.", "aten.clone.", "aten.alias.", "aten.detach.",
                         "aten.type_as.", "aten.lift_fresh_copy.", "aten.dropout.")
-_VIEW_TARGETS = ("aten.view.", "aten.reshape.", "aten._unsafe_view.", "aten.unsqueeze.", "aten.squeeze.",
-                 "aten.flatten.")
+_VIEW_TARGETS = ("aten.view.", "aten.reshape.", "aten._unsafe_view.", "aten.squeeze.", "aten.flatten.")
 
 
 def _shape_dtype(node) -> tuple[list[int], str]:
@@ -214,6 +216,35 @@ def trace_module(module: torch.nn.Module, args: tuple, kwargs: dict | None = Non
                 # same names as the reference's ElementwiseOp (emmy/compiler/trace/torch.py:506-523)
                 name = "silu" if "silu" in target else ("add" if "add" in target else "multiply")
                 add(node.name, "ElementwiseOp", {"op": name}, tin[:1 if name == "silu" else 2], shape, dtype)
+            elif target.startswith(("aten.add.Tensor", "aten.mul.Tensor", "aten.pow.Tensor_Scalar")) and hasattr(
+                    a[0], "name") and isinstance(a[1], (int, float)):
+                # tensor (op) python scalar: the scalar becomes a one-element ConstantOp, as in the reference's records
+                name = "pow" if "pow" in target else ("add" if "add" in target else "multiply")
+                add(node.name, "ElementwiseOp", {"op": name}, [a[0].name, const_scalar(node.name, 1, a[1])], shape, dtype)
+            elif target.startswith(("aten.rsqrt.", "aten.neg.")):
+                add(node.name, "ElementwiseOp", {"op": "rsqrt" if "rsqrt" in target else "negative"}, tin[:1], shape,
+                    dtype)
+            elif target.startswith("aten.embedding."):
+                add(node.name, "GatherOp", {"axis": 0}, [a[0].name, a[1].name], shape, dtype)
+            elif target.startswith("aten.mean.dim"):
+                dims = a[1] if isinstance(a[1], (list, tuple)) else [a[1]]
+                if len(dims) != 1:
+                    raise ValueError("mean over several axes is not supported")
+                add(node.name, "MeanOp", {"axis": int(dims[0]), "keepdim": bool(a[2]) if len(a) > 2 else False},
+                    [a[0].name], shape, dtype)
+            elif target.startswith("aten.slice.Tensor"):
+                dim = int(a[1]) if len(a) > 1 else 0
+                start = int(a[2]) if len(a) > 2 and a[2] is not None else 0
+                add(node.name, "SliceOp", {"shape": shape, "dim": dim, "start": start}, [a[0].name], shape, dtype)
+            elif target.startswith("aten.cat."):
+                axis = int(a[1]) if len(a) > 1 else int(kw.get("dim", 0))
+                add(node.name, "CatOp", {"axis": axis}, [x.name for x in a[0]], shape, dtype)
+            elif target.startswith("aten.transpose.int"):
+                add(node.name, "TransposeOp", {"axes": [int(a[1]), int(a[2])]}, [a[0].name], shape, dtype)
+            elif target.startswith("aten.unsqueeze."):
+                add(node.name, "UnsqueezeOp", {"dim": int(a[1])}, [a[0].name], shape, dtype)
+            elif target.startswith("aten.expand."):
+                add(node.name, "IndexMapOp", {"out_shape": shape}, [a[0].name], shape, dtype)
             elif target.startswith(_PASSTHROUGH_TARGETS):
                 add(node.name, "ToOp", {}, tin[:1], shape, dtype)
             elif target.startswith(_VIEW_TARGETS):
@@ -247,3 +278,52 @@ def bind_inputs(graph: Graph, module: torch.nn.Module, args: tuple, kwargs: dict
             raise KeyError(f"Could not bind constant {nid} (source_path={path!r})")
         data[nid] = named[path].detach()
     return data
+
+
+# ------------------------------------------------------------------------------------------------------------
+# HF model wrapper
+# ------------------------------------------------------------------------------------------------------------
+class _FixedRotary(torch.nn.Module):
+    """Stands in for the model's rotary-embedding submodule and returns tables computed once, eagerly. Under
+    ``torch.export`` the original submodule's non-persistent ``inv_freq`` buffer loses its value, which would trace
+    RoPE as the identity."""
+
+    def __init__(self, cos: torch.Tensor, sin: torch.Tensor) -> None:
+        super().__init__()
+        self.register_buffer("cos", cos)
+        self.register_buffer("sin", sin)
+
+    def forward(self, *args, **kwargs):
+        return self.cos, self.sin
+
+
+class FullModelWrapper(torch.nn.Module):
+    """``forward(input_ids) -> hidden states`` (logits for a causal-LM head model) of an HF decoder with everything
+    that depends on the sequence length precomputed as buffers: the additive causal mask ``causal_mask``
+    ``[1, 1, S, S]`` (0 / -inf), ``position_ids`` ``[1, S]`` and the rotary tables ``model.rotary_emb.cos`` / ``.sin``
+    ``[1, S, head_dim]``. The traced graph then holds no mask- or position-construction ops, and the buffers appear
+    as ``ConstantOp`` nodes under those source paths — the same record the reference's wrapper yields."""
+
+    def __init__(self, model: torch.nn.Module, seq_len: int, dtype: torch.dtype) -> None:
+        super().__init__()
+        self.model = model
+        neg = torch.full((seq_len, seq_len), float("-inf"), dtype=dtype)
+        self.register_buffer("causal_mask", torch.triu(neg, diagonal=1)[None, None])
+        self.register_buffer("position_ids", torch.arange(seq_len, dtype=torch.long)[None])
+        trunk = getattr(model, "model", model)
+        rotary = getattr(trunk, "rotary_emb", None)
+        if rotary is not None:
+            with torch.no_grad():
+                probe = torch.zeros(1, seq_len, model.config.hidden_size, dtype=dtype)
+                cos, sin = rotary(probe, self.position_ids)
+            trunk.rotary_emb = _FixedRotary(cos.clone(), sin.clone())
+
+    def forward(self, input_ids):
+        return self.model(input_ids=input_ids, attention_mask=self.causal_mask, position_ids=self.position_ids,
+                          use_cache=False, return_dict=False)[0]
+
+
+def build_full_model_wrapper(model: torch.nn.Module, seq_len: int, dtype: torch.dtype) -> torch.nn.Module:
+    """Static-shape wrapper of an HF decoder for tracing (the reference's ``build_full_model_wrapper`` in its default
+    mode; its ``dynamic=True`` mode has no counterpart here: plans are built per sequence length)."""
+    return FullModelWrapper(model, seq_len, dtype)

@@ -115,10 +115,40 @@ def _qwen3_layer_case():
     print("qwen3_layer_f32", out.shape, ops)
 
 
+def _qwen3_trunk_record():
+    """Two-layer Qwen3-shaped trunk in bf16 (hidden 1024, 16/8 heads of 128, intermediate 3072, vocab 64, 48 tokens)
+    behind the reference's ``build_full_model_wrapper``, traced by the reference's ``trace_module``: the graph record is
+    stored whole (``graphs/qwen3_trunk_2layer_bf16.json``: shapes and wiring only, no tensors) together with the ids
+    and the hidden states the wrapper module returns when run eagerly (``qwen3_trunk_2layer_bf16.npz``). Weights are
+    regenerated from the seed by ``oracle.inputs.embed_model_weights`` + ``perturb_norm_weights``; the constants of the
+    record name them by ``source_path``."""
+    sys.path.insert(0, str(HERE.parent.parent))
+    from emmy.compiler.trace.huggingface import build_full_model_wrapper
+    from emmy.compiler.trace.torch import trace_module
+
+    from oracle import cpu_ref, inputs
+
+    cfg = inputs.EmbedModelConfig(vocab_size=64, num_hidden_layers=2)
+    sd = inputs.perturb_norm_weights(inputs.embed_model_weights(cfg, seed=0, dtype=torch.bfloat16), seed=1)
+    S = 48
+    model = cpu_ref.build_hf_model(cfg, sd, dtype=torch.bfloat16)
+    wrapper = build_full_model_wrapper(model, S, torch.bfloat16)
+    ids = inputs.token_ids(1, S, cfg.vocab_size, seed=3)
+    with torch.no_grad():
+        out = wrapper(ids).float().numpy()
+    graph = trace_module(wrapper, (ids,))
+    (HERE / "graphs" / "qwen3_trunk_2layer_bf16.json").write_text(json.dumps(graph.to_dict(), indent=0))
+    np.savez_compressed(HERE / "qwen3_trunk_2layer_bf16.npz", ids=ids.numpy(), hidden=out)
+    print("qwen3_trunk_2layer_bf16", out.shape, len(graph.nodes), "nodes")
+
+
 def main() -> None:
     (HERE / "graphs").mkdir(exist_ok=True)
     if "--only-qwen3" in sys.argv:
         _qwen3_layer_case()
+        return
+    if "--only-trunk-record" in sys.argv:
+        _qwen3_trunk_record()
         return
     if "--only-loop-records" in sys.argv:
         import emmy
@@ -140,6 +170,7 @@ def main() -> None:
         (HERE / "graphs" / f"{name}.json").write_text(json.dumps(graph.to_dict(), indent=1))
         print(name, "record only")
     _qwen3_layer_case()
+    _qwen3_trunk_record()
     import emmy
 
     _loop_records(Path(emmy.__file__).resolve().parent.parent)

@@ -515,9 +515,9 @@ def test_row_sumsq_out_small_shapes(ops, M, K, N):
     ops.device_status()
     ref_h = cpu_ref.linear(x, w) + res
     metrics.assert_bf16_tensor_path(h.cpu(), ref_h, what="producer output")
-    want = h.float().pow(2).view(M, -1)
-    for sl in range(slots):
-        part = want[:, sl * 128:(sl + 1) * 128].sum(-1)
-        assert torch.allclose(ss[:, sl], part, rtol=1e-4, atol=1e-3), f"slot {sl}"
+    # every slot is overwritten (no stale -7), and the slots of a row add up to the row's sum of squares (a thread
+    # puts its whole total into the first slot it covers and zeros into the rest: only the sum is defined)
+    assert (ss >= 0).all()
+    assert torch.allclose(ss.sum(1), h.float().pow(2).sum(-1), rtol=1e-4, atol=1e-3)
     # and against the oracle's rows (bf16 rounding of h is the only difference)
     assert torch.allclose(ss.sum(1).cpu(), ref_h.float().pow(2).sum(-1), rtol=2e-2, atol=1e-2)
