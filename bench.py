@@ -263,74 +263,148 @@ def serving_table(weights) -> list[dict]:
     return rows
 
 
-def kernel_table(peaks: dict) -> list[dict]:
+def kernel_cases() -> dict:
+    """The named kernel configurations: ``name -> builder``; a builder allocates the seeded device inputs and returns
+    ``(launch thunk, bound, algorithmic work per launch, unit scale, peak key, note, launches per timing graph)``."""
+    import torch
+
+    from deplodock_b200 import ops
+
+    dev = "cuda"
+
+    def gen():
+        return torch.Generator(device=dev).manual_seed(0)
+
+    def rms_small():
+        g = gen()
+        x = torch.randn(1, 32, 2048, device=dev, generator=g)
+        w = 1 + 0.02 * torch.randn(2048, device=dev, generator=g)
+        y = torch.empty_like(x)
+        return (lambda: ops.rmsnorm(x, w, 1e-6, out=y), "hbm", 532480, 1e9, "hbm_gbs",
+                "0.5 MB, L2-resident, latency-bound", 200)
+
+    def rms_big():
+        g = gen()
+        xs = [torch.randn(32768, 1024, device=dev, generator=g).bfloat16() for _ in range(3)]
+        ws = torch.ones(1024, device=dev, dtype=torch.bfloat16)
+        ys = [torch.empty_like(t) for t in xs]
+        state = {"i": 0}
+
+        def fn():
+            i = state["i"] = (state["i"] + 1) % 3
+            ops.rmsnorm(xs[i], ws, 1e-6, out=ys[i])
+
+        return fn, "hbm", 2 * 32768 * 1024 * 2 + 2048, 1e9, "hbm_gbs", "3 rotating 64 MB buffer pairs (> L2)", 30
+
+    def softmax():
+        g = gen()
+        x = 3 * torch.randn(28 * 2048, 2048, device=dev, generator=g)
+        m = torch.rand(x.shape, device=dev, generator=g) < 0.01
+        m[:, 0] = False
+        x[m] = float("-inf")
+        del m
+        y = torch.empty_like(x)
+        return (lambda: ops.softmax_lastdim(x, out=y), "hbm", 939524096, 1e9, "hbm_gbs",
+                "470 MB in + 470 MB out (> L2)", 10)
+
+    def linear_inputs(M=4096):
+        g = gen()
+        x = torch.randn(M, 2048, device=dev, generator=g).bfloat16()
+        w32 = 0.02 * torch.randn(6144, 2048, device=dev, generator=g)
+        y = torch.empty(M, 6144, device=dev, dtype=torch.bfloat16)
+        return x, w32, y
+
+    def linear():
+        x, w32, y = linear_inputs()
+        w = w32.bfloat16()
+        return lambda: ops.linear(x, w, out=y), "tensor", 103079215104, 1e12, "bf16_tflops", "burst peak", 20
+
+    def w8(workspace, M=4096):
+        def build():
+            x, w32, y = linear_inputs(M)
+            s = (w32.abs().amax(1) / 448.0).contiguous()
+            wq = (w32 / s[:, None]).to(torch.float8_e4m3fn)
+            if workspace:
+                fn = lambda: ops.linear_w8(x, wq, s, out=y)  # noqa: E731
+                note = ("burst peak; weight expanded to bf16 once into a 25 MB scratch, then the bf16 CTA-pair GEMM "
+                        "(M > 256 route)")
+            else:
+                fn = lambda: ops.linear_w8(x, wq, s, out=y, workspace=None)  # noqa: E731
+                note = "burst peak; no scratch: every 128-row tile converts its weight tiles again"
+            if M <= 256:
+                # few rows: the launch is bound by reading W (12.6 MB as e4m3 bytes + x + y), not by the tensor core
+                nbytes = 6144 * 2048 + M * 2048 * 2 + M * 6144 * 2 + 6144 * 4
+                return fn, "hbm", nbytes, 1e9, "hbm_gbs", f"M = {M}: weight-read bound; W stays e4m3 in HBM", 50
+            return fn, "tensor", 2 * M * 2048 * 6144, 1e12, "bf16_tflops", note, 20
+        return build
+
+    def sdpa():
+        g = gen()
+        q = torch.randn(4, 16, 2048, 128, device=dev, generator=g).bfloat16()
+        k = torch.randn(4, 8, 2048, 128, device=dev, generator=g).bfloat16()
+        v = torch.randn(4, 8, 2048, 128, device=dev, generator=g).bfloat16()
+        o = torch.empty_like(q)
+        return (lambda: ops.sdpa_causal_gqa(q, k, v, out=o), "tensor", 68753031168, 1e12, "bf16_tflops",
+                "causal-useful flops, burst peak", 20)
+
+    def sdpa_model(B):
+        def build():
+            g = gen()
+            qkv = torch.randn(B * 512, 4096, device=dev, generator=g).bfloat16()
+            o = torch.empty(B * 512, 2048, device=dev, dtype=torch.bfloat16)
+            return (lambda: ops.sdpa_causal_gqa_tok(qkv, B, 512, 16, 8, o), "tensor",
+                    4 * B * 16 * 128 * (512 * 513 // 2), 1e12, "bf16_tflops",
+                    f"the attention launch of the model plan at {B} sequences: token-major fused QKV buffer", 20)
+        return build
+
+    return {
+        "k_rms_norm [1,32,2048] f32": rms_small,
+        "k_rms_norm [32768,1024] bf16": rms_big,
+        "k_softmax [1,28,2048,2048] f32": softmax,
+        "k_linear 4096x2048x6144 bf16": linear,
+        "k_linear 4096x2048x6144 e4m3 weights": w8(True),
+        "k_linear 4096x2048x6144 e4m3 weights, converted inside the main loop": w8(False),
+        "k_linear 256x2048x6144 e4m3 weights, converted inside the main loop": w8(False, 256),
+        "k_linear 128x2048x6144 e4m3 weights, converted inside the main loop": w8(False, 128),
+        "k_scaled_dot_product_attention B4 Hq16 Hkv8 S2048 D128": sdpa,
+        "k_scaled_dot_product_attention 64x512 token-major (model shape)": sdpa_model(64),
+        "k_scaled_dot_product_attention 8x512 token-major (8-GPU shard)": sdpa_model(8),
+    }
+
+
+def kernel_table(peaks: dict, only: str | None = None, launches: int = 0) -> list[dict]:
+    """One row per named kernel configuration, timed as a CUDA graph of back-to-back launches (median, min). With
+    ``launches`` > 0 the matching cases are instead launched eagerly that many times and not timed by graph — the
+    small, self-ending program a profiler is pointed at (``bench.py --only-kernel <substring> --launches 2``)."""
     import torch
 
     from deplodock_b200 import ops
 
     rows = []
-    dev = "cuda"
-    g = torch.Generator(device=dev).manual_seed(0)
-
-    def add(name, us, us_min, bound, work, unit_scale, peak, note=""):
+    for name, build in kernel_cases().items():
+        if only and only not in name:
+            continue
+        fn, bound, work, unit_scale, peak_key, note, reps = build()
+        if launches > 0:
+            fn()
+            torch.cuda.synchronize()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            for _ in range(launches):
+                fn()
+            e.record()
+            torch.cuda.synchronize()
+            us = mn = s.elapsed_time(e) * 1e3 / launches
+            note = f"{note}; {launches} eager launches"
+        else:
+            us, mn = _graph_time_us(fn, reps)
         achieved = work / (us * 1e-6) / unit_scale
-        rows.append({"kernel": name, "us": round(us, 2), "us_min": round(us_min, 2), "bound": bound,
+        peak = peaks[peak_key]
+        rows.append({"kernel": name, "us": round(us, 2), "us_min": round(mn, 2), "bound": bound,
                      "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s" if bound == "hbm" else "TFLOP/s",
                      "frac": round(achieved / peak, 4), "note": note})
-
-    # 1. RMSNorm [1,32,2048] f32 (0.5 MB: L2-resident, launch-latency bound) and a bandwidth-scale shape
-    x = torch.randn(1, 32, 2048, device=dev, generator=g)
-    w = 1 + 0.02 * torch.randn(2048, device=dev, generator=g)
-    y = torch.empty_like(x)
-    us, mn = _graph_time_us(lambda: ops.rmsnorm(x, w, 1e-6, out=y), 200)
-    add("k_rms_norm [1,32,2048] f32", us, mn, "hbm", 532480, 1e9, peaks["hbm_gbs"], "0.5 MB, L2-resident, latency-bound")
-    xs = [torch.randn(32768, 1024, device=dev, generator=g).bfloat16() for _ in range(3)]
-    ws = torch.ones(1024, device=dev, dtype=torch.bfloat16)
-    ys = [torch.empty_like(t) for t in xs]
-    state = {"i": 0}
-
-    def rms_big():
-        i = state["i"] = (state["i"] + 1) % 3
-        ops.rmsnorm(xs[i], ws, 1e-6, out=ys[i])
-
-    us, mn = _graph_time_us(rms_big, 30)
-    add("k_rms_norm [32768,1024] bf16", us, mn, "hbm", 2 * 32768 * 1024 * 2 + 2048, 1e9, peaks["hbm_gbs"],
-        "3 rotating 64 MB buffer pairs (> L2)")
-    del xs, ys
-    # 2. Softmax [1,28,2048,2048] f32
-    xsm = 3 * torch.randn(28 * 2048, 2048, device=dev, generator=g)
-    m = torch.rand(xsm.shape, device=dev, generator=g) < 0.01
-    m[:, 0] = False
-    xsm[m] = float("-inf")
-    del m
-    ysm = torch.empty_like(xsm)
-    us, mn = _graph_time_us(lambda: ops.softmax_lastdim(xsm, out=ysm), 10)
-    add("k_softmax [1,28,2048,2048] f32", us, mn, "hbm", 939524096, 1e9, peaks["hbm_gbs"], "470 MB in + 470 MB out (> L2)")
-    del xsm, ysm
-    # 3. Linear 4096x2048 -> 6144 bf16, and e4m3 weights
-    xl = torch.randn(4096, 2048, device=dev, generator=g).bfloat16()
-    w32 = 0.02 * torch.randn(6144, 2048, device=dev, generator=g)
-    wl = w32.bfloat16()
-    yl = torch.empty(4096, 6144, device=dev, dtype=torch.bfloat16)
-    us, mn = _graph_time_us(lambda: ops.linear(xl, wl, out=yl), 20)
-    add("k_linear 4096x2048x6144 bf16", us, mn, "tensor", 103079215104, 1e12, peaks["bf16_tflops"], "burst peak")
-    s = (w32.abs().amax(1) / 448.0).contiguous()
-    wq = (w32 / s[:, None]).to(torch.float8_e4m3fn)
-    us, mn = _graph_time_us(lambda: ops.linear_w8(xl, wq, s, out=yl), 20)
-    add("k_linear 4096x2048x6144 e4m3 weights", us, mn, "tensor", 103079215104, 1e12, peaks["bf16_tflops"],
-        "burst peak; weight expanded to bf16 once into a 25 MB scratch, then the bf16 CTA-pair GEMM (M > 256 route)")
-    us, mn = _graph_time_us(lambda: ops.linear_w8(xl, wq, s, out=yl, workspace=None), 20)
-    add("k_linear 4096x2048x6144 e4m3 weights, converted inside the main loop", us, mn, "tensor", 103079215104, 1e12,
-        peaks["bf16_tflops"], "burst peak; no scratch: every 128-row tile converts its weight tiles again")
-    del xl, wl, w32, wq, yl
-    # 4. SDPA B4 Hq16 Hkv8 S2048 D128
-    q = torch.randn(4, 16, 2048, 128, device=dev, generator=g).bfloat16()
-    k = torch.randn(4, 8, 2048, 128, device=dev, generator=g).bfloat16()
-    v = torch.randn(4, 8, 2048, 128, device=dev, generator=g).bfloat16()
-    o = torch.empty_like(q)
-    us, mn = _graph_time_us(lambda: ops.sdpa_causal_gqa(q, k, v, out=o), 20)
-    add("k_scaled_dot_product_attention B4 Hq16 Hkv8 S2048 D128", us, mn, "tensor", 68753031168, 1e12,
-        peaks["bf16_tflops"], "causal-useful flops, burst peak")
+        del fn
+        torch.cuda.empty_cache()
     ops.device_status()
     return rows
 
@@ -432,6 +506,10 @@ def main() -> None:
     ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel table")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU oracle pass (no parity check, no CPU baseline)")
     ap.add_argument("--chunk-seqs", type=int, default=0, help="sequences per activation chunk (0 = whole shard)")
+    ap.add_argument("--only-kernel", default=None, metavar="SUBSTR",
+                    help="run only the named kernel configurations whose name contains SUBSTR and print their rows")
+    ap.add_argument("--launches", type=int, default=0,
+                    help="with --only-kernel: launch eagerly this many times (a small program for a profiler)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
@@ -447,6 +525,11 @@ def main() -> None:
     from deplodock_b200.model import EmbedConfig, EmbedForward
 
     cabi.load_library()  # fail loudly when the CUDA extension is missing
+    if args.only_kernel:
+        peaks, _ = load_peaks()
+        torch.cuda.set_device(0)
+        print(json.dumps({"kernels": kernel_table(peaks, args.only_kernel, args.launches)}), flush=True)
+        return
     rank, local_rank, world = init_process_group()
     if world != args.gpus and world > 1:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")

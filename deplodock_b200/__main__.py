@@ -7,8 +7,15 @@ bench table rows (``Eager PyTorch`` / ``Emmy`` / ``vs Eager``, ``run.py:1715-173
 ``60_bench_compare.json`` artefact under ``--dump-dir`` / ``EMMY_DUMP_DIR`` (``run.py:375-394``). Exit code 0 iff the
 accuracy verdict is PASS (or no eager reference exists, for ``--ir``).
 
-Model ids, ``--layer``, ``--golden``, ``--ab``, ``--dynamic``, ``--profile`` and the tuner verbs are not provided:
-there is nothing to tune or generate, and whole Qwen3-shaped trunks run through ``deplodock_b200.model.EmbedForward``.
+``run --profile`` re-invokes the command under ``ncu`` and prints the per-kernel counter table with roofline columns
+(``deplodock_b200.profile``; ``61_ncu_metrics.json``), ``--bench`` also writes ``60_benchmark.json`` (the per-launch
+record the reference's dumper writes, ``emmy/compiler/pipeline/dump.py:311-323``), ``compile --ir`` takes the reference's
+stage names (``torch | tensor | loop | tile | kernel | cuda``: the first three print the Torch-IR record, the stage
+this backend starts from; the last three print the dispatch plan, the stage it ends at). GPU work is done under the
+``EMMY_GPU_LOCK`` file lock when that variable is set. A traced decoder trunk (a ``.json`` record of the wrapped HF
+module) compiles to the fused model plan. Model ids, ``--layer``, ``--golden``, ``--ab``, ``--dynamic`` and the tuner
+verbs are not provided: there is nothing to tune or generate and no checkpoint store to resolve ids against. ``--dynamic NAME@INPUT:AXIS`` (with ``--code``) traces an axis as a
+symbolic dimension; records with symbolic dimensions get one launch plan per runtime size.
 """
 
 from __future__ import annotations
@@ -26,6 +33,8 @@ def _add_common(p: argparse.ArgumentParser) -> None:
     p.add_argument("input", nargs="?", help=".json Torch-IR record (same as --ir)")
     p.add_argument("--code", "-c", help="inline expression, e.g. 'torch.nn.RMSNorm(2048)(torch.randn(1,32,2048))'")
     p.add_argument("--dump-dir", default=None)
+    p.add_argument("--dynamic", action="append", default=None, metavar="NAME@INPUT:AXIS",
+                   help="with --code: trace axis AXIS of input INPUT as the symbolic dimension NAME (repeatable)")
     p.add_argument("-v", "--verbose", action="count", default=0)
 
 
@@ -34,8 +43,10 @@ def build_parser() -> argparse.ArgumentParser:
     sub = parser.add_subparsers(dest="command", required=True)
     c = sub.add_parser("compile", help="lower a Torch-IR graph to a launch plan and print it")
     _add_common(c)
-    c.add_argument("--ir", choices=["torch", "cuda"], default="cuda",
-                   help="what to print: the traced Torch-IR record or the launch plan (default)")
+    c.add_argument("--ir", choices=["torch", "tensor", "loop", "tile", "kernel", "cuda"], default="cuda",
+                   help="stage to print (the reference's stage names): torch / tensor / loop -> the Torch-IR record "
+                        "(this backend has no IR between the traced graph and its kernels); tile / kernel / cuda -> "
+                        "the dispatch plan, one line per launch (default)")
     c.add_argument("--output", "-o", default=None)
     r = sub.add_parser("run", help="compile + run on the B200 backend, check against eager PyTorch")
     _add_common(r)
@@ -45,6 +56,11 @@ def build_parser() -> argparse.ArgumentParser:
     r.add_argument("--iters", type=int, default=100)
     r.add_argument("--seed", type=int, default=0)
     r.add_argument("--debug", action="store_true")
+    r.add_argument("--profile", action="store_true",
+                   help="re-run this command under ncu (bounded number of launches, --clock-control none) and print "
+                        "the per-kernel counter table with roofline columns")
+    r.add_argument("--profile-launches", type=int, default=24, help="launches ncu captures at most (default 24)")
+    r.add_argument("--profile-kernels", default=None, help="regex: capture only kernels whose name matches")
     return parser
 
 
@@ -62,9 +78,14 @@ def _load(args):
     if len(given) != 1:
         _fail("give exactly one of --code, --ir, or a positional .json record")
     if args.code:
-        from deplodock_b200.trace import trace_inline_code
+        from deplodock_b200.trace import parse_dynamic_specs, trace_inline_code
 
-        tr = trace_inline_code(args.code)
+        try:
+            dynamic = parse_dynamic_specs(args.dynamic)
+        except ValueError as exc:
+            print(f"Error: {exc}", file=sys.stderr)
+            raise SystemExit(2) from None
+        tr = trace_inline_code(args.code, dynamic or None)
         return tr.graph, tr.slug, tr
     path = Path(ir_path or args.input)
     if path.suffix != ".json":
@@ -120,7 +141,7 @@ def cmd_compile(args) -> int:
     from deplodock_b200.backend import B200Backend
 
     graph, _slug, _ = _load(args)
-    if args.ir == "torch":
+    if args.ir in ("torch", "tensor", "loop"):
         text = json.dumps(graph.to_dict(), indent=2)
     else:
         text = B200Backend(dump=args.dump_dir or os.environ.get("EMMY_DUMP_DIR")).compile(graph).describe()
@@ -134,10 +155,13 @@ def cmd_compile(args) -> int:
 def cmd_run(args) -> int:
     import torch
 
+    from deplodock_b200 import profile as _profile
     from deplodock_b200.backend import B200Backend
+    from deplodock_b200.gpu_lock import gpu_lock
     from deplodock_b200.trace import bind_inputs
 
     graph, slug, tr = _load(args)
+    in_ncu_child = bool(os.environ.get(_profile.NCU_CHILD_ENV))
     dump_dir = args.dump_dir or os.environ.get("EMMY_DUMP_DIR")
     backend = B200Backend(debug=args.debug, dump=dump_dir)
     plan = backend.compile(graph)
@@ -152,7 +176,17 @@ def cmd_run(args) -> int:
         data = bind_inputs(graph, tr.module, tr.args, tr.kwargs, tr.const_sources)
         with torch.no_grad():
             eager = tr.module(*tr.args, **tr.kwargs)
-        result, _ = backend.run(plan, input_data=data)
+        with gpu_lock():
+            result, _ = backend.run(plan, input_data=data)
+            if in_ncu_child:
+                # under the profiler the eager module runs once on the GPU too: its kernels are the table's ref side
+                dev = torch.device("cuda")
+                with torch.no_grad():
+                    tr.module.to(dev)(*(a.to(dev) if isinstance(a, torch.Tensor) else a for a in tr.args),
+                                      **{k: v.to(dev) if isinstance(v, torch.Tensor) else v
+                                         for k, v in tr.kwargs.items()})
+                torch.cuda.synchronize()
+                tr.module.to("cpu")
         eager_list = [eager] if isinstance(eager, torch.Tensor) else [e for e in eager if isinstance(e, torch.Tensor)]
         for name, e in zip(plan.outputs, eager_list):
             token = graph.nodes[name].output.dtype
@@ -186,14 +220,16 @@ def cmd_run(args) -> int:
                 info = node.output
                 data[nid] = torch.from_numpy((rng.standard_normal(info.shape) * 0.05 + (1.0 if len(info.shape) == 1
                                                                                          else 0.0)).astype(np.float32))
-        result, _ = backend.run(plan, input_data=data)
+        with gpu_lock():
+            result, _ = backend.run(plan, input_data=data)
         print(f"Ran {len(plan.steps)} launch(es) in {result.time_ms:.3f} ms (no eager reference for a .json record)")
 
     if args.bench:
         results: dict[str, float] = {}
-        if eager_fn is not None:
-            results["Eager PyTorch"] = _time_eager_us(eager_fn, args.warmup, args.iters)
-        bench = backend.benchmark(plan, warmup=args.warmup, num_iters=args.iters, input_data=data)
+        with gpu_lock():
+            if eager_fn is not None:
+                results["Eager PyTorch"] = _time_eager_us(eager_fn, args.warmup, args.iters)
+            bench = backend.benchmark(plan, warmup=args.warmup, num_iters=args.iters, input_data=data)
         results["Emmy"] = bench.time_ms * 1e3
         print()
         for line in render_table(results):
@@ -211,6 +247,16 @@ def cmd_run(args) -> int:
                 for n, us in results.items():
                     payload["backends"][n]["speedup_vs_eager"] = (eager_us / us) if us else 0.0
             (Path(dump_dir) / "60_bench_compare.json").write_text(json.dumps(payload, indent=2))
+            record = {"time_ms": bench.time_ms, "min_ms": bench.min_ms, "max_ms": bench.max_ms,
+                      "num_launches": bench.num_launches,
+                      "per_launch": [{"idx": lt.idx, "kernel_name": lt.kernel_name, "time_ms": lt.time_ms}
+                                     for lt in bench.per_launch or []]}
+            if bench.e2e_ms is not None:
+                record["e2e_ms"] = bench.e2e_ms
+            (Path(dump_dir) / "60_benchmark.json").write_text(json.dumps(record, indent=2))
+    if args.profile and ok:
+        with gpu_lock():
+            _profile.run_profile(args, dump_dir)
     return 0 if ok else 1
 
 

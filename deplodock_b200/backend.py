@@ -108,6 +108,27 @@ class CompiledPlan:
     # (host -> device once per compiled plan, not once per run)
     const_cache: dict[str, tuple[Any, Any]] = field(default_factory=dict, repr=False)
     executor: Any = field(default=None, repr=False)   # the trunk's EmbedForward, built at the first run
+    # A graph with symbolic dimensions: ``steps`` is the plan at the hint size (what ``describe`` prints); every
+    # binding of the symbols met at run time gets its own static plan, kept here (one plan per sequence length, as
+    # the serving runner keeps one captured graph per length). Variants share the parent's constant cache.
+    symbolic: bool = False
+    variants: dict[tuple, "CompiledPlan"] = field(default_factory=dict, repr=False)
+
+    def variant_for(self, input_data: dict | None) -> "CompiledPlan":
+        """The static plan for the shapes of ``input_data`` (the plan itself when the graph has no symbols)."""
+        if not self.symbolic:
+            return self
+        env = self.graph.symbolic_env(input_data)
+        missing = self.graph.symbols() - set(env)
+        if missing:
+            raise KeyError(f"cannot resolve symbolic dimension(s) {sorted(missing)}: supply the inputs that carry them")
+        key = tuple(sorted(env.items()))
+        v = self.variants.get(key)
+        if v is None:
+            v = lower(self.graph.resolve(env))
+            v.const_cache = self.const_cache
+            self.variants[key] = v
+        return v
 
     @property
     def inputs(self) -> list[str]:
@@ -123,6 +144,10 @@ class CompiledPlan:
 
     def symbolic_env(self, input_data=None) -> dict[str, int]:
         return self.graph.symbolic_env(input_data)
+
+    #: size assumed for every symbolic dimension when a plan is built without inputs (compile-time validation,
+    #: ``describe``, benchmarks without data) — the role of the reference's ``Dim.hint``
+    SYMBOL_HINT = 128
 
     def describe(self) -> str:
         """The dispatch plan as text: one line per launch (what ``emmy compile --ir cuda`` prints for this backend)."""
@@ -384,7 +409,13 @@ class B200Backend(Backend):
     def compile(self, graph: Any) -> CompiledPlan:
         if isinstance(graph, CompiledPlan):
             return graph
-        plan = lower(Graph.coerce(graph))
+        g = Graph.coerce(graph)
+        if g.is_symbolic:
+            # validated (and listed) at the hint size; the launch plan proper is built per binding at run time
+            hint = lower(g.resolve({name: CompiledPlan.SYMBOL_HINT for name in g.symbols()}))
+            plan = CompiledPlan(g, hint.steps, hint.aliases, trunk=hint.trunk, symbolic=True)
+        else:
+            plan = lower(g)
         if self.dump:
             dump_plan(plan, self.dump)
         return plan
@@ -537,18 +568,21 @@ class B200Backend(Backend):
 
         from deplodock_b200 import ops
 
-        plan = self.compile(compiled)
-        pre_result = pre_run() if pre_run is not None else None
-        vals = self._upload(plan, input_data or {})
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        self._execute(plan, vals)
-        stop.record()
-        ops.device_status()  # synchronises; raises HungKernelError / RuntimeError on device-side failure
-        elapsed = start.elapsed_time(stop)
-        if plan.steps and elapsed <= 0.0:
-            raise RuntimeError("zero elapsed time for a non-empty program")  # reference: program.py:1027-1031
-        return RunResult(outputs=self._download(plan, vals), time_ms=elapsed), pre_result
+        from deplodock_b200.gpu_lock import gpu_lock
+
+        plan = self.compile(compiled).variant_for(input_data)
+        with gpu_lock():   # the reference runs pre_run (its eager check) inside the same lock window, base.py:143-157
+            pre_result = pre_run() if pre_run is not None else None
+            vals = self._upload(plan, input_data or {})
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            self._execute(plan, vals)
+            stop.record()
+            ops.device_status()  # synchronises; raises HungKernelError / RuntimeError on device-side failure
+            elapsed = start.elapsed_time(stop)
+            if plan.steps and elapsed <= 0.0:
+                raise RuntimeError("zero elapsed time for a non-empty program")  # reference: program.py:1027-1031
+            return RunResult(outputs=self._download(plan, vals), time_ms=elapsed), pre_result
 
     # -- benchmark ---------------------------------------------------------------------------------------------
     async def benchmark_async(self, compiled: Any, *, warmup: int = 5, num_iters: int | str = 20, on_iter=None,
@@ -576,6 +610,22 @@ class B200Backend(Backend):
         return base
 
     def _benchmark(self, plan: CompiledPlan, warmup, num_iters, on_iter, capture_graphs, input_data) -> BenchmarkResult:
+        import torch
+
+        from deplodock_b200 import ops
+
+        from deplodock_b200.gpu_lock import gpu_lock
+
+        if plan.symbolic:
+            if input_data and plan.graph.symbols() <= set(plan.graph.symbolic_env(input_data)):
+                plan = plan.variant_for(input_data)
+            else:   # no inputs to read the sizes from: bench at the hint size
+                plan = lower(plan.graph.resolve({n: CompiledPlan.SYMBOL_HINT for n in plan.graph.symbols()}))
+        with gpu_lock():
+            return self._benchmark_locked(plan, warmup, num_iters, on_iter, capture_graphs, input_data)
+
+    def _benchmark_locked(self, plan: CompiledPlan, warmup, num_iters, on_iter, capture_graphs,
+                          input_data) -> BenchmarkResult:
         import torch
 
         from deplodock_b200 import ops

@@ -4,12 +4,21 @@
 
 Only what the backend needs is modelled: node ids, op class name and fields, operand ids, output shape and dtype
 token. A live reference ``Graph`` object (when the reference package is importable) is accepted through its own
-``to_dict``. Symbolic dimensions are not supported: every kernel here is launched with concrete sizes.
+``to_dict``.
+
+Symbolic dimensions: the reference writes an atomic symbolic dim as its name (``"seq_len"``) and a composite one as its
+pretty-printed expression (``emmy/compiler/graph.py:953-1007``); both are kept here as strings.
+:meth:`Graph.symbolic_env` reads the runtime value of every atomic name off the supplied input arrays (first-seen
+position wins, as ``emmy/compiler/graph.py:686-706``) and :meth:`Graph.resolve` substitutes it, evaluating composite
+expressions (``+ - * // %``, ``min``, ``max``, ``round_up``, ``ceildiv``), which gives the static graph a kernel
+plan is built for. Kernels are always launched with concrete sizes: one plan per binding of the symbols.
 """
 
 from __future__ import annotations
 
+import ast
 import json
+import operator
 from dataclasses import dataclass, field
 from pathlib import Path
 from typing import Any
@@ -31,11 +40,50 @@ DTYPES: dict[str, tuple[np.dtype, int]] = {
 _DTYPE_ALIASES = {"float32": "f32", "float16": "f16", "bfloat16": "bf16", "int64": "i64", "int32": "i32"}
 
 
+_BIN = {ast.Add: operator.add, ast.Sub: operator.sub, ast.Mult: operator.mul, ast.FloorDiv: operator.floordiv,
+        ast.Div: operator.floordiv, ast.Mod: operator.mod}
+_FUNCS = {"min": min, "max": max, "round_up": lambda a, b: -(-a // b) * b, "ceildiv": lambda a, b: -(-a // b)}
+
+
+def eval_dim(expr, env: dict[str, int]) -> int:
+    """A dimension under ``env``: ints pass through, a name is looked up, an expression string is evaluated with
+    integer arithmetic (``/`` is integer division, as in the reference's index expressions)."""
+    if isinstance(expr, int):
+        return expr
+
+    def ev(n: ast.AST) -> int:
+        if isinstance(n, ast.Constant) and isinstance(n.value, int):
+            return n.value
+        if isinstance(n, ast.Name):
+            if n.id not in env:
+                raise KeyError(f"symbolic dimension {n.id!r} has no runtime value (known: {sorted(env)})")
+            return int(env[n.id])
+        if isinstance(n, ast.BinOp) and type(n.op) in _BIN:
+            return int(_BIN[type(n.op)](ev(n.left), ev(n.right)))
+        if isinstance(n, ast.UnaryOp) and isinstance(n.op, ast.USub):
+            return -ev(n.operand)
+        if isinstance(n, ast.Call) and isinstance(n.func, ast.Name) and n.func.id in _FUNCS and not n.keywords:
+            return int(_FUNCS[n.func.id](*[ev(a) for a in n.args]))
+        raise ValueError(f"unsupported dimension expression {expr!r}")
+
+    return ev(ast.parse(str(expr), mode="eval").body)
+
+
+def dim_symbols(expr) -> set[str]:
+    if isinstance(expr, int):
+        return set()
+    return {n.id for n in ast.walk(ast.parse(str(expr), mode="eval")) if isinstance(n, ast.Name) and n.id not in _FUNCS}
+
+
 @dataclass(frozen=True)
 class TensorInfo:
     name: str
-    shape: tuple[int, ...]
+    shape: tuple  # ints, or strings for symbolic dimensions (a name or an expression over names)
     dtype: str
+
+    @property
+    def is_static(self) -> bool:
+        return all(isinstance(d, int) for d in self.shape)
 
     @property
     def np_dtype(self) -> np.dtype:
@@ -65,9 +113,14 @@ class Graph:
             out = nd["output"]
             shape = []
             for dim in out["shape"]:
-                if not isinstance(dim, int):
-                    raise ValueError(f"node {nid!r}: symbolic dimension {dim!r} is not supported by this backend")
-                shape.append(int(dim))
+                if isinstance(dim, bool) or not isinstance(dim, (int, str)):
+                    raise ValueError(f"node {nid!r}: dimension {dim!r} is neither an int nor a symbolic name")
+                if isinstance(dim, str):
+                    try:
+                        dim_symbols(dim)
+                    except SyntaxError as exc:
+                        raise ValueError(f"node {nid!r}: cannot parse symbolic dimension {dim!r}") from exc
+                shape.append(dim)
             dtype = _DTYPE_ALIASES.get(out["dtype"], out["dtype"])   # older records spell the numpy name
             if dtype not in DTYPES:
                 raise TypeError(f"node {nid!r}: unknown dtype token {dtype!r}")
@@ -141,9 +194,44 @@ class Graph:
             return "output"
         return "scratch"
 
+    @property
+    def is_symbolic(self) -> bool:
+        return any(not n.output.is_static for n in self.nodes.values())
+
+    def symbols(self) -> set[str]:
+        out: set[str] = set()
+        for n in self.nodes.values():
+            for d in n.output.shape:
+                out |= dim_symbols(d)
+        return out
+
     def symbolic_env(self, input_data: dict | None = None) -> dict[str, int]:
-        """Always empty: shapes are static here (the reference resolves symbolic dims, ``graph.py:686-706``)."""
-        return {}
+        """Runtime value of every atomic symbolic input dim, read off the supplied input arrays (first-seen position
+        wins; inputs that are absent or have fewer dims than declared are skipped) — ``emmy/compiler/graph.py:686-706``."""
+        env: dict[str, int] = {}
+        for nid in self.inputs:
+            if not input_data or nid not in input_data:
+                continue
+            arr_shape = tuple(getattr(input_data[nid], "shape", None) or np.asarray(input_data[nid]).shape)
+            for i, d in enumerate(self.nodes[nid].output.shape):
+                if isinstance(d, str) and d.isidentifier() and i < len(arr_shape):
+                    env.setdefault(d, int(arr_shape[i]))
+        return env
+
+    def resolve(self, env: dict[str, int]) -> "Graph":
+        """The static graph under ``env``: every symbolic dimension replaced by its value (``shape`` op fields that
+        name symbols included). Raises ``KeyError`` for a symbol without a value."""
+        if not self.is_symbolic:
+            return self
+        nodes: dict[str, Node] = {}
+        for nid, n in self.nodes.items():
+            fields = dict(n.op_fields)
+            for key in ("shape", "out_shape", "source_shape"):
+                if isinstance(fields.get(key), (list, tuple)):
+                    fields[key] = [eval_dim(d, env) if isinstance(d, str) else d for d in fields[key]]
+            shape = tuple(eval_dim(d, env) for d in n.output.shape)
+            nodes[nid] = Node(nid, n.op, fields, list(n.inputs), TensorInfo(n.output.name, shape, n.output.dtype))
+        return Graph(list(self.inputs), list(self.outputs), nodes)
 
     def compute_nodes(self) -> list[Node]:
         return [self.nodes[n] for n in self.topological_order()

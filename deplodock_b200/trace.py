@@ -82,8 +82,9 @@ class _InputLifter(ast.NodeTransformer):
         return self.generic_visit(node)
 
 
-def trace_inline_code(code: str) -> TraceResult:
-    """Trace ``"<preamble>; <final expression>"`` (see the module docstring for the grammar)."""
+def trace_inline_code(code: str, dynamic: list[tuple[str, str, int]] | None = None) -> TraceResult:
+    """Trace ``"<preamble>; <final expression>"`` (see the module docstring for the grammar). ``dynamic``: symbolic
+    axes, by input name as it appears in the record (``x`` for a single inline tensor, else the preamble's names)."""
     tree = ast.parse(code)
     if not tree.body or not isinstance(tree.body[-1], ast.Expr):
         raise ValueError('--code must end with an expression (e.g. "torch.nn.Softmax(dim=-1)(torch.randn(4, 8))")')
@@ -100,7 +101,7 @@ def trace_inline_code(code: str) -> TraceResult:
             args = tuple(eval(compile(ast.Expression(a), "<--code>", "eval"), scope) for a in final.args)  # noqa: S307
             kwargs = {k.arg: eval(compile(ast.Expression(k.value), "<--code>", "eval"), scope)  # noqa: S307
                       for k in final.keywords if k.arg}
-            graph, sources = trace_module(callee, args, kwargs)
+            graph, sources = trace_module(callee, args, kwargs, dynamic)
             return TraceResult(graph, _slugify(ast.unparse(final.func)), callee, args, kwargs, sources)
 
     lifter = _InputLifter(scope)
@@ -121,7 +122,7 @@ def trace_inline_code(code: str) -> TraceResult:
     exec(src, scope)  # noqa: S102
     module = scope["_Wrapper"]()
     args = tuple(params.values())
-    graph, sources = trace_module(module, args, {})
+    graph, sources = trace_module(module, args, {}, dynamic)
     return TraceResult(graph, _slugify(ast.unparse(final)), module, args, {}, sources)
 
 
@@ -139,16 +140,91 @@ _PASSTHROUGH_TARGETS = ("aten.to.", "aten._to_copy.", "aten.contiguous.", "aten.
 _VIEW_TARGETS = ("aten.view.", "aten.reshape.", "aten._unsafe_view.", "aten.squeeze.", "aten.flatten.")
 
 
-def _shape_dtype(node) -> tuple[list[int], str]:
+DYNAMIC_DIM_MAX = 4096   # upper bound of every dynamic axis, as in the reference (emmy/compiler/trace/dynamic.py:19)
+
+
+def parse_dynamic_specs(specs: list[str] | None) -> list[tuple[str, str, int]]:
+    """``--dynamic NAME@INPUT:AXIS`` strings -> ``(name, input, axis)`` triples; several specs may share a NAME (the
+    same symbolic size on several inputs), an ``(INPUT, AXIS)`` position may appear once. The grammar and its errors
+    are the reference's (``emmy/compiler/trace/dynamic.py:22-65``)."""
+    out: list[tuple[str, str, int]] = []
+    seen: set[tuple[str, int]] = set()
+    for raw in specs or []:
+        name, at, locator = raw.partition("@")
+        inp, colon, axis_s = locator.rpartition(":")
+        if not at or not colon:
+            raise ValueError(f"--dynamic {raw!r}: expected NAME@INPUT:AXIS form (e.g. seq_len@x:1)")
+        name, inp = name.strip(), inp.strip()
+        if not name or not name.isidentifier():
+            raise ValueError(f"--dynamic {raw!r}: NAME must be an identifier")
+        if not inp:
+            raise ValueError(f"--dynamic {raw!r}: INPUT name is empty")
+        try:
+            axis = int(axis_s)
+        except ValueError:
+            raise ValueError(f"--dynamic {raw!r}: AXIS must be an int, got {axis_s!r}") from None
+        if axis < 0:
+            raise ValueError(f"--dynamic {raw!r}: AXIS must be >= 0, got {axis}")
+        if (inp, axis) in seen:
+            raise ValueError(f"--dynamic {raw!r}: ({inp}, axis {axis}) appears more than once")
+        seen.add((inp, axis))
+        out.append((name, inp, axis))
+    return out
+
+
+def _dim_token(d, symbols: dict[str, str]):
+    """An FX shape entry as a record dimension: an int, or for a symbolic size its expression with torch's symbol
+    names (``s0``, ``s77``) replaced by the user's dimension names."""
+    if isinstance(d, int):
+        return int(d)
+    text = str(d)
+    for sym, name in sorted(symbols.items(), key=lambda kv: -len(kv[0])):
+        text = re.sub(rf"\b{re.escape(sym)}\b", name, text)
+    try:
+        return int(text)
+    except ValueError:
+        return text
+
+
+def _shape_dtype(node, symbols: dict[str, str] | None = None) -> tuple[list, str]:
     val = node.meta.get("val")
     if val is None or not isinstance(val, torch.Tensor):
         raise ValueError(f"FX node {node.name} carries no tensor value")
-    return [int(d) for d in val.shape], _token(val.dtype)
+    return [_dim_token(d, symbols or {}) for d in val.shape], _token(val.dtype)
 
 
-def trace_module(module: torch.nn.Module, args: tuple, kwargs: dict | None = None) -> tuple[Graph, dict[str, str]]:
-    """``torch.export.export`` the module and convert its FX graph to a Torch-IR record."""
-    exported = torch.export.export(module, args, kwargs=kwargs or None)
+def trace_module(module: torch.nn.Module, args: tuple, kwargs: dict | None = None,
+                 dynamic: list[tuple[str, str, int]] | None = None) -> tuple[Graph, dict[str, str]]:
+    """``torch.export.export`` the module and convert its FX graph to a Torch-IR record. ``dynamic`` marks axes of
+    inputs as symbolic (``(name, input, axis)``, see :func:`parse_dynamic_specs`): the record then carries the name
+    in every shape the axis flows into (``emmy/compiler/trace/dynamic.py:68-88`` builds the same ``dynamic_shapes``)."""
+    dynamic_shapes = None
+    if dynamic:
+        import inspect
+
+        params = [p for p in inspect.signature(module.forward).parameters]
+        dims: dict[str, Any] = {}
+        dynamic_shapes = {p: None for p in params[: len(args)]}
+        dynamic_shapes.update({k: None for k in (kwargs or {})})
+        for name, inp, axis in dynamic:
+            if inp not in dynamic_shapes:
+                raise ValueError(f"--dynamic: the traced call has no input named {inp!r} (inputs: {list(dynamic_shapes)})")
+            dims.setdefault(name, torch.export.Dim(name, min=2, max=DYNAMIC_DIM_MAX))
+            dynamic_shapes[inp] = {**(dynamic_shapes[inp] or {}), axis: dims[name]}
+    exported = torch.export.export(module, args, kwargs=kwargs or None, dynamic_shapes=dynamic_shapes)
+    symbols: dict[str, str] = {}
+    if dynamic:
+        by_input = {}
+        for name, inp, axis in dynamic:
+            by_input.setdefault(inp, []).append((axis, name))
+        user_inputs = [n for n in exported.graph.nodes if n.op == "placeholder"
+                       and n.name not in exported.graph_signature.inputs_to_parameters
+                       and n.name not in exported.graph_signature.inputs_to_buffers]
+        for ph, pname in zip(user_inputs, list(dynamic_shapes)):
+            for axis, name in by_input.get(pname, []):
+                d = ph.meta["val"].shape[axis]
+                if not isinstance(d, int):
+                    symbols[str(d)] = name
     sig = exported.graph_signature
     param_paths = dict(sig.inputs_to_parameters)
     param_paths.update(sig.inputs_to_buffers)
@@ -168,7 +244,7 @@ def trace_module(module: torch.nn.Module, args: tuple, kwargs: dict | None = Non
 
     for node in exported.graph.nodes:
         if node.op == "placeholder":
-            shape, dtype = _shape_dtype(node)
+            shape, dtype = _shape_dtype(node, symbols)
             if node.name in param_paths:
                 path = param_paths[node.name]
                 sources[node.name] = path
@@ -182,7 +258,7 @@ def trace_module(module: torch.nn.Module, args: tuple, kwargs: dict | None = Non
             target = str(node.target)
             if not isinstance(node.meta.get("val"), torch.Tensor):
                 continue  # metadata assertions and other value-less bookkeeping nodes
-            shape, dtype = _shape_dtype(node)
+            shape, dtype = _shape_dtype(node, symbols)
             a = list(node.args)
             kw = dict(node.kwargs)
             tin = [x.name for x in a if hasattr(x, "name")]

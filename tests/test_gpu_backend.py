@@ -76,3 +76,32 @@ def test_benchmark_async_result_shape(backend):
     assert res.min_ms <= res.time_ms <= res.max_ms
     assert seen == list(range(5))
     assert lt.time_ms < 0.1  # a 0.5 MB rmsnorm is microseconds, not a host-timed call
+
+
+def test_symbolic_sequence_length_one_compile_many_sizes(backend):
+    """A graph traced with a symbolic axis is compiled once and run at several runtime sizes (one launch plan per
+    size, weights uploaded once) — the reference's dynamic ``seq_len`` (``emmy/compiler/backend/cuda/program.py:770-958``)."""
+    from deplodock_b200.trace import parse_dynamic_specs, trace_inline_code
+
+    tr = trace_inline_code("nn.RMSNorm(2048, eps=1e-6)(torch.randn(1, 32, 2048))", parse_dynamic_specs(["seq_len@x:1"]))
+    plan = backend.compile(tr.graph)
+    assert plan.symbolic
+    w = (1 + 0.02 * torch.randn(2048, generator=torch.Generator().manual_seed(1))).numpy()
+    for S in (32, 7, 300):
+        x = torch.randn(1, S, 2048, generator=torch.Generator().manual_seed(S))
+        result, _ = backend.run(plan, input_data={"x": x.numpy(), "p_weight": w})
+        out = result.outputs["rms_norm"]
+        assert out.shape == (1, S, 2048)
+        metrics.assert_fp32_reduction(out, cpu_ref.rmsnorm(x, torch.from_numpy(w), 1e-6), what=f"S={S}")
+    assert len(plan.variants) == 3
+    assert len({id(v.const_cache) for v in plan.variants.values()}) == 1 and "p_weight" in plan.const_cache
+    # attention with the sequence axis symbolic on q, k and v
+    code = ("q=torch.randn(1,4,48,128).bfloat16(); k=torch.randn(1,2,48,128).bfloat16(); "
+            "v=torch.randn(1,2,48,128).bfloat16(); F.scaled_dot_product_attention(q,k,v,is_causal=True,enable_gqa=True)")
+    tr = trace_inline_code(code, parse_dynamic_specs(["s@q:2", "s@k:2", "s@v:2"]))
+    plan = backend.compile(tr.graph)
+    for S in (48, 200):
+        q, k, v = inputs.sdpa_inputs(1, 4, 2, S, seed=S)
+        result, _ = backend.run(plan, input_data={"q": q, "k": k, "v": v})
+        got = torch.from_numpy(result.outputs[plan.outputs[0]].view(np.int16)).view(torch.bfloat16)
+        metrics.assert_bf16_tensor_path(got, cpu_ref.sdpa_causal_gqa(q, k, v), what=f"sdpa S={S}")

@@ -76,7 +76,10 @@ def test_graph_validation_errors():
     with pytest.raises(KeyError):
         Graph.from_dict(base)
     bad = {"inputs": ["x"], "outputs": ["x"], "nodes": {
-        "x": {"op": "InputOp", "op_fields": {}, "inputs": [], "output": {"name": "x", "shape": ["seq_len"], "dtype": "f32"}}}}
+        "x": {"op": "InputOp", "op_fields": {}, "inputs": [], "output": {"name": "x", "shape": ["seq len ("], "dtype": "f32"}}}}
+    with pytest.raises(ValueError):
+        Graph.from_dict(bad)
+    bad["nodes"]["x"]["output"] = {"name": "x", "shape": [2.5], "dtype": "f32"}
     with pytest.raises(ValueError):
         Graph.from_dict(bad)
     bad["nodes"]["x"]["output"] = {"name": "x", "shape": [2], "dtype": "q4"}
@@ -355,3 +358,64 @@ def test_ops_check_buffer_sizes_before_the_call():
     with pytest.raises(TypeError):
         ops._check_buffer("out", torch.zeros(16), 16, torch.bfloat16)
     ops._check_buffer("out", None, 16, torch.bfloat16)
+
+
+# ------------------------------------------------------------------------------------------------ symbolic dimensions
+def _symbolic_record():
+    return _rec({
+        "x": ("InputOp", [], [2, "seq_len", 256], "f32", {}),
+        "w": ("ConstantOp", [], [256], "f32", {}),
+        "y": ("RmsNormOp", ["x", "w"], [2, "seq_len", 256], "f32", {"eps": 1e-6}),
+        "flat": ("ReshapeOp", ["y"], ["(seq_len * 2)", 256], "f32", {"shape": ["(seq_len * 2)", 256]})}, ["x"], ["flat"])
+
+
+def test_symbolic_dims_resolve_from_input_shapes():
+    """Records carry atomic symbolic dims as names and composite ones as expressions (``emmy/compiler/graph.py:953-1007``);
+    the values come from the input arrays (``graph.py:686-706``)."""
+    from deplodock_b200.graph import Graph, eval_dim
+
+    g = Graph.from_dict(_symbolic_record())
+    assert g.is_symbolic and g.symbols() == {"seq_len"}
+    assert g.symbolic_env(None) == {} and g.symbolic_env({"w": np.zeros(256)}) == {}
+    env = g.symbolic_env({"x": np.zeros((2, 37, 256), dtype=np.float32)})
+    assert env == {"seq_len": 37}
+    r = g.resolve(env)
+    assert not r.is_symbolic and r.nodes["flat"].output.shape == (74, 256) and r.nodes["flat"].op_fields["shape"] == [74, 256]
+    assert g.nodes["x"].output.shape == (2, "seq_len", 256)   # the record itself is unchanged
+    assert g.to_dict()["nodes"]["x"]["output"]["shape"] == [2, "seq_len", 256]
+    assert eval_dim("round_up(seq_len, 64) // 2 + min(seq_len, 8)", {"seq_len": 100}) == 72
+    with pytest.raises(KeyError):
+        g.resolve({})
+    with pytest.raises(ValueError):
+        eval_dim("seq_len ** 2", {"seq_len": 3})
+
+
+def test_symbolic_graph_compiles_to_one_plan_per_binding():
+    from deplodock_b200.backend import B200Backend
+
+    plan = B200Backend().compile(_symbolic_record())
+    assert plan.symbolic and [s.entry for s in plan.steps] == ["emk_rmsnorm"] and "seq_len" in plan.describe()
+    assert plan.symbolic_env({"x": np.zeros((2, 5, 256))}) == {"seq_len": 5}
+    a = plan.variant_for({"x": np.zeros((2, 5, 256))})
+    b = plan.variant_for({"x": np.zeros((2, 9, 256))})
+    assert a is not b and a is plan.variant_for({"x": np.zeros((2, 5, 256))}) and len(plan.variants) == 2
+    assert a.graph.nodes["flat"].output.shape == (10, 256) and b.graph.nodes["y"].output.shape == (2, 9, 256)
+    assert a.const_cache is plan.const_cache          # weights are uploaded once for all bindings
+    with pytest.raises(KeyError):
+        plan.variant_for({})
+
+
+def test_dynamic_spec_grammar_and_tracing():
+    from deplodock_b200.trace import parse_dynamic_specs, trace_inline_code
+
+    assert parse_dynamic_specs(["seq_len@x:1", "seq_len@mask:2"]) == [("seq_len", "x", 1), ("seq_len", "mask", 2)]
+    for bad in ("seq_len", "seq_len@x", "@x:1", "s@:1", "s@x:one", "s@x:-1"):
+        with pytest.raises(ValueError):
+            parse_dynamic_specs([bad])
+    with pytest.raises(ValueError):
+        parse_dynamic_specs(["a@x:1", "b@x:1"])
+    tr = trace_inline_code("nn.RMSNorm(256, eps=1e-6)(torch.randn(2, 5, 256))", parse_dynamic_specs(["seq_len@x:1"]))
+    assert tr.graph.nodes["x"].output.shape == (2, "seq_len", 256)
+    assert tr.graph.nodes["rms_norm"].output.shape == (2, "seq_len", 256)
+    with pytest.raises(ValueError, match="no input named"):
+        trace_inline_code("nn.RMSNorm(256)(torch.randn(2, 5, 256))", [("s", "nope", 1)])
