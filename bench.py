@@ -226,9 +226,11 @@ def _graph_time_us(fn, reps: int, iters: int = 5) -> tuple[float, float]:
 
 
 def serving_table(weights) -> list[dict]:
-    """Requests per second of the serving-side runner (``deplodock_b200.runner``) on the two workloads the reference
-    quotes for its vLLM plugin (64 requests x 256 tokens; uniform 512 tokens): ids resident on the device, hidden
-    states of every token produced and cloned per request, all requests submitted at once."""
+    """Requests per second of the serving-side runner (``deplodock_b200.runner``): the two workloads the reference
+    quotes for its vLLM plugin (64 requests x 256 tokens; uniform 512 tokens) through the per-length and padded-group
+    routes, and the packed variable-length route (one forward over the concatenated stream, no padding) on the same
+    uniform workloads and on 64 requests of mixed lengths 64..512 — next to the padded route on that mix. Ids resident
+    on the device, hidden states of every token produced, all requests submitted at once."""
     import time
 
     import torch
@@ -238,6 +240,18 @@ def serving_table(weights) -> list[dict]:
     rows = []
     cfg = weights.cfg
     gen = torch.Generator().manual_seed(0)
+
+    def best_of(serve, n=3):
+        serve()   # captures the graph(s)
+        torch.cuda.synchronize()
+        best = float("inf")
+        for _ in range(n):
+            t0 = time.perf_counter()
+            out = serve()
+            torch.cuda.synchronize()
+            best = min(best, time.perf_counter() - t0)
+        return best, out
+
     for tokens, batch_cap in ((256, 1), (256, 8), (256, 32), (512, 32)):
         runner = EmbedForwardRunner(weights, max_seq_len=tokens, batch_cap=batch_cap)
         reqs = [torch.randint(0, cfg.vocab_size, (tokens,), generator=gen).cuda() for _ in range(64)]
@@ -247,17 +261,24 @@ def serving_table(weights) -> list[dict]:
                 return [runner.forward_hidden_states(r) for r in reqs]
             return runner.forward_hidden_states_batched(reqs)
 
-        serve()   # captures the graph(s)
-        torch.cuda.synchronize()
-        best = float("inf")
-        for _ in range(3):
-            t0 = time.perf_counter()
-            out = serve()
-            torch.cuda.synchronize()
-            best = min(best, time.perf_counter() - t0)
+        best, out = best_of(serve)
         assert len(out) == 64 and tuple(out[0].shape) == (tokens, cfg.hidden_size)
-        rows.append({"requests": 64, "tokens_per_request": tokens, "batch_cap": batch_cap,
-                     "req_per_s": round(64 / best, 1), "ms_total": round(best * 1e3, 2)})
+        rows.append({"route": "one graph per length" if batch_cap == 1 else "padded groups", "requests": 64,
+                     "tokens_per_request": tokens, "batch_cap": batch_cap, "req_per_s": round(64 / best, 1),
+                     "ms_total": round(best * 1e3, 2)})
+        del runner
+        torch.cuda.empty_cache()
+    mixed = [int(x) for x in torch.randint(64, 513, (64,), generator=gen)]
+    for label, lens in (("64 x 256", [256] * 64), ("64 x 512", [512] * 64), ("64 x mixed 64..512", mixed)):
+        runner = EmbedForwardRunner(weights, max_seq_len=512, batch_cap=64)
+        ids = torch.cat([torch.randint(0, cfg.vocab_size, (n,), generator=gen) for n in lens]).cuda()
+        pos = torch.cat([torch.arange(n) for n in lens])
+        for route, fn in (("packed variable-length", runner.forward_packed),
+                          ("padded groups", runner.forward_packed_padded)):
+            best, out = best_of(lambda fn=fn: fn(ids, pos))
+            assert tuple(out.shape) == (sum(lens), cfg.hidden_size)
+            rows.append({"route": route, "requests": 64, "tokens_per_request": label, "tokens": sum(lens),
+                         "req_per_s": round(64 / best, 1), "ms_total": round(best * 1e3, 2)})
         del runner
         torch.cuda.empty_cache()
     return rows
@@ -489,10 +510,11 @@ def gemm_event_pass(model, passes: int = 8, heat=None, gpu_index: int = 0) -> di
 
 
 # DRAM read + write bytes of ONE gemm2_bf16_kernel launch from an ncu capture of the model's down projection at the
-# full row count of a one-GPU shard (32768 x 3072 -> 1024 with the residual epilogue and the row sums of squares;
-# 201 MB activations + 67 MB residual in, 67 MB out: none of it fits the 126 MB L2 together). The summary with the
-# command is profiles/gemm2_bf16_down_proj_32768x3072x1024.md. Rows scale the figure for a smaller shard.
-GEMM_TRAFFIC_CAPTURE = {"bytes": None, "rows": 32768, "algorithmic_bytes": 32768 * (3072 + 1024 + 1024) * 2 + 1024 * 3072 * 2,
+# full row count of a one-GPU shard (32768 x 3072 -> 1024 with the residual epilogue; 201 MB activations + 67 MB
+# residual in, 67 MB out: together they do not fit the 126 MB L2, so the figure is not flattered by a resident
+# output): 292.3 MB read + 52.3 MB written = 344.6 MB against 341.8 MB algorithmic. The summary with the command is
+# profiles/gemm2_bf16_down_proj_32768x3072x1024.md. Rows scale the figure for a smaller shard.
+GEMM_TRAFFIC_CAPTURE = {"bytes": 344595712, "rows": 32768, "algorithmic_bytes": 32768 * (3072 + 1024 + 1024) * 2 + 1024 * 3072 * 2,
                         "kernel": "gemm2_bf16_kernel, down projection + residual of one rank's shard",
                         "source": "profiles/gemm2_bf16_down_proj_32768x3072x1024.md"}
 

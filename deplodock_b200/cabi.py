@@ -42,6 +42,7 @@ class GemmDesc(ctypes.Structure):
         ("row_sumsq_out", c_void_p),
         ("q_norm_weight", c_void_p), ("k_norm_weight", c_void_p), ("rope_chunk_major", c_void_p),
         ("seq_len", c_int64), ("num_q_heads", c_int64), ("num_kv_heads", c_int64), ("qk_eps", c_float),
+        ("positions", c_void_p),
     ]
 
 
@@ -88,6 +89,11 @@ _SIGNATURES: dict[str, list] = {
                                  c_int64, c_int64, c_float, c_void_p],
     "emk_sdpa_causal_gqa_bf16_tok": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                      c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_float, c_void_p],
+    "emk_sdpa_varlen_workspace_bytes": [c_int64, c_int64],
+    "emk_sdpa_causal_gqa_bf16_varlen": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                                        c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_float,
+                                        c_void_p, c_int64, c_void_p],
+    "emk_pool_norm_l2_varlen": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_float, c_void_p],
     "emk_sdpa_simt": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
                       c_int64, c_float, c_int, c_int, c_void_p],
     "emk_embed_gather": [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p],
@@ -98,7 +104,7 @@ _SIGNATURES: dict[str, list] = {
     "emk_selftest_wait_expiry": [c_void_p, c_int, c_void_p],
 }
 _RESTYPES = {"emk_status_string": c_char_p, "emk_last_error": c_char_p,
-             "emk_linear_bf16_w8_workspace_bytes": c_int64}
+             "emk_linear_bf16_w8_workspace_bytes": c_int64, "emk_sdpa_varlen_workspace_bytes": c_int64}
 
 #: every symbol ``include/emk.h`` declares; ``tests/test_cabi_symbols.py`` checks the header against this list
 EXPORTED_SYMBOLS = tuple(_SIGNATURES)

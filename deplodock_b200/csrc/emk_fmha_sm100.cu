@@ -64,6 +64,11 @@ struct FmhaArgs {
   float scale_log2;
   int* status;
   unsigned long long limit_ns;
+  // packed variable-length mode: one entry per 128-row query block of every sequence, heaviest first, written by
+  // varlen_items_kernel into the caller's workspace: {first token row of the sequence, q0 within it, its length, 0};
+  // n_entries[0] holds their number. Null in the fixed-length modes.
+  const int4* vl_items;
+  const int* vl_n_entries;
 };
 
 struct __align__(8) FmhaBarriers {
@@ -111,7 +116,14 @@ __device__ __forceinline__ unsigned long long add_f32x2(unsigned long long a, un
 // One unit of work: 128 query rows of the (up to) two query heads `hq0`, `hq0 + 1` that share KV head `hkv`.
 struct WorkItem {
   int b, hkv, hq0, q0, nblk;
+  int row0;   // token-row offset of the item's sequence (packed mode; 0 otherwise)
+  int slen;   // length of the item's sequence
   bool two;
+};
+
+// Number of work items and of rounds over the grid; fixed at launch, or read from the item table in packed mode.
+struct Sched {
+  int n_items, n_rounds;
 };
 
 // Items are numbered heaviest query block first and dealt to the CTAs in boustrophedon order (round r left to right,
@@ -122,6 +134,26 @@ __device__ __forceinline__ int item_of_round(int round, int cta, int grid) {
 
 __device__ __forceinline__ WorkItem decode_item(const FmhaArgs& a, int w) {
   WorkItem it;
+  if (a.vl_items != nullptr) {
+    // packed mode: entries are ordered heaviest query block first; the (KV head, head pair) combinations of an entry
+    // are consecutive items, so they run at the same time on neighbouring SMs and share the sequence's K/V in L2
+    const int per_entry = a.Hkv * a.pairs;
+    const int e = w / per_entry;
+    int rem = w - e * per_entry;
+    const int4 ent = __ldg(a.vl_items + e);
+    const int pair = rem % a.pairs;
+    it.hkv = rem / a.pairs;
+    it.b = 0;
+    it.hq0 = it.hkv * a.group + 2 * pair;
+    it.two = (2 * pair + 1) < a.group;
+    it.row0 = ent.x;
+    it.q0 = ent.y;
+    it.slen = ent.z;
+    it.nblk = ent.y / FM + 1;
+    return it;
+  }
+  it.row0 = 0;
+  it.slen = a.S;
   // (batch, KV head, head pair) triples are taken `a.gp` at a time; within such a group the query blocks go heaviest
   // first. Items that read the same K/V blocks then run at about the same time on different SMs, so all but the
   // first read hit in L2; with one group (small K/V) this is plain heaviest-first order.
@@ -152,10 +184,10 @@ __device__ __forceinline__ void reg_shrink() {
 }
 
 // Work items of this CTA in order: the item of the first round >= `rnd` that exists; returns false past the end.
-__device__ __forceinline__ bool next_item(const FmhaArgs& a, int& rnd, WorkItem& it) {
-  for (; rnd < a.n_rounds; ++rnd) {
+__device__ __forceinline__ bool next_item(const FmhaArgs& a, const Sched& sc, int& rnd, WorkItem& it) {
+  for (; rnd < sc.n_rounds; ++rnd) {
     const int w = item_of_round(rnd, (int)blockIdx.x, (int)gridDim.x);
-    if (w < a.n_items) {
+    if (w < sc.n_items) {
       it = decode_item(a, w);
       return true;
     }
@@ -214,6 +246,11 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   const WaitCtx wc{&bars->abort_flag, a.status, a.limit_ns};
   grid_dependency_wait();      // everything above overlaps the tail of the previous kernel in the stream
   grid_launch_dependents();
+  Sched sc{a.n_items, a.n_rounds};
+  if (a.vl_items != nullptr) {   // the item table was written by the kernel before this one in the stream
+    sc.n_items = *reinterpret_cast<const volatile int*>(a.vl_n_entries) * a.Hkv * a.pairs;
+    sc.n_rounds = (sc.n_items + (int)gridDim.x - 1) / (int)gridDim.x;
+  }
 
   // The CTA is persistent: every role walks the same list of work items with running counters for the barrier
   // phases. Nothing drains between items: the first S of the next item is issued right behind the last PV of the
@@ -226,19 +263,19 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
       uint32_t qn[2] = {0, 0};   // Q tiles loaded per tile slot
       bool ok = true;
       WorkItem it;
-      for (int rnd = 0; ok && next_item(a, rnd, it); ++rnd) {
+      for (int rnd = 0; ok && next_item(a, sc, rnd, it); ++rnd) {
         const int ntile = it.two ? 2 : 1;
         for (int t = 0; t < ntile && ok; ++t) {
           ok = mbar_wait(&bars->q_empty[t], (qn[t] & 1u) ^ 1u, wc, EMK_DEV_TIMEOUT_PRODUCER);
           if (!ok) break;
           ++qn[t];
           const int hq = it.hq0 + t;
-          const int y = it.b * a.q_rb + hq * a.q_rh + it.q0;
+          const int y = it.row0 + it.b * a.q_rb + hq * a.q_rh + it.q0;
           mbar_arrive_expect_tx(&bars->q_full[t], TILE_BYTES);
           tma_load_2d(sQ + t * TILE_BYTES, &tma_q, &bars->q_full[t], hq * a.q_cs, y);
           tma_load_2d(sQ + t * TILE_BYTES + HALF_BYTES, &tma_q, &bars->q_full[t], hq * a.q_cs + 64, y);
         }
-        const int ykv = it.b * a.kv_rb + it.hkv * a.kv_rh;
+        const int ykv = it.row0 + it.b * a.kv_rb + it.hkv * a.kv_rh;
         const int xkv = it.hkv * a.kv_cs;
         for (int j = 0; j < it.nblk && ok; ++j, ++kv_count) {
           const int st = (int)(kv_count % KV_STAGES);
@@ -300,13 +337,13 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
       };
       WorkItem it, nx;
       int rnd = 0;
-      bool have = next_item(a, rnd, it);
+      bool have = next_item(a, sc, rnd, it);
       if (have) {
         for (int t = 0; t < (it.two ? 2 : 1) && ok; ++t) first_s(t, 0, 0u, t == 0);
       }
       while (have && ok) {
         int rn = rnd + 1;
-        const bool have_next = next_item(a, rn, nx);
+        const bool have_next = next_item(a, sc, rn, nx);
         const int ntile = it.two ? 2 : 1;
         const int ntile_next = have_next ? (nx.two ? 2 : 1) : 0;
         for (int j = 0; j < it.nblk && ok; ++j, ++kv_count) {
@@ -359,7 +396,7 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     uint32_t items[2] = {0, 0};
     bool ok = true;
     WorkItem it;
-    for (int rnd = 0; ok && next_item(a, rnd, it); ++rnd) {
+    for (int rnd = 0; ok && next_item(a, sc, rnd, it); ++rnd) {
       const int ntile = it.two ? 2 : 1;
       for (int t = 0; t < ntile && ok; ++t) {
         const uint32_t tO = tmem_base + lane_base + 256u + (uint32_t)(t * HD);
@@ -373,10 +410,11 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
           mbar_arrive(&bars->v_empty[(kv_base + (uint32_t)it.nblk - 1u) % KV_STAGES]);
         const float inv = __fdividef(1.0f, bars->row_l[t][r_in_tile]);
         const int hq = it.hq0 + t;
-        const bool full = it.q0 + FM <= a.S;
+        const bool full = it.q0 + FM <= it.slen;
         const int q_row = it.q0 + r_in_tile;
         __nv_bfloat16* orow =
-            a.o + ((int64_t)it.b * a.o_rb + (int64_t)hq * a.o_rh + q_row) * a.ld_o + (int64_t)hq * a.o_cs;
+            a.o + ((int64_t)it.row0 + (int64_t)it.b * a.o_rb + (int64_t)hq * a.o_rh + q_row) * a.ld_o +
+            (int64_t)hq * a.o_cs;
         // the stores of the previous tile out of the staging buffers must have read them
         if (lane == 0) tma_store_wait_read();
         __syncwarp();
@@ -412,11 +450,11 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
               __syncwarp();
               if (lane == 0) {
                 tma_store_2d(&tma_o, stage + (c >> 1) * OSTAGE_BYTES, hq * a.o_cs + (c >> 1) * 64,
-                             it.b * a.o_rb + hq * a.o_rh + it.q0 + quarter * 32);
+                             it.row0 + it.b * a.o_rb + hq * a.o_rh + it.q0 + quarter * 32);
                 tma_store_commit();
               }
             }
-          } else if (q_row < a.S) {
+          } else if (q_row < it.slen) {
             // ragged last tile of a sequence: rows past the end are not stored
             st_global_v8(orow + c * 32, v);
             st_global_v8(orow + c * 32 + 16, v + 8);
@@ -441,7 +479,7 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     uint32_t item_n = 0;    // items this tile took part in
     bool ok = true;
     WorkItem it;
-    for (int rnd = 0; ok && next_item(a, rnd, it); ++rnd) {
+    for (int rnd = 0; ok && next_item(a, sc, rnd, it); ++rnd) {
       const int nblk = it.nblk;
       if (t == 1 && !it.two) {  // this tile sits the item out
         kv_base += (uint32_t)nblk;
@@ -487,10 +525,14 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
         }
         const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
         const float m_new = fmaxf(m_used, mx * a.scale_log2);
-        const bool need = (m_new - m_used) > RESCALE_THRESHOLD;  // true on the first block (m_used = -inf)
+        // The decision to move a row's reference maximum is the row's own (true on the first block, m_used = -inf),
+        // so a row's arithmetic does not depend on which rows share its warp; only the tensor-memory round trip that
+        // rescales O is taken warp-wide, with factor 1 for the rows that keep their maximum.
+        const bool need = (m_new - m_used) > RESCALE_THRESHOLD;
         if (__any_sync(0xffffffffu, need)) {
+          const float m_next = need ? m_new : m_used;
           if (j > 0) {  // PV of block j-1 has completed: implied by the S commit waited on above
-            const float alpha = ex2_approx(m_used - m_new);
+            const float alpha = need ? ex2_approx(m_used - m_next) : 1.0f;
             l *= alpha;
 #pragma unroll 1
             for (int c = 0; c < HD / 32; ++c) {
@@ -503,7 +545,7 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
             }
             tmem_st_wait();
           }
-          m_used = m_new;
+          m_used = m_next;
         }
         const unsigned long long neg_m2 = pack_f32x2(-m_used, -m_used);
         const unsigned long long scale2 = pack_f32x2(a.scale_log2, a.scale_log2);
@@ -560,12 +602,64 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   if (warp == 0) tmem_dealloc(tmem_base, 512);
 }
 
+// Item table of the packed variable-length mode. One 1024-thread CTA: thread l owns query-block level l (query rows
+// 128 l .. 128 l + 127) and walks the sequences twice — once to count how many are long enough to have that block,
+// once to write their entries — so entries come out grouped by level, deepest (= most KV blocks) level first, in
+// sequence order within a level. table[0].x receives the number of entries; entries start at table[1].
+constexpr int VL_MAX_LEVELS = 1024;
+
+__global__ void __launch_bounds__(VL_MAX_LEVELS) varlen_items_kernel(const int* __restrict__ cu_seqlens, int B,
+                                                                     int levels, int4* __restrict__ table) {
+  __shared__ int count[VL_MAX_LEVELS];
+  __shared__ int offset[VL_MAX_LEVELS];
+  const int l = (int)threadIdx.x;
+  grid_dependency_wait();
+  grid_launch_dependents();
+  int c = 0;
+  if (l < levels) {
+    for (int b = 0; b < B; ++b) {
+      const int len = cu_seqlens[b + 1] - cu_seqlens[b];
+      c += (len > l * FM) ? 1 : 0;
+    }
+  }
+  count[l] = c;
+  __syncthreads();
+  if (l == 0) {
+    int run = 0;
+    for (int k = levels - 1; k >= 0; --k) {   // deepest level first
+      offset[k] = run;
+      run += count[k];
+    }
+    table[0] = make_int4(run, 0, 0, 0);
+  }
+  __syncthreads();
+  if (l < levels && c > 0) {
+    int4* out = table + 1 + offset[l];
+    for (int b = 0; b < B; ++b) {
+      const int r0 = cu_seqlens[b];
+      const int len = cu_seqlens[b + 1] - r0;
+      if (len > l * FM) *out++ = make_int4(r0, l * FM, len, 0);
+    }
+  }
+}
+
 constexpr int FMHA_SMEM = (2 + 2 * KV_STAGES) * TILE_BYTES + 8 * OSTAGE_BYTES + 1024 + (int)sizeof(FmhaBarriers);
 static_assert(FMHA_SMEM <= 232448, "shared memory budget");
 
+// Packed mode: `cu_seqlens` (device, B + 1 ints) is given, S is the longest sequence the caller admits and `total`
+// the number of token rows; the operands are token-major.
+struct VarlenArgs {
+  const int* cu_seqlens;
+  int64_t total;
+  void* workspace;
+  int64_t workspace_bytes;
+};
+
+int64_t varlen_max_entries(int64_t B, int64_t total) { return total / FM + B; }
+
 int fmha_launch(emk_handle_t h, const void* q, const void* k, const void* v, void* o, int64_t B, int64_t Hq,
                 int64_t Hkv, int64_t S, int64_t D, bool token_major, int64_t ld_q, int64_t ld_k, int64_t ld_v,
-                int64_t ld_o, float scale, cudaStream_t s) {
+                int64_t ld_o, float scale, cudaStream_t s, const VarlenArgs* vl = nullptr) {
   if (!h || !q || !k || !v || !o) return EMK_ERR_ARG;
   if (B <= 0 || Hq <= 0 || Hkv <= 0 || S <= 0) return EMK_ERR_SHAPE;
   if (D != HD) {
@@ -577,7 +671,23 @@ int fmha_launch(emk_handle_t h, const void* q, const void* k, const void* v, voi
                 (long long)Hkv);
     return EMK_ERR_SHAPE;
   }
-  if (B * Hq * S > 0x7fffffffLL || B * S > 0x7fffffffLL) return EMK_ERR_SHAPE;
+  if (!vl && (B * Hq * S > 0x7fffffffLL || B * S > 0x7fffffffLL)) return EMK_ERR_SHAPE;
+  const int64_t rows = vl ? vl->total : B * S;   // token rows of the token-major operands
+  if (vl) {
+    if (!token_major || !vl->cu_seqlens || !vl->workspace || vl->total <= 0 || vl->total > 0x7fffffffLL)
+      return EMK_ERR_ARG;
+    if ((S + FM - 1) / FM > VL_MAX_LEVELS) {
+      EMK_SET_ERR(h, "emk_sdpa_causal_gqa_bf16_varlen: max_seqlen %lld exceeds %d tokens", (long long)S,
+                  VL_MAX_LEVELS * FM);
+      return EMK_ERR_LIMIT;
+    }
+    if (vl->workspace_bytes < (1 + varlen_max_entries(B, vl->total)) * (int64_t)sizeof(int4) ||
+        ((uintptr_t)vl->workspace & 15u) != 0) {
+      EMK_SET_ERR(h, "emk_sdpa_causal_gqa_bf16_varlen: workspace of %lld bytes is too small or not 16-byte aligned "
+                  "(see emk_sdpa_varlen_workspace_bytes)", (long long)vl->workspace_bytes);
+      return EMK_ERR_WORKSPACE;
+    }
+  }
   if ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)o) & 15u) != 0) return EMK_ERR_ALIGN;
   if (token_major && ((ld_q | ld_k | ld_v | ld_o) % 8) != 0) return EMK_ERR_ALIGN;
 
@@ -593,6 +703,8 @@ int fmha_launch(emk_handle_t h, const void* q, const void* k, const void* v, voi
   a.scale_log2 = scale * 1.4426950408889634f;
   a.status = h->status_dev;
   a.limit_ns = h->wait_limit_ns;
+  a.vl_items = nullptr;
+  a.vl_n_entries = nullptr;
 
   CUtensorMap tq, tk, tv, to;
   int rc;
@@ -619,16 +731,16 @@ int fmha_launch(emk_handle_t h, const void* q, const void* k, const void* v, voi
     a.o_cs = HD; a.o_rb = (int)S; a.o_rh = 0;
     a.ld_o = ld_o;
     if (ld_q < Hq * HD || ld_k < Hkv * HD || ld_v < Hkv * HD || ld_o < Hq * HD) return EMK_ERR_SHAPE;
-    rc = emk_make_tmap_2d(h, &tq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, q, (uint64_t)(Hq * HD), (uint64_t)(B * S),
+    rc = emk_make_tmap_2d(h, &tq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, q, (uint64_t)(Hq * HD), (uint64_t)rows,
                           (uint64_t)ld_q * 2, 64, FM, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
-    rc = emk_make_tmap_2d(h, &tk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, k, (uint64_t)(Hkv * HD), (uint64_t)(B * S),
+    rc = emk_make_tmap_2d(h, &tk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, k, (uint64_t)(Hkv * HD), (uint64_t)rows,
                           (uint64_t)ld_k * 2, 64, FN, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
-    rc = emk_make_tmap_2d(h, &tv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, v, (uint64_t)(Hkv * HD), (uint64_t)(B * S),
+    rc = emk_make_tmap_2d(h, &tv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, v, (uint64_t)(Hkv * HD), (uint64_t)rows,
                           (uint64_t)ld_v * 2, 64, FN, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
-    rc = emk_make_tmap_2d(h, &to, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, o, (uint64_t)(Hq * HD), (uint64_t)(B * S),
+    rc = emk_make_tmap_2d(h, &to, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, o, (uint64_t)(Hq * HD), (uint64_t)rows,
                           (uint64_t)ld_o * 2, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
   }
@@ -641,7 +753,8 @@ int fmha_launch(emk_handle_t h, const void* q, const void* k, const void* v, voi
       once.done[h->device] = true;
     }
   }
-  const int64_t n_items = (int64_t)a.nqblk * B * Hkv * a.pairs;
+  // packed mode: the item count is known on the device only; the grid is sized for the upper bound
+  const int64_t n_items = (vl ? varlen_max_entries(B, vl->total) : (int64_t)a.nqblk * B) * Hkv * a.pairs;
   if (n_items > 0x7fffffffLL) return EMK_ERR_SHAPE;
   a.n_items = (int)n_items;
   const int grid = a.n_items < h->sm_count ? a.n_items : h->sm_count;  // persistent: one CTA per SM
@@ -655,6 +768,16 @@ int fmha_launch(emk_handle_t h, const void* q, const void* k, const void* v, voi
     if (gp < 1) gp = 1;
     if (gp > per_qblk) gp = per_qblk;
     a.gp = (int)gp;
+  }
+  if (vl) {
+    int4* table = (int4*)vl->workspace;
+    a.vl_n_entries = (const int*)table;
+    a.vl_items = table + 1;
+    a.B = 1;
+    a.q_rb = a.kv_rb = a.o_rb = 0;
+    EMK_CUDA_TRY(h, launch_after_prologue(varlen_items_kernel, 1u, (unsigned)VL_MAX_LEVELS, 0, s,
+                                          h->overlap_launch != 0, vl->cu_seqlens, (int)B, (int)((S + FM - 1) / FM),
+                                          table));
   }
   EMK_CUDA_TRY(h, launch_after_prologue(fmha_causal_kernel, (unsigned)grid, FMHA_THREADS, FMHA_SMEM, s,
                                         h->overlap_launch != 0, tq, tk, tv, to, a));
@@ -675,4 +798,19 @@ extern "C" int emk_sdpa_causal_gqa_bf16_tok(emk_handle_t h, const void* q, const
                                             int64_t ld_k, int64_t ld_v, int64_t ld_o, float scale,
                                             emk_stream_t stream) {
   return fmha_launch(h, q, k, v, o, B, Hq, Hkv, S, D, true, ld_q, ld_k, ld_v, ld_o, scale, (cudaStream_t)stream);
+}
+
+extern "C" int64_t emk_sdpa_varlen_workspace_bytes(int64_t B, int64_t total_tokens) {
+  if (B <= 0 || total_tokens <= 0) return 0;
+  return (1 + varlen_max_entries(B, total_tokens)) * (int64_t)sizeof(int4);
+}
+
+extern "C" int emk_sdpa_causal_gqa_bf16_varlen(emk_handle_t h, const void* q, const void* k, const void* v, void* o,
+                                               const int32_t* cu_seqlens, int64_t B, int64_t total_tokens,
+                                               int64_t max_seqlen, int64_t Hq, int64_t Hkv, int64_t D, int64_t ld_q,
+                                               int64_t ld_k, int64_t ld_v, int64_t ld_o, float scale, void* workspace,
+                                               int64_t workspace_bytes, emk_stream_t stream) {
+  VarlenArgs vl{cu_seqlens, total_tokens, workspace, workspace_bytes};
+  return fmha_launch(h, q, k, v, o, B, Hq, Hkv, max_seqlen, D, true, ld_q, ld_k, ld_v, ld_o, scale,
+                     (cudaStream_t)stream, &vl);
 }

@@ -26,6 +26,7 @@ struct GemmArgs {
   const __nv_bfloat16* qk_rope;  // chunk-major cos|sin table [8][S][16] bf16 (see emk.h)
   int qk_S, qk_Hq, qk_Hkv;
   float qk_eps;
+  const int* qk_pos;             // rotary position of every row (packed sequences); null: position = row % qk_S
   // RMSNorm folded around the GEMM (the norm weight is folded into W by the caller):
   //   ss_in   partial sums of squares [M][ss_in_segs] of the un-normalised input rows (one slot per 128 columns):
   //           accumulator rows are scaled by rsqrt(sum_s ss_in[s][row] * ss_inv_dim + ss_eps) before the epilogue
@@ -159,6 +160,13 @@ __device__ __forceinline__ float epilogue_store32(const GemmArgs& g, const uint3
 }
 
 
+// Rotary position of output row `row`: given per row for packed sequences (clamped to the table), else the row's
+// offset within its fixed-length sequence.
+__device__ __forceinline__ int rope_position(const GemmArgs& g, int row) {
+  if (g.qk_pos != nullptr) return min(max(__ldg(g.qk_pos + row), 0), g.qk_S - 1);
+  return row % g.qk_S;
+}
+
 // Issued by an epilogue thread BEFORE it waits for its accumulator: everything the epilogue will read from global
 // memory for this row segment is pulled towards the SM while the tensor core is still working on the tile, so the
 // epilogue (two warps per scheduler, little latency hiding of its own) finds it in L1 / L2.
@@ -169,7 +177,7 @@ __device__ __forceinline__ void epilogue_prefetch(const GemmArgs& g, int row, in
   }
   if (g.epi == EMK_EPI_QKNORM_ROPE_INTERNAL) {
     if ((n0 >> 7) < g.qk_Hq + g.qk_Hkv) {
-      const __nv_bfloat16* tp = g.qk_rope + (int64_t)(row % g.qk_S) * 16;
+      const __nv_bfloat16* tp = g.qk_rope + (int64_t)rope_position(g, row) * 16;
 #pragma unroll
       for (int q = 0; q < 8; ++q) asm volatile("prefetch.global.L1 [%0];" ::"l"(tp + (int64_t)q * g.qk_S * 16));
     }
@@ -227,7 +235,7 @@ __device__ __forceinline__ void epilogue_head_qknorm_rope(const GemmArgs& g, uin
     // The table is chunk-major: chunk q of position s is 32 bytes (8 cos then 8 sin values of elements 8q..8q+7;
     // cos[i] == cos[i + 64] so the first 64 elements suffice). The lanes of a warp are consecutive rows, hence
     // consecutive positions, so each of these loads is one contiguous kilobyte per warp.
-    const int s = row % g.qk_S;
+    const int s = rope_position(g, row);
     const __nv_bfloat16* tp = g.qk_rope + (int64_t)s * 16;
 #pragma unroll
     for (int q = 0; q < 8; ++q) {

@@ -199,6 +199,7 @@ struct QkRopeArgs {
   const void *qw, *kw, *rope;
   int S, Hq, Hkv;
   float eps;
+  const int* pos;
 };
 
 struct RowStatArgs {
@@ -250,6 +251,7 @@ int gemm_dispatch(emk_handle_t h, const void* x, const void* w, const void* resi
     g.ss_out = rsx->ss_out;
   }
   g.qk_qw = g.qk_kw = g.qk_rope = nullptr;
+  g.qk_pos = nullptr;
   g.qk_S = g.qk_Hq = g.qk_Hkv = 0;
   g.qk_eps = 0.f;
   if (qk) {  // fused q/k-norm + RoPE epilogue: 256-column CTA-pair tiles only (two whole heads per tile)
@@ -261,6 +263,7 @@ int gemm_dispatch(emk_handle_t h, const void* x, const void* w, const void* resi
     g.qk_Hq = qk->Hq;
     g.qk_Hkv = qk->Hkv;
     g.qk_eps = qk->eps;
+    g.qk_pos = qk->pos;
     return emk_gemm2_launch(h, x, w, g, wlayout, s);
   }
   // CTA-pair tiles (256x256) when the problem has at least one full pair tile; single-CTA tiles otherwise.
@@ -329,14 +332,17 @@ extern "C" int emk_gemm_bf16_fused(emk_handle_t h, const emk_gemm_desc_t* d, emk
   if (d->epilogue == EMK_EPI_QKNORM_ROPE) {
     if (!d->x || !d->w || !d->y || !d->q_norm_weight || !d->k_norm_weight || !d->rope_chunk_major) return EMK_ERR_ARG;
     const int64_t S = d->seq_len, Hq = d->num_q_heads, Hkv = d->num_kv_heads;
-    if (S <= 0 || Hq <= 0 || Hkv <= 0 || d->N != (Hq + 2 * Hkv) * 128 || d->M % S != 0 || d->wlayout != EMK_W_NK) {
-      EMK_SET_ERR(h, "q/k-norm + RoPE epilogue: N must be (Hq + 2*Hkv)*128, M a multiple of seq_len, W [N,K]");
+    if (S <= 0 || Hq <= 0 || Hkv <= 0 || d->N != (Hq + 2 * Hkv) * 128 || (!d->positions && d->M % S != 0) ||
+        d->wlayout != EMK_W_NK) {
+      EMK_SET_ERR(h, "q/k-norm + RoPE epilogue: N must be (Hq + 2*Hkv)*128, M a multiple of seq_len (unless "
+                  "positions are given), W [N,K]");
       return EMK_ERR_SHAPE;
     }
     if ((((uintptr_t)d->q_norm_weight | (uintptr_t)d->k_norm_weight) & 15u) != 0 ||
         (((uintptr_t)d->y | (uintptr_t)d->rope_chunk_major) & 31u) != 0)
       return EMK_ERR_ALIGN;
-    QkRopeArgs qk{d->q_norm_weight, d->k_norm_weight, d->rope_chunk_major, (int)S, (int)Hq, (int)Hkv, d->qk_eps};
+    QkRopeArgs qk{d->q_norm_weight, d->k_norm_weight, d->rope_chunk_major, (int)S, (int)Hq, (int)Hkv, d->qk_eps,
+                  d->positions};
     return gemm_dispatch(h, d->x, d->w, nullptr, nullptr, d->y, d->M, d->N, d->K, EMK_W_NK, EMK_EPI_NONE, s, &qk,
                          any_rs ? &rs : nullptr);
   }

@@ -119,15 +119,25 @@ __global__ void __launch_bounds__(512, 2) qknorm_rope_kernel(__nv_bfloat16* __re
 
 // One CTA per sequence: RMSNorm of the last token's hidden row, rounded to bf16 like the module output, then L2
 // normalisation in fp32.
+// `cu_seqlens` null: sequence b is rows b*S .. b*S+S-1; else its last row is cu_seqlens[b+1]-1 (packed sequences).
 __global__ void __launch_bounds__(256) pool_norm_l2_kernel(const __nv_bfloat16* __restrict__ hs,
                                                            const __nv_bfloat16* __restrict__ w,
-                                                           float* __restrict__ out, int S, int hidden, float eps) {
+                                                           float* __restrict__ out, int S, int hidden, float eps,
+                                                           const int* __restrict__ cu_seqlens) {
   __shared__ float red[8];
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   const int64_t b = blockIdx.x;
-  const __nv_bfloat16* row = hs + (b * S + (S - 1)) * (int64_t)hidden;
   grid_dependency_wait();
   grid_launch_dependents();
+  int64_t last = b * S + (S - 1);
+  if (cu_seqlens != nullptr) {
+    last = (int64_t)cu_seqlens[b + 1] - 1;
+    if (cu_seqlens[b + 1] <= cu_seqlens[b]) {   // empty sequence: a zero row
+      for (int c = threadIdx.x; c < hidden; c += 256) out[b * hidden + c] = 0.f;
+      return;
+    }
+  }
+  const __nv_bfloat16* row = hs + last * (int64_t)hidden;
   float ss = 0.f;
   for (int c = threadIdx.x; c < hidden; c += 256) {
     const float f = __bfloat162float(row[c]);
@@ -256,7 +266,20 @@ extern "C" int emk_pool_norm_l2(emk_handle_t h, const void* hidden_states, const
   if (B <= 0 || S <= 0 || hidden <= 0) return EMK_ERR_SHAPE;
   EMK_CUDA_TRY(h, launch_after_prologue(pool_norm_l2_kernel, (unsigned)B, 256u, 0, (cudaStream_t)stream,
                                         h->overlap_launch != 0, (const __nv_bfloat16*)hidden_states,
-                                        (const __nv_bfloat16*)w, out, (int)S, (int)hidden, eps));
+                                        (const __nv_bfloat16*)w, out, (int)S, (int)hidden, eps,
+                                        (const int*)nullptr));
+  EMK_LAUNCH_CHECK(h);
+  return EMK_OK;
+}
+
+extern "C" int emk_pool_norm_l2_varlen(emk_handle_t h, const void* hidden_states, const void* w, float* out,
+                                       const int32_t* cu_seqlens, int64_t B, int64_t hidden, float eps,
+                                       emk_stream_t stream) {
+  if (!h || !hidden_states || !w || !out || !cu_seqlens) return EMK_ERR_ARG;
+  if (B <= 0 || hidden <= 0) return EMK_ERR_SHAPE;
+  EMK_CUDA_TRY(h, launch_after_prologue(pool_norm_l2_kernel, (unsigned)B, 256u, 0, (cudaStream_t)stream,
+                                        h->overlap_launch != 0, (const __nv_bfloat16*)hidden_states,
+                                        (const __nv_bfloat16*)w, out, 0, (int)hidden, eps, (const int*)cu_seqlens));
   EMK_LAUNCH_CHECK(h);
   return EMK_OK;
 }

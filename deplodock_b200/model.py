@@ -335,3 +335,93 @@ class EmbedForward:
             raise ValueError(f"expected ids of shape {(self.batch, self.seq)}, got {tuple(ids.shape)}")
         self.ids.copy_(ids, non_blocking=True)
         return self.replay()
+
+
+class PackedForward:
+    """The same trunk over a PACKED stream of sequences of different lengths: ``tokens`` rows in all, up to
+    ``max_seqs`` sequences, none longer than ``max_seq_len`` — the wire format of the reference's vLLM plugin
+    (``emmy/serving/vllm_model.py:70-91``: packed ``(num_tokens,)`` ids and 0-based per-request positions), run the way
+    its serving notes ask for as follow-up #1 (``emmy/serving/ARCHITECTURE.md:133-137``): one forward at mixed lengths,
+    no padding between sequences. The GEMMs run over the token rows as they are (rows are independent); the fused
+    QKV epilogue takes each row's rotary position from ``positions``; attention walks a table of 128-row query blocks
+    built on the device from ``cu_seqlens``; pooling reads each sequence's last row.
+
+    Everything that varies between requests lives in device buffers (``ids``, ``positions``, ``cu_seqlens``), so one
+    captured CUDA graph per token budget serves any mix of lengths. Rows past the last sequence are computed from
+    token 0 and ignored."""
+
+    def __init__(self, weights: EmbedWeights, *, tokens: int, max_seqs: int, max_seq_len: int,
+                 workspace: EmbedWorkspace | None = None, hidden_states: bool = True, pool: bool = True) -> None:
+        self.weights = weights
+        self.cfg = c = weights.cfg
+        if not weights.fold_rmsnorm:
+            raise ValueError("the packed plan uses the folded-RMSNorm weights")
+        self.device = dev = weights.device
+        self.tokens, self.max_seqs, self.max_seq_len = int(tokens), int(max_seqs), int(max_seq_len)
+        self.hidden_states, self.pool = bool(hidden_states), bool(pool)
+        T = self.tokens
+        if workspace is None:
+            workspace = EmbedWorkspace(c, T, self.max_seqs, dev)
+        if workspace.max_tokens < T or workspace.max_batch < self.max_seqs:
+            raise ValueError("workspace too small for this plan")
+        ws = self.workspace = workspace
+        self.ids = ws.ids[:T]
+        self.h, self.hs = ws.h[:T], ws.hs[:T]
+        self.qkv, self.attn, self.mlp = ws.qkv[:T], ws.attn[:T], ws.mlp[:T]
+        self.ss1, self.ss2 = ws.ss1[:T], ws.ss2[:T]
+        self.out = ws.out[: self.max_seqs]
+        self.attn.zero_()   # rows outside every sequence are never written by the attention kernel
+        self.positions = torch.zeros(T, dtype=torch.int32, device=dev)
+        self.cu_seqlens = torch.zeros(self.max_seqs + 1, dtype=torch.int32, device=dev)
+        self.vl_ws = ops.sdpa_varlen_workspace(self.max_seqs, T, dev)
+        cos, sin = rope_tables(self.max_seq_len, c.head_dim, c.rope_theta, dev)
+        self.rope_cm = ops.rope_chunk_major(cos, sin)
+        self._graph: torch.cuda.CUDAGraph | None = None
+
+    @property
+    def num_launches(self) -> int:
+        return 1 + 6 * self.cfg.num_hidden_layers + int(self.hidden_states) + int(self.pool)
+
+    def set_batch(self, ids: torch.Tensor, positions: torch.Tensor, cu_seqlens: torch.Tensor) -> None:
+        """Copy a packed batch into the static buffers: ``ids`` / ``positions`` ``(n,)`` with ``n <= tokens``,
+        ``cu_seqlens`` ``(b + 1,)`` with ``b <= max_seqs`` (unused sequence slots become empty sequences)."""
+        n, b = int(ids.shape[0]), int(cu_seqlens.shape[0]) - 1
+        if n > self.tokens or b > self.max_seqs:
+            raise ValueError(f"batch of {n} tokens / {b} sequences exceeds the plan ({self.tokens} / {self.max_seqs})")
+        self.ids[:n].copy_(ids, non_blocking=True)
+        self.positions[:n].copy_(positions, non_blocking=True)
+        if n < self.tokens:
+            self.ids[n:].zero_()
+            self.positions[n:].zero_()
+        self.cu_seqlens[: b + 1].copy_(cu_seqlens, non_blocking=True)
+        if b < self.max_seqs:
+            self.cu_seqlens[b + 1:].fill_(n)
+
+    def forward_eager(self) -> None:
+        c = self.cfg
+        nq, nkv, H, eps = c.num_attention_heads, c.num_key_value_heads, c.hidden_size, c.rms_norm_eps
+        ops.embed_gather(self.weights.embed, self.ids, out=self.h, row_sumsq=self.ss1)
+        for lw in self.weights.layers:
+            ops.gemm_fused(self.h, lw.wqkv, self.qkv, epilogue="qknorm_rope", row_sumsq_in=self.ss1, norm_dim=H,
+                           norm_eps=eps, q_weight=lw.qn, k_weight=lw.kn, rope_cm=self.rope_cm, S=self.max_seq_len,
+                           Hq=nq, Hkv=nkv, qk_eps=eps, positions=self.positions)
+            ops.sdpa_causal_gqa_varlen(self.qkv, self.cu_seqlens, self.max_seq_len, nq, nkv, self.attn,
+                                       workspace=self.vl_ws)
+            ops.gemm_fused(self.attn, lw.wo, self.h, epilogue="residual", residual=self.h, row_sumsq_out=self.ss2)
+            ops.gemm_fused(self.h, lw.wgu, self.mlp, epilogue="swiglu", row_sumsq_in=self.ss2, norm_dim=H,
+                           norm_eps=eps)
+            ops.gemm_fused(self.mlp, lw.wdown, self.h, epilogue="residual", residual=self.h, row_sumsq_out=self.ss1)
+        if self.hidden_states:
+            ops.rmsnorm(self.h, self.weights.final_norm, eps, out=self.hs)
+        if self.pool:
+            ops.pool_norm_l2_varlen(self.h, self.weights.final_norm, self.cu_seqlens, eps, out=self.out)
+
+    def replay(self) -> None:
+        if self._graph is None:
+            self.forward_eager()
+            torch.cuda.synchronize(self.device)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self.forward_eager()
+            self._graph = g
+        self._graph.replay()

@@ -183,7 +183,8 @@ def linear_qknorm_rope(x, w_qkv, q_weight, k_weight, rope_cm, S: int, Hq: int, H
 
 def gemm_fused(x, w, out, *, epilogue: str = "none", residual=None, w_is_kn: bool = False, row_sumsq_in=None,
                norm_dim: int = 0, norm_eps: float = 1e-6, row_sumsq_out=None, q_weight=None,
-               k_weight=None, rope_cm=None, S: int = 0, Hq: int = 0, Hkv: int = 0, qk_eps: float = 1e-6):
+               k_weight=None, rope_cm=None, S: int = 0, Hq: int = 0, Hkv: int = 0, qk_eps: float = 1e-6,
+               positions=None):
     """``emk_gemm_bf16_fused``: the tcgen05 GEMM with an epilogue (``none | residual | bias | swiglu | qknorm_rope``)
     and an RMSNorm folded around it through per-row partial sum-of-squares buffers ``[M, dim/128]`` fp32 (see
     ``emk_gemm_desc_t``)."""
@@ -220,6 +221,10 @@ def gemm_fused(x, w, out, *, epilogue: str = "none", residual=None, w_is_kn: boo
     d.k_norm_weight = k_weight.data_ptr() if k_weight is not None else None
     d.rope_chunk_major = rope_cm.data_ptr() if rope_cm is not None else None
     d.seq_len, d.num_q_heads, d.num_kv_heads, d.qk_eps = int(S), int(Hq), int(Hkv), float(qk_eps)
+    if positions is not None:   # rotary position per row (packed sequences); S is then the table length
+        _check_cuda_contig(positions)
+        _check_buffer("positions", positions, M, torch.int32)
+        d.positions = positions.data_ptr()
     h = handle()
     h.check(h.lib.emk_gemm_bf16_fused(h.ptr, _ct.byref(d), _stream()), "emk_gemm_bf16_fused")
     return out
@@ -419,6 +424,57 @@ def sdpa_causal_gqa_tok(qkv: torch.Tensor, B: int, S: int, Hq: int, Hkv: int, ou
         h.ptr, c_void_p(qp), c_void_p(qp + Hq * D * esz), c_void_p(qp + (Hq + Hkv) * D * esz), _ptr(out), B, Hq, Hkv,
         S, D, ld, ld, ld, Hq * D, float(scale), _stream()), "emk_sdpa_causal_gqa_bf16_tok")
     return out
+
+
+def sdpa_varlen_workspace(B: int, total_tokens: int, device) -> torch.Tensor:
+    """Scratch for :func:`sdpa_causal_gqa_varlen` (the table of query blocks built from ``cu_seqlens``)."""
+    n = int(handle().lib.emk_sdpa_varlen_workspace_bytes(int(B), int(total_tokens)))
+    return torch.empty(max(n, 16), dtype=torch.uint8, device=device)
+
+
+def sdpa_causal_gqa_varlen(qkv: torch.Tensor, cu_seqlens: torch.Tensor, max_seqlen: int, Hq: int, Hkv: int,
+                           out: torch.Tensor, workspace: torch.Tensor | None = None,
+                           scale: float | None = None) -> torch.Tensor:
+    """Causal GQA attention over packed sequences: ``qkv [T, (Hq+2*Hkv)*128]`` token-major, sequence ``b`` in rows
+    ``cu_seqlens[b]:cu_seqlens[b+1]`` (int32 CUDA tensor ``[B+1]``), none longer than ``max_seqlen``; writes
+    ``out [T, Hq*128]``. One launch whatever the mix of lengths, no padding between sequences."""
+    _check_cuda_contig(qkv, cu_seqlens, out, workspace)
+    D = 128
+    ld = qkv.shape[-1]
+    T = qkv.numel() // ld
+    B = cu_seqlens.numel() - 1
+    if cu_seqlens.dtype != torch.int32 or B <= 0:
+        raise TypeError("cu_seqlens must be an int32 tensor of B + 1 entries")
+    if qkv.dtype != torch.bfloat16 or ld != (Hq + 2 * Hkv) * D:
+        raise ValueError("qkv must be bfloat16 [T, (Hq + 2*Hkv) * 128]")
+    _check_buffer("out", out, T * Hq * D, torch.bfloat16)
+    if workspace is None:
+        workspace = sdpa_varlen_workspace(B, T, qkv.device)
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    esz = qkv.element_size()
+    h = handle()
+    qp = qkv.data_ptr()
+    h.check(h.lib.emk_sdpa_causal_gqa_bf16_varlen(
+        h.ptr, c_void_p(qp), c_void_p(qp + Hq * D * esz), c_void_p(qp + (Hq + Hkv) * D * esz), _ptr(out),
+        _ptr(cu_seqlens), B, T, int(max_seqlen), Hq, Hkv, D, ld, ld, ld, Hq * D, float(scale), _ptr(workspace),
+        workspace.numel() * workspace.element_size(), _stream()), "emk_sdpa_causal_gqa_bf16_varlen")
+    return out
+
+
+def pool_norm_l2_varlen(hidden_states, weight, cu_seqlens: torch.Tensor, eps: float = 1e-6, out=None) -> torch.Tensor:
+    """Last-token pooling of packed sequences + final RMSNorm + L2 normalisation: ``[B, hidden]`` fp32."""
+    _check_cuda_contig(hidden_states, weight, cu_seqlens, out)
+    if cu_seqlens.dtype != torch.int32:
+        raise TypeError("cu_seqlens must be int32")
+    B = cu_seqlens.numel() - 1
+    hidden = hidden_states.shape[-1]
+    y = torch.empty(B, hidden, dtype=torch.float32, device=hidden_states.device) if out is None else out
+    _check_buffer("out", y, B * hidden, torch.float32)
+    h = handle()
+    h.check(h.lib.emk_pool_norm_l2_varlen(h.ptr, _ptr(hidden_states), _ptr(weight), _ptr(y), _ptr(cu_seqlens), B,
+                                          hidden, float(eps), _stream()), "emk_pool_norm_l2_varlen")
+    return y
 
 
 def sdpa_simt(q, k, v, causal: bool, scale: float | None = None) -> torch.Tensor:

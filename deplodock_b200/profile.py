@@ -62,7 +62,7 @@ REF_ROWS_MAX = 12
 #: CUDA function names of this library's kernels (the reference's emitted kernels are literally called ``k_*``; the
 #: hand-written ones are told apart from PyTorch's by this pattern)
 OWN_KERNEL_RE = re.compile(
-    r"^(?:void\s+)?(?:\(anonymous namespace\)::|emk::)*"
+    r"^(?:void\s+)?(?:\(anonymous namespace\)::|<unnamed>::|emk::)*"
     r"(rmsnorm_|softmax_|gemm2?_|gemm_w8|gemm_f32|expand_e4m3|fmha_|sdpa_|embed_gather|pool_norm|qknorm_rope|"
     r"elementwise_|loop_|linear_|varlen_|emk_|k_)")
 

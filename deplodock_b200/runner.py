@@ -11,10 +11,14 @@ its vLLM model (``emmy/serving/vllm_model.py:70-91``, ``emmy/serving/packed.py:6
   (and graph) per ``(group size, padded length)``; right padding is exact under the causal mask (a token attends only to
   earlier positions), and padded rows are not read out.
 * ``forward_packed(input_ids, positions)`` — vLLM's packed ``(num_tokens,)`` ids with 0-based per-request positions,
-  split at ``positions == 0`` (``split_spans``), run batched, concatenated back; the tail is zero-padded to
-  ``num_tokens`` like ``EmmyEmbedModel.forward``.
+  split at ``positions == 0`` (``split_spans``) and run as ONE variable-length forward over the stream as it is
+  (``deplodock_b200.model.PackedForward``: rotary positions per row, attention over a ``cu_seqlens`` table, no padding
+  between sequences; one captured graph per token budget of 128-token steps) — the reference's stated follow-up for
+  this seam (``emmy/serving/ARCHITECTURE.md:133-137``); the result covers ``num_tokens`` rows like
+  ``EmmyEmbedModel.forward``. ``forward_packed_padded`` keeps the earlier route (groups padded to their longest
+  sequence) for comparison.
 * ``embed_packed`` — last-token pooling + L2 normalisation of each span (what vLLM's pooler does after the reference's
-  forward, ``vllm_model.py:50-58``).
+  forward, ``vllm_model.py:50-58``), from the same variable-length forward.
 
 The trunk dtype is bf16 (the reference's runner supports fp16 / fp32 only, ``vllm_model.py:34-45``).
 """
@@ -25,7 +29,7 @@ from collections import OrderedDict
 
 import torch
 
-from deplodock_b200.model import EmbedConfig, EmbedForward, EmbedWeights, EmbedWorkspace
+from deplodock_b200.model import EmbedConfig, EmbedForward, EmbedWeights, EmbedWorkspace, PackedForward
 
 #: plans (CUDA graphs) kept per runner before the least recently used one is dropped
 PLAN_CACHE_MAX = 64
@@ -67,6 +71,13 @@ class EmbedForwardRunner:
             raise ValueError("max_tokens is smaller than one padded sequence")
         self.workspace = EmbedWorkspace(self.cfg, self.max_tokens, self.batch_cap, weights.device)
         self._plans: OrderedDict[tuple[int, int], EmbedForward] = OrderedDict()
+        self._packed: OrderedDict[int, PackedForward] = OrderedDict()
+        #: sequences one packed forward admits (a packed stream of max_tokens one-token requests at the extreme)
+        self.packed_max_seqs = max(self.batch_cap, min(self.max_tokens, 1024))
+        if self.workspace.out.shape[0] < self.packed_max_seqs:
+            self.workspace.out = torch.empty(self.packed_max_seqs, self.cfg.hidden_size, dtype=torch.float32,
+                                             device=weights.device)
+            self.workspace.max_batch = self.packed_max_seqs
         self.captures = 0   # plans built so far (each one captures a CUDA graph on first use)
 
     @classmethod
@@ -150,9 +161,59 @@ class EmbedForwardRunner:
         return results  # type: ignore[return-value]
 
     # -- the packed seam of the vLLM plugin ------------------------------------------------------------------------
+    def _packed_plan(self, tokens: int) -> PackedForward:
+        bucket = min(-(-max(tokens, 1) // PAD_TO) * PAD_TO, -(-self.max_tokens // PAD_TO) * PAD_TO)
+        plan = self._packed.get(bucket)
+        if plan is not None:
+            self._packed.move_to_end(bucket)
+            return plan
+        plan = PackedForward(self.weights, tokens=bucket, max_seqs=self.packed_max_seqs, max_seq_len=self.max_seq_len,
+                             workspace=self.workspace if bucket <= self.workspace.max_tokens else None)
+        self.captures += 1
+        self._packed[bucket] = plan
+        if len(self._packed) > PLAN_CACHE_MAX:
+            self._packed.popitem(last=False)
+        return plan
+
+    def _run_packed(self, input_ids: torch.Tensor, positions):
+        """One variable-length forward per ``max_tokens`` worth of whole spans. Yields ``(plan, first row of the
+        chunk in the stream, rows, spans of the chunk relative to it)`` after each replay; the plan's buffers are
+        valid until the next one."""
+        n = int(input_ids.shape[0])
+        dev = self.weights.device
+        ids = input_ids.to(device=dev).clamp(0, self.cfg.vocab_size - 1).to(torch.int64)
+        pos = positions.detach().cpu().reshape(-1).tolist() if isinstance(positions, torch.Tensor) else list(positions)
+        spans = split_spans(pos, self.max_seq_len)
+        i = 0
+        while i < len(spans):
+            j, start = i, spans[i][0]
+            while j < len(spans) and spans[j][1] - start <= self.max_tokens and j - i < self.packed_max_seqs:
+                j += 1
+            end = spans[j - 1][1]
+            rel = [(a - start, b - start) for a, b in spans[i:j]]
+            plan = self._packed_plan(end - start)
+            # positions restart at 0 in every span (a span cut at max_seq_len continues a request: it is a new
+            # sequence for the trunk, as in the reference's split)
+            p = torch.cat([torch.arange(b - a, dtype=torch.int32) for a, b in rel]).to(dev, non_blocking=True)
+            cu = torch.tensor([0] + [b for _, b in rel], dtype=torch.int32).to(dev, non_blocking=True)
+            plan.set_batch(ids[start:end], p, cu)
+            plan.replay()
+            yield plan, start, end - start, rel
+            i = j
+        if not spans and n:
+            return
+
     def forward_packed(self, input_ids: torch.Tensor, positions) -> torch.Tensor:
         """``input_ids`` ``(num_tokens,)`` packed sequences, ``positions`` their 0-based per-request positions (tensor or
-        sequence); returns ``(num_tokens, hidden)`` bf16, zero rows where the spans do not cover the tail."""
+        sequence); returns ``(num_tokens, hidden)`` bf16 final-norm hidden states."""
+        n = int(input_ids.shape[0])
+        out = torch.zeros(n, self.hidden_size, dtype=torch.bfloat16, device=self.weights.device)
+        for plan, start, rows, _ in self._run_packed(input_ids, positions):
+            out[start:start + rows].copy_(plan.hs[:rows])
+        return out
+
+    def forward_packed_padded(self, input_ids: torch.Tensor, positions) -> torch.Tensor:
+        """The same result by the padded route: spans run as batched groups, each padded to its longest sequence."""
         n = int(input_ids.shape[0])
         ids = input_ids.clamp(0, self.cfg.vocab_size - 1).to(torch.int64)
         pos = positions.detach().cpu().reshape(-1).tolist() if isinstance(positions, torch.Tensor) else list(positions)
@@ -168,8 +229,7 @@ class EmbedForwardRunner:
 
     def embed_packed(self, input_ids: torch.Tensor, positions) -> torch.Tensor:
         """Last-token pooling and L2 normalisation per span: ``(num_sequences, hidden)`` fp32."""
-        pos = positions.detach().cpu().reshape(-1).tolist() if isinstance(positions, torch.Tensor) else list(positions)
-        spans = split_spans(pos, self.max_seq_len)
-        hidden = self.forward_packed(input_ids, pos)
-        last = torch.tensor([b - 1 for _, b in spans], dtype=torch.int64, device=hidden.device)
-        return torch.nn.functional.normalize(hidden.index_select(0, last).float(), p=2.0, dim=-1)
+        rows = [plan.out[: len(rel)].clone() for plan, _, _, rel in self._run_packed(input_ids, positions)]
+        if not rows:
+            return torch.zeros(0, self.hidden_size, dtype=torch.float32, device=self.weights.device)
+        return torch.cat(rows, dim=0)

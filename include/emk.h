@@ -160,6 +160,10 @@ typedef struct {
   const void* rope_chunk_major;
   int64_t seq_len, num_q_heads, num_kv_heads;
   float qk_eps;
+  /* optional, EMK_EPI_QKNORM_ROPE: rotary position of every row, int32 [M] on the device (packed sequences of
+   * different lengths, the "positions" of the reference's packed serving seam, emmy/serving/packed.py:6-34); seq_len
+   * is then the number of positions the table holds and M need not be a multiple of it. NULL: position = m % seq_len */
+  const int32_t* positions;
 } emk_gemm_desc_t;
 int emk_gemm_bf16_fused(emk_handle_t h, const emk_gemm_desc_t* desc, emk_stream_t stream);
 
@@ -193,6 +197,26 @@ int emk_embed_gather_sumsq(emk_handle_t h, const void* table, const int64_t* ids
 int emk_sdpa_causal_gqa_bf16_tok(emk_handle_t h, const void* q, const void* k, const void* v, void* o, int64_t B,
                                  int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int64_t ld_q, int64_t ld_k,
                                  int64_t ld_v, int64_t ld_o, float scale, emk_stream_t stream);
+
+/* Causal GQA attention over PACKED sequences of different lengths (the follow-up the reference names for its serving
+ * path: cu_seqlens-aware attention tiles, one launch at mixed lengths, emmy/serving/ARCHITECTURE.md:133-137;
+ * emmy/serving/packed.py:6-34 defines the packed stream). Token-major operands as in emk_sdpa_causal_gqa_bf16_tok over
+ * `total_tokens` rows; sequence b occupies rows cu_seqlens[b] .. cu_seqlens[b+1]-1 (int32 [B+1] ON THE DEVICE, so the
+ * call can be replayed from a CUDA graph with new lengths); no sequence may be longer than max_seqlen (<= 131072).
+ * Rows not covered by any sequence are not written. `workspace` (device, 16-byte aligned, at least
+ * emk_sdpa_varlen_workspace_bytes(B, total_tokens)) receives the table of 128-row query blocks a small kernel
+ * builds from cu_seqlens before the attention kernel runs. */
+int64_t emk_sdpa_varlen_workspace_bytes(int64_t B, int64_t total_tokens);
+int emk_sdpa_causal_gqa_bf16_varlen(emk_handle_t h, const void* q, const void* k, const void* v, void* o,
+                                    const int32_t* cu_seqlens, int64_t B, int64_t total_tokens, int64_t max_seqlen,
+                                    int64_t Hq, int64_t Hkv, int64_t D, int64_t ld_q, int64_t ld_k, int64_t ld_v,
+                                    int64_t ld_o, float scale, void* workspace, int64_t workspace_bytes,
+                                    emk_stream_t stream);
+
+/* Pooling for packed sequences: out[b,:] = L2-normalise(RMSNorm(hidden_states[cu_seqlens[b+1]-1, :]; w, eps)), the
+ * last token of every sequence (emk_pool_norm_l2 with per-sequence lengths). Empty sequences give zero rows. */
+int emk_pool_norm_l2_varlen(emk_handle_t h, const void* hidden_states, const void* w, float* out,
+                            const int32_t* cu_seqlens, int64_t B, int64_t hidden, float eps, emk_stream_t stream);
 
 /* In place on the fused QKV projection output [T, (Hq+2*Hkv)*128] (T tokens, bf16, position of token t = t % S):
  * per-head RMSNorm (weights qw, kw [128] bf16, eps) on the Hq query heads and Hkv key heads, then rotate-half RoPE

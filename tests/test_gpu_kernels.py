@@ -521,3 +521,77 @@ def test_row_sumsq_out_small_shapes(ops, M, K, N):
     assert torch.allclose(ss.sum(1), h.float().pow(2).sum(-1), rtol=1e-4, atol=1e-3)
     # and against the oracle's rows (bf16 rounding of h is the only difference)
     assert torch.allclose(ss.sum(1).cpu(), ref_h.float().pow(2).sum(-1), rtol=2e-2, atol=1e-2)
+
+
+# ------------------------------------------------------------------------------------------------------------
+# Packed variable-length attention and pooling
+# ------------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("lens,Hq,Hkv", [([33, 128, 5], 4, 2), ([1, 127, 129, 0, 300, 256], 16, 8), ([512], 2, 2),
+                                         ([130, 130, 130, 7], 3, 1)])
+def test_sdpa_varlen_matches_per_sequence_oracle(ops, lens, Hq, Hkv):
+    """Sequences packed back to back (no padding), one launch; every sequence against the eager CPU call on its own
+    rows; an empty sequence and a trailing run of rows outside every sequence are left untouched."""
+    g = torch.Generator().manual_seed(sum(lens) + Hq)
+    tail = 9
+    T = sum(lens) + tail
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * 128, generator=g).bfloat16()
+    cu = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32)
+    out = torch.full((T, Hq * 128), 7.0, dtype=torch.bfloat16, device="cuda")
+    ops.sdpa_causal_gqa_varlen(_dev(qkv), _dev(cu), max(lens), Hq, Hkv, out)
+    ops.device_status()
+    got = out.cpu()
+    off = 0
+    for n in lens:
+        if n:
+            rows = qkv[off:off + n]
+            q = rows[:, : Hq * 128].view(1, n, Hq, 128).transpose(1, 2)
+            k = rows[:, Hq * 128: (Hq + Hkv) * 128].view(1, n, Hkv, 128).transpose(1, 2)
+            v = rows[:, (Hq + Hkv) * 128:].view(1, n, Hkv, 128).transpose(1, 2)
+            ref = cpu_ref.sdpa_causal_gqa(q, k, v).transpose(1, 2).reshape(n, Hq * 128)
+            metrics.assert_bf16_tensor_path(got[off:off + n], ref, what=f"sequence of {n} at row {off}")
+        off += n
+    assert (got[off:] == 7.0).all(), "rows outside every sequence were written"
+
+
+def test_sdpa_varlen_equals_fixed_length_kernel_bitwise(ops):
+    """Equal lengths: the packed path must give the bits of the fixed-length token-major path (same blocks of keys,
+    same per-row arithmetic; only the order in which work items are visited differs)."""
+    B, S, Hq, Hkv = 5, 300, 4, 2
+    qkv = torch.randn(B * S, (Hq + 2 * Hkv) * 128, generator=torch.Generator().manual_seed(3)).bfloat16().cuda()
+    a = torch.empty(B * S, Hq * 128, dtype=torch.bfloat16, device="cuda")
+    b = torch.empty_like(a)
+    ops.sdpa_causal_gqa_tok(qkv, B, S, Hq, Hkv, a)
+    cu = torch.arange(0, (B + 1) * S, S, dtype=torch.int32, device="cuda")
+    ops.sdpa_causal_gqa_varlen(qkv, cu, S, Hq, Hkv, b)
+    ops.device_status()
+    assert torch.equal(a, b)
+
+
+def test_sdpa_varlen_argument_checks(ops):
+    qkv = torch.zeros(256, 4 * 128, dtype=torch.bfloat16, device="cuda")
+    out = torch.zeros(256, 2 * 128, dtype=torch.bfloat16, device="cuda")
+    cu = torch.tensor([0, 256], dtype=torch.int32, device="cuda")
+    with pytest.raises(ValueError, match="workspace"):
+        ops.sdpa_causal_gqa_varlen(qkv, cu, 256, 2, 1, out, workspace=torch.zeros(16, dtype=torch.uint8, device="cuda"))
+    with pytest.raises(TypeError):
+        ops.sdpa_causal_gqa_varlen(qkv, cu.long(), 256, 2, 1, out)
+    with pytest.raises(ValueError):
+        ops.sdpa_causal_gqa_varlen(qkv, cu, 1 << 20, 2, 1, out)   # longer than the query-block table admits
+
+
+def test_pool_norm_l2_varlen(ops):
+    H = 1024
+    lens = [5, 0, 9, 1]
+    g = torch.Generator().manual_seed(2)
+    hs = torch.randn(sum(lens), H, generator=g).bfloat16()
+    w = (1 + 0.1 * torch.randn(H, generator=g)).bfloat16()
+    cu = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32)
+    got = ops.pool_norm_l2_varlen(_dev(hs), _dev(w), _dev(cu)).cpu()
+    ops.device_status()
+    for b, n in enumerate(lens):
+        if n == 0:
+            assert float(got[b].abs().max()) == 0.0
+            continue
+        last = hs[int(cu[b + 1]) - 1]
+        ref = torch.nn.functional.normalize(cpu_ref.rmsnorm_hf(last[None], w).float(), dim=-1)[0]
+        assert (got[b] - ref).abs().max().item() < 2e-4

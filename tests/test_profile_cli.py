@@ -45,6 +45,9 @@ def test_csv_reduction_sides_and_roofline_columns():
     assert parsed[own]["sm__warps_active.avg.pct_of_peak_sustained_active"] == 12.0   # everything else is averaged
     assert parsed[own]["launches"] == 2 and parsed[ref]["launches"] == 1
     assert profile.is_own_kernel(own) and not profile.is_own_kernel(ref)
+    # ncu's own spelling of an anonymous namespace, with and without a return type
+    assert profile.is_own_kernel("void <unnamed>::gemm2_bf16_kernel<256, 3, 1, 2>(CUtensorMap_st, CUtensorMap_st, GemmArgs)")
+    assert profile.is_own_kernel("<unnamed>::gemm_w8_kernel(CUtensorMap_st, CUtensorMap_st, W8Args)")
     units = profile.ncu_units(csv_text)
     assert units["gpu__time_duration.sum"] == "nsecond"
     profile.add_roofline(parsed, units, 6454.9)

@@ -131,6 +131,44 @@ def test_packed_forward_and_pooling(small_runner):
 
 
 @pytest.mark.gpu
+def test_packed_mixed_lengths_equal_per_sequence_runs(small_runner):
+    """The variable-length forward (one launch of every kernel over the packed stream, no padding) against each
+    sequence run alone through its own fixed-length plan: rows are independent in every kernel and the attention
+    kernel visits the same blocks of keys, so the hidden states agree to the bit for sequences on the same GEMM
+    kernel (more than 128 rows) and to rounding noise otherwise; and against the padded route."""
+    cfg, sd, runner = small_runner
+    lens = [200, 384, 130, 256, 7, 1, 129]
+    seqs = [inputs.token_ids(1, n, cfg.vocab_size, seed=50 + i)[0] for i, n in enumerate(lens)]
+    packed = torch.cat(seqs).cuda()
+    positions = torch.cat([torch.arange(n) for n in lens]).cuda()
+    before = runner.captures
+    out = runner.forward_packed(packed, positions)
+    assert runner.captures == before + 1            # one plan (one graph) for the whole stream
+    assert tuple(out.shape) == (sum(lens), cfg.hidden_size)
+    padded = runner.forward_packed_padded(packed, positions)
+    off = 0
+    for s, n in zip(seqs, lens):
+        alone = runner.forward_hidden_states(s.cuda())
+        if n > 128:
+            assert torch.equal(out[off:off + n], alone), f"sequence of {n} tokens at row {off}"
+        assert _cos(out[off:off + n].float(), alone.float()).min().item() >= 0.9999
+        assert _cos(out[off:off + n].float(), padded[off:off + n].float()).min().item() >= 0.9999
+        _assert_hidden(out[off:off + n], cpu_ref.trunk_hidden_states(s[None], cfg, sd)[0], f"len {n}")
+        off += n
+    # a second stream with other lengths in the same token budget replays the same graph
+    lens2 = [384, 384, 300, 39]
+    seqs2 = [inputs.token_ids(1, n, cfg.vocab_size, seed=70 + i)[0] for i, n in enumerate(lens2)]
+    assert sum(lens2) == sum(lens)
+    c0 = runner.captures
+    out2 = runner.forward_packed(torch.cat(seqs2).cuda(), torch.cat([torch.arange(n) for n in lens2]).cuda())
+    assert runner.captures == c0
+    off = 0
+    for s, n in zip(seqs2, lens2):
+        _assert_hidden(out2[off:off + n], cpu_ref.trunk_hidden_states(s[None], cfg, sd)[0], f"second stream, len {n}")
+        off += n
+
+
+@pytest.mark.gpu
 def test_limits(small_runner):
     cfg, _, runner = small_runner
     with pytest.raises(ValueError, match="exceeds max_seq_len"):
