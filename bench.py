@@ -176,7 +176,12 @@ def reference_emitted_kernels():
         if not torch.cuda.is_available() or not ref_kernels.available():
             return None
         rows = []
-        for name in ("rmsnorm", "softmax", "linear", "sdpa"):
+        import json as _json
+
+        built = _json.loads((ref_kernels.REF_DIR / "manifest.json").read_text())
+        for name in ("rmsnorm", "softmax", "linear", "sdpa", "matmul_f32"):
+            if name not in built:
+                continue
             k = ref_kernels.RefKernel(name)
             if name == "rmsnorm":
                 x, w = inputs.rmsnorm_inputs()
@@ -186,6 +191,9 @@ def reference_emitted_kernels():
             elif name == "linear":
                 x, w = inputs.linear_inputs()
                 k.bind(input=x, linear_wt=w.t().contiguous())
+            elif name == "matmul_f32":
+                g = torch.Generator().manual_seed(0)
+                k.bind(a=torch.randn(512, 1024, generator=g), b=torch.randn(1024, 2048, generator=g))
             else:
                 q, kk, v = inputs.sdpa_inputs()
                 k.bind(q=q, k=kk, v=v)
@@ -284,6 +292,22 @@ def serving_table(weights) -> list[dict]:
     return rows
 
 
+def loop_record_table() -> list[dict]:
+    """The reference's eleven shipped Loop-IR kernel records (``kernels/*.json``, held as fixtures under
+    ``tests/golden/loop_records``) through ``B200Backend.benchmark``: recognised, lowered to one launch each, timed
+    with the backend's own protocol (CUDA-graph windows, median)."""
+    from deplodock_b200.backend import B200Backend
+
+    rows = []
+    be = B200Backend()
+    for path in sorted((ROOT / "tests" / "golden" / "loop_records").glob("k_*.json")):
+        plan = be.compile(path)
+        res = be.benchmark(plan, warmup=3, num_iters=10)
+        rows.append({"record": path.stem, "entry": plan.steps[0].entry, "us": round(res.time_ms * 1e3, 2),
+                     "us_min": round((res.min_ms or 0.0) * 1e3, 2)})
+    return rows
+
+
 def kernel_cases() -> dict:
     """The named kernel configurations: ``name -> builder``; a builder allocates the seeded device inputs and returns
     ``(launch thunk, bound, algorithmic work per launch, unit scale, peak key, note, launches per timing graph)``."""
@@ -378,7 +402,34 @@ def kernel_cases() -> dict:
                     f"the attention launch of the model plan at {B} sequences: token-major fused QKV buffer", 20)
         return build
 
+    def matmul_f32(M, K, N, extra=None):
+        """The fp32 tier of the reference's perf suite (tests/perf/cases.py:60-74): Qwen3 projection shapes as
+        torch.matmul (B row-major [K, N]), torch.matmul + r and silu(x @ wg) * (x @ wu)."""
+        def build():
+            g = gen()
+            a = torch.randn(M, K, device=dev, generator=g)
+            b = torch.randn(K, N, device=dev, generator=g)
+            flops = 2 * M * K * N
+            note = "fp32 CUDA-core FMAs (72 TFLOP/s nominal at 148 SMs x 128 lanes x 1.9 GHz), not a tensor-core rate"
+            if extra == "add":
+                r = torch.randn(M, N, device=dev, generator=g)
+                fn = lambda: ops.elementwise("add", ops.linear_f32(a, b, None, True), r)  # noqa: E731
+            elif extra == "gated":
+                b2 = torch.randn(K, N, device=dev, generator=g)
+                fn = lambda: ops.elementwise("silu_multiply", ops.linear_f32(a, b, None, True),  # noqa: E731
+                                             ops.linear_f32(a, b2, None, True))
+                flops *= 2
+            else:
+                fn = lambda: ops.linear_f32(a, b, None, True)  # noqa: E731
+            return fn, "fma", flops, 1e12, "f32_tflops_nominal", note, 20
+        return build
+
     return {
+        "k_matmul f32 512x1024x2048 (q_proj s512)": matmul_f32(512, 1024, 2048),
+        "k_matmul f32 128x1024x2048 (q_proj s128)": matmul_f32(128, 1024, 2048),
+        "k_matmul f32 32x1024x2048 (q_proj s32)": matmul_f32(32, 1024, 2048),
+        "k_matmul_add f32 512x3072x1024 (down_proj + r s512)": matmul_f32(512, 3072, 1024, "add"),
+        "k_gated_mlp f32 512x1024x3072 (silu(x@wg)*(x@wu) s512)": matmul_f32(512, 1024, 3072, "gated"),
         "k_rms_norm [1,32,2048] f32": rms_small,
         "k_rms_norm [32768,1024] bf16": rms_big,
         "k_softmax [1,28,2048,2048] f32": softmax,
@@ -420,7 +471,7 @@ def kernel_table(peaks: dict, only: str | None = None, launches: int = 0) -> lis
         else:
             us, mn = _graph_time_us(fn, reps)
         achieved = work / (us * 1e-6) / unit_scale
-        peak = peaks[peak_key]
+        peak = peaks.get(peak_key, 72.0)   # fp32 CUDA-core rows: nominal 148 SMs x 128 FMA lanes x 2 x 1.9 GHz
         rows.append({"kernel": name, "us": round(us, 2), "us_min": round(mn, 2), "bound": bound,
                      "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s" if bound == "hbm" else "TFLOP/s",
                      "frac": round(achieved / peak, 4), "note": note})
@@ -681,6 +732,7 @@ def main() -> None:
             del weights
             torch.cuda.empty_cache()
             line["kernels"] = kernel_table(peaks)
+            line["loop_records"] = loop_record_table()
         parity_ok = True
         if check:
             # The CPU oracle (eager trunk) on the same weights and the same 64 sequences: it is the timed CPU baseline

@@ -1,4 +1,5 @@
-"""Recipe for ``oracle/_ref/``: the reference compiler's own emitted CUDA kernels for the four kernel configurations.
+"""Recipe for ``oracle/_ref/``: the reference compiler's own emitted CUDA kernels for the four kernel configurations
+and for one fp32 projection of its perf suite.
 
 TEST AND REFERENCE-TIMING INFRASTRUCTURE, not product code. Run where the reference checkout is importable (it is not on the GPU
 box; the outputs travel there):
@@ -33,6 +34,8 @@ CONFIGS = {
     "sdpa": ("q=torch.randn(4, 16, 2048, 128).bfloat16(); k=torch.randn(4, 8, 2048, 128).bfloat16(); "
              "v=torch.randn(4, 8, 2048, 128).bfloat16(); "
              "F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)"),
+    # the fp32 tier the reference's own perf suite drives (tests/perf/cases.py:60-74): the Qwen3 q_proj at 512 tokens
+    "matmul_f32": "a=torch.randn(512,1024); b=torch.randn(1024,2048); torch.matmul(a,b)",
 }
 
 

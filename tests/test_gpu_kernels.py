@@ -595,3 +595,31 @@ def test_pool_norm_l2_varlen(ops):
         last = hs[int(cu[b + 1]) - 1]
         ref = torch.nn.functional.normalize(cpu_ref.rmsnorm_hf(last[None], w).float(), dim=-1)[0]
         assert (got[b] - ref).abs().max().item() < 2e-4
+
+
+# ------------------------------------------------------------------------------------------------------------
+# fp32 contraction on CUDA cores (register-tiled), both weight layouts, bias, ragged and unaligned shapes
+# ------------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("M,K,N", [(512, 1024, 2048), (32, 1024, 2048), (128, 3072, 1024), (100, 68, 132),
+                                   (65, 16, 64), (1, 8, 4), (70, 36, 90), (33, 30, 50)])
+@pytest.mark.parametrize("kn", [False, True])
+def test_linear_f32_tiled_and_fallback(ops, M, K, N, kn):
+    """K (and N for [K,N] weights) a multiple of 4 takes the register-tiled kernel, anything else the one-output-per
+    thread kernel; both against a float64 product, and the tiled kernel bit-for-bit against the serial fmaf chain."""
+    g = torch.Generator().manual_seed(M + K + N)
+    x = torch.randn(M, K, generator=g)
+    w = torch.randn(N, K, generator=g)
+    bias = torch.randn(N, generator=g)
+    wd = _dev(w.t().contiguous() if kn else w)
+    got = ops.linear_f32(_dev(x), wd, _dev(bias), kn).cpu()
+    ops.device_status()
+    want = x.double() @ w.double().t() + bias.double()
+    scale = want.abs().max().item()
+    assert (got.double() - want).abs().max().item() <= 1e-5 * scale
+    if M * N <= 100 * 132:   # serial chain on the host: fmaf over k in ascending order, then + bias
+        acc = np.zeros((M, N), dtype=np.float32)
+        xn, wn = x.numpy(), w.numpy()
+        for k in range(K):
+            acc = np.asarray(np.float64(xn[:, k:k + 1]) * np.float64(wn[None, :, k]) + np.float64(acc), dtype=np.float32)
+        ref = acc + bias.numpy()[None, :]
+        assert np.array_equal(got.numpy(), ref), "not the serial fmaf chain"

@@ -65,3 +65,23 @@ def test_sdpa_matches_emitted_kernel(ops):
     ref = k.output.cpu()
     got = ops.sdpa_causal_gqa(q.cuda(), kk.cuda(), v.cuda()).cpu()
     metrics.assert_bf16_tensor_path(got, ref, what="sdpa vs emitted kernel")
+
+
+def test_fp32_matmul_matches_emitted_kernel(ops):
+    """The fp32 tier: the q_proj shape of the reference's perf suite (512 x 1024 x 2048, B row-major [K, N])."""
+    if "matmul_f32" not in __import__("json").loads((ref_kernels.REF_DIR / "manifest.json").read_text()):
+        pytest.skip("oracle/_ref was built without the fp32 matmul configuration")
+    g = torch.Generator().manual_seed(0)
+    a = torch.randn(512, 1024, generator=g)
+    b = torch.randn(1024, 2048, generator=g)
+    k = ref_kernels.RefKernel("matmul_f32")
+    k.bind(a=a, b=b)
+    k.launch()
+    ref = k.output.cpu()
+    got = ops.linear_f32(a.cuda(), b.cuda(), None, True).cpu()
+    want = torch.matmul(a.double(), b.double())
+    scale = want.abs().max().item()
+    # both sum 1024 fp32 products per output, in different orders: a few 1e-6 of the output scale apart
+    assert (got.double() - want).abs().max().item() <= 2e-5 * scale
+    assert (ref.double() - want).abs().max().item() <= 2e-5 * scale
+    assert (got - ref).abs().max().item() <= 4e-5 * scale
