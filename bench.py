@@ -410,7 +410,9 @@ def kernel_cases() -> dict:
             a = torch.randn(M, K, device=dev, generator=g)
             b = torch.randn(K, N, device=dev, generator=g)
             flops = 2 * M * K * N
-            note = "fp32 CUDA-core FMAs (72 TFLOP/s nominal at 148 SMs x 128 lanes x 1.9 GHz), not a tensor-core rate"
+            note = ("fp32 in / fp32 out; 256 rows and up run on the tensor cores over exactly split bf16 operands "
+                    "(6x the flops at bf16 rate), fewer rows on CUDA cores; the fraction is of the nominal fp32 "
+                    "CUDA-core rate (72 TFLOP/s = 148 SMs x 128 lanes x 2 x 1.9 GHz), which the split route can exceed")
             if extra == "add":
                 r = torch.randn(M, N, device=dev, generator=g)
                 fn = lambda: ops.elementwise("add", ops.linear_f32(a, b, None, True), r)  # noqa: E731

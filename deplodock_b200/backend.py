@@ -252,7 +252,15 @@ def lower(graph: Graph) -> CompiledPlan:
                 N = w_shape[1] if kn else w_shape[0]
                 entry = "emk_linear_bf16" if (K % 8 == 0 and N % 8 == 0) else "emk_linear_bf16_simt"
             elif dt == "f32":
-                entry = "emk_linear_f32_simt"
+                # fp32 graphs: tensor cores on exactly split bf16 operands from 256 rows on, the register-tiled
+                # CUDA-core kernel below that (and for K or N not a multiple of 8)
+                from deplodock_b200.ops import F32_TC_MIN_ROWS
+
+                K = w_shape[0] if kn else w_shape[1]
+                N = w_shape[1] if kn else w_shape[0]
+                rows = int(np.prod(node.output.shape[:-1])) if len(node.output.shape) > 1 else 1
+                entry = "emk_linear_f32_tc" if (K % 8 == 0 and N % 8 == 0 and rows >= F32_TC_MIN_ROWS) \
+                    else "emk_linear_f32_simt"
             else:
                 raise LoweringError(f"{node.id}: {op} in {dt} has no kernel")
             steps.append(PlanStep(_name("linear", node), entry, node.id, ins[: 3 if has_bias else 2],
@@ -519,8 +527,9 @@ class B200Backend(Backend):
                            w_is_kn=s.attrs["kn"])
                 else:
                     y = fn(a[0], a[1], bias=a[2].reshape(-1) if s.attrs["has_bias"] else None, w_is_kn=s.attrs["kn"])
-            elif s.entry == "emk_linear_f32_simt":
-                y = ops.linear_f32(a[0], a[1], a[2].reshape(-1) if s.attrs["has_bias"] else None, s.attrs["kn"])
+            elif s.entry in ("emk_linear_f32_simt", "emk_linear_f32_tc"):
+                y = ops.linear_f32(a[0], a[1], a[2].reshape(-1) if s.attrs["has_bias"] else None, s.attrs["kn"],
+                                   route="tc" if s.entry == "emk_linear_f32_tc" else "simt")
             elif s.entry == "emk_loop_linear_f32":
                 at = s.attrs
                 extra = a[2] if len(a) > 2 else None

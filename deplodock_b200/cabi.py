@@ -71,6 +71,9 @@ _SIGNATURES: dict[str, list] = {
                              c_int, c_void_p],
     "emk_linear_f32_simt": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int,
                             c_void_p],
+    "emk_linear_f32_tc_workspace_bytes": [c_int64, c_int64, c_int64],
+    "emk_linear_f32_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p,
+                          c_int64, c_void_p],
     "emk_linear_bf16_qknorm_rope": [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p,
                                     c_void_p, c_void_p, c_int64, c_int64, c_int64, c_float, c_void_p],
     "emk_gemm_bf16_fused": [c_void_p, c_void_p, c_void_p],
@@ -104,7 +107,8 @@ _SIGNATURES: dict[str, list] = {
     "emk_selftest_wait_expiry": [c_void_p, c_int, c_void_p],
 }
 _RESTYPES = {"emk_status_string": c_char_p, "emk_last_error": c_char_p,
-             "emk_linear_bf16_w8_workspace_bytes": c_int64, "emk_sdpa_varlen_workspace_bytes": c_int64}
+             "emk_linear_bf16_w8_workspace_bytes": c_int64, "emk_sdpa_varlen_workspace_bytes": c_int64,
+             "emk_linear_f32_tc_workspace_bytes": c_int64}
 
 #: every symbol ``include/emk.h`` declares; ``tests/test_cabi_symbols.py`` checks the header against this list
 EXPORTED_SYMBOLS = tuple(_SIGNATURES)

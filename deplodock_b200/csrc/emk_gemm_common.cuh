@@ -27,6 +27,7 @@ struct GemmArgs {
   int qk_S, qk_Hq, qk_Hkv;
   float qk_eps;
   const int* qk_pos;             // rotary position of every row (packed sequences); null: position = row % qk_S
+  const float* f32_bias;         // epi == EMK_EPI_F32_INTERNAL: optional fp32 bias [N]; y is then fp32 [M,N]
   // RMSNorm folded around the GEMM (the norm weight is folded into W by the caller):
   //   ss_in   partial sums of squares [M][ss_in_segs] of the un-normalised input rows (one slot per 128 columns):
   //           accumulator rows are scaled by rsqrt(sum_s ss_in[s][row] * ss_inv_dim + ss_eps) before the epilogue
@@ -42,6 +43,7 @@ struct GemmArgs {
 };
 
 constexpr int EMK_EPI_QKNORM_ROPE_INTERNAL = 100;
+constexpr int EMK_EPI_F32_INTERNAL = 101;  // store the fp32 accumulator (+ fp32 bias) unrounded: y is float [M,N]
 
 // Tile order of the persistent kernels: tiles are walked in groups of GROUP_M row-tiles by all column-tiles, rows
 // fastest inside a group, so the CTAs running at one time share a few A row-blocks and a few W column-blocks and
@@ -85,6 +87,22 @@ __device__ __forceinline__ float epilogue_store32(const GemmArgs& g, const uint3
     } else {
       if (col0 < g.N) *reinterpret_cast<uint4*>(out) = make_uint4(o[0], o[1], o[2], o[3]);
       if (col0 + 16 < g.N) *reinterpret_cast<uint4*>(out + 8) = make_uint4(o[4], o[5], o[6], o[7]);
+    }
+    return 0.f;
+  }
+  if (g.epi == EMK_EPI_F32_INTERNAL) {
+    float* out = reinterpret_cast<float*>(g.y) + (int64_t)row * g.ldy + col0;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      if (col0 + q * 4 < g.N) {   // N is a multiple of 8: a quad is inside or outside as a whole
+        float4 v4 = make_float4(__uint_as_float(r[q * 4]), __uint_as_float(r[q * 4 + 1]), __uint_as_float(r[q * 4 + 2]),
+                                __uint_as_float(r[q * 4 + 3]));
+        if (g.f32_bias != nullptr) {
+          const float4 b4 = __ldg(reinterpret_cast<const float4*>(g.f32_bias + col0 + q * 4));
+          v4.x += b4.x; v4.y += b4.y; v4.z += b4.z; v4.w += b4.w;
+        }
+        *reinterpret_cast<float4*>(out + q * 4) = v4;
+      }
     }
     return 0.f;
   }

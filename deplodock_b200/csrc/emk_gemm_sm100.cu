@@ -211,7 +211,8 @@ struct RowStatArgs {
 
 int gemm_dispatch(emk_handle_t h, const void* x, const void* w, const void* residual, const float* scale, void* y,
                   int64_t M, int64_t N, int64_t K, int wlayout, int epilogue, cudaStream_t s,
-                  const QkRopeArgs* qk = nullptr, const RowStatArgs* rsx = nullptr) {
+                  const QkRopeArgs* qk = nullptr, const RowStatArgs* rsx = nullptr, bool f32_out = false,
+                  const float* f32_bias = nullptr) {
   if (!h || !x || !w || !y) return EMK_ERR_ARG;
   if (M <= 0 || N <= 0 || K <= 0 || M > 0x7fffffff || N > 0x7fffffff || K > 0x7fffffff) return EMK_ERR_SHAPE;
   if (wlayout != EMK_W_NK && wlayout != EMK_W_KN) return EMK_ERR_ARG;
@@ -226,7 +227,10 @@ int gemm_dispatch(emk_handle_t h, const void* x, const void* w, const void* resi
     EMK_SET_ERR(h, "emk_linear_bf16: operands must be 16-byte aligned");
     return EMK_ERR_ALIGN;
   }
-  const int BN = (N > 128) ? 256 : 128;
+  // Few output tiles (the fp32-output route runs a 6x longer K loop over small M x N): 128-wide single-CTA tiles
+  // put more SMs to work than 256-wide ones.
+  const bool narrow = f32_out && ((M + BM - 1) / BM) * ((N + 255) / 256) < h->sm_count / 2;
+  const int BN = (N > 128 && !narrow) ? 256 : 128;
   GemmArgs g = {};
   g.y = (__nv_bfloat16*)y;
   g.residual = (const __nv_bfloat16*)residual;
@@ -252,6 +256,12 @@ int gemm_dispatch(emk_handle_t h, const void* x, const void* w, const void* resi
   }
   g.qk_qw = g.qk_kw = g.qk_rope = nullptr;
   g.qk_pos = nullptr;
+  g.f32_bias = nullptr;
+  if (f32_out) {
+    if ((((uintptr_t)y | (uintptr_t)f32_bias) & 15u) != 0) return EMK_ERR_ALIGN;
+    g.epi = EMK_EPI_F32_INTERNAL;
+    g.f32_bias = f32_bias;
+  }
   g.qk_S = g.qk_Hq = g.qk_Hkv = 0;
   g.qk_eps = 0.f;
   if (qk) {  // fused q/k-norm + RoPE epilogue: 256-column CTA-pair tiles only (two whole heads per tile)
@@ -267,7 +277,7 @@ int gemm_dispatch(emk_handle_t h, const void* x, const void* w, const void* resi
     return emk_gemm2_launch(h, x, w, g, wlayout, s);
   }
   // CTA-pair tiles (256x256) when the problem has at least one full pair tile; single-CTA tiles otherwise.
-  const bool pair_ok = M > BM && N > 128;
+  const bool pair_ok = M > BM && N > 128 && !narrow;
   // The pair kernel's 128-wide tiles give each epilogue thread 64 columns, half of a row_sumsq_out slot: two threads
   // would write one slot. Such outputs (N <= 128) always take the single-CTA kernel, whose threads own whole slots.
   const bool pair_forced = h->gemm_impl == 2 && !(g.ss_out != nullptr && N <= 128);
@@ -297,6 +307,13 @@ int emk_gemm_bf16_colscale_launch(emk_handle_t h, const void* x, const void* w, 
   return gemm_dispatch(h, x, w, nullptr, scale, y, M, N, K, EMK_W_NK, EMK_EPI_NONE, s);
 }
 
+
+// y (fp32 [M,N]) = x·W (+ bias) with bf16 operands and the unrounded fp32 accumulator stored: the multiply step of
+// the split-operand fp32 linear (emk_gemm_f32_split.cu).
+int emk_gemm_bf16_f32out_launch(emk_handle_t h, const void* x, const void* w, const float* bias, float* y, int64_t M,
+                                int64_t N, int64_t K, int wlayout, cudaStream_t s) {
+  return gemm_dispatch(h, x, w, nullptr, nullptr, y, M, N, K, wlayout, EMK_EPI_NONE, s, nullptr, nullptr, true, bias);
+}
 
 extern "C" int emk_linear_bf16(emk_handle_t h, const void* x, const void* w, const void* residual, void* y, int64_t M,
                                int64_t N, int64_t K, int wlayout, int epilogue, emk_stream_t stream) {

@@ -154,7 +154,8 @@ __global__ void __launch_bounds__(256) gemm_f32_tiled_kernel(const float* __rest
                                                              const float* __restrict__ residual,
                                                              const float* __restrict__ gate, float* __restrict__ y,
                                                              int M, int N, int K, int64_t x_inner,
-                                                             int64_t x_stride_outer, int64_t x_stride_m) {
+                                                             int64_t x_stride_outer, int64_t x_stride_m,
+                                                             int k_per_split) {
   __shared__ __align__(16) float As[2][FT_K][FT_LD];
   __shared__ __align__(16) float Bs[2][FT_K][FT_LD];
   const int tid = threadIdx.x;
@@ -164,21 +165,25 @@ __global__ void __launch_bounds__(256) gemm_f32_tiled_kernel(const float* __rest
   const int lrow = tid >> 2, lkq = (tid & 3) * 4;
   const int bk = tid >> 4, bnq = (tid & 15) * 4;
   const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  // split-K (gridDim.z > 1, few output tiles): this CTA sums k in [k_begin, k_lim) and adds its partial result to y,
+  // which the host zeroed; with one split the result is stored and every output is one fmaf chain over all of k
+  const int k_begin = (int)blockIdx.z * k_per_split;
+  const int k_lim = min(K, k_begin + k_per_split);
 
   auto load_a = [&](int k0) -> float4 {
     const int m = m0 + lrow, k = k0 + lkq;
-    if (m >= M || k >= K) return zero4;
+    if (m >= M || k >= k_lim) return zero4;
     const int64_t off = (int64_t)(k / x_inner) * x_stride_outer + (int64_t)m * x_stride_m + (k % x_inner);
     return __ldg(reinterpret_cast<const float4*>(x + off));
   };
   auto load_b = [&](int k0) -> float4 {
     if (WL == 0) {
       const int n = n0 + lrow, k = k0 + lkq;
-      if (n >= N || k >= K) return zero4;
+      if (n >= N || k >= k_lim) return zero4;
       return __ldg(reinterpret_cast<const float4*>(w + (int64_t)n * K + k));
     }
     const int k = k0 + bk, n = n0 + bnq;
-    if (k >= K || n >= N) return zero4;
+    if (k >= k_lim || n >= N) return zero4;
     return __ldg(reinterpret_cast<const float4*>(w + (int64_t)k * N + n));
   };
   auto store_tiles = [&](int buf, const float4& a, const float4& b) {
@@ -196,15 +201,16 @@ __global__ void __launch_bounds__(256) gemm_f32_tiled_kernel(const float* __rest
 #pragma unroll
     for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
 
-  const int nk = (K + FT_K - 1) / FT_K;
-  float4 ra = load_a(0), rb = load_b(0);
+  const int nk = (k_lim - k_begin + FT_K - 1) / FT_K;
+  if (nk <= 0) return;
+  float4 ra = load_a(k_begin), rb = load_b(k_begin);
   store_tiles(0, ra, rb);
   __syncthreads();
   for (int kt = 0; kt < nk; ++kt) {
     const int buf = kt & 1;
     if (kt + 1 < nk) {
-      ra = load_a((kt + 1) * FT_K);
-      rb = load_b((kt + 1) * FT_K);
+      ra = load_a(k_begin + (kt + 1) * FT_K);
+      rb = load_b(k_begin + (kt + 1) * FT_K);
     }
 #pragma unroll
     for (int k = 0; k < FT_K; ++k) {
@@ -231,6 +237,11 @@ __global__ void __launch_bounds__(256) gemm_f32_tiled_kernel(const float* __rest
       if (n >= N) continue;
       const int64_t idx = (int64_t)m * N + n;
       float v = acc[i][j];
+      if (gridDim.z > 1) {   // partial sum of one K range (no residual / gate epilogue on this path)
+        if (blockIdx.z == 0 && bias != nullptr) v = v + bias[n];
+        atomicAdd(y + idx, v);
+        continue;
+      }
       if (bias != nullptr) v = v + bias[n];
       if (residual != nullptr) v = residual[idx] + v;
       if (gate != nullptr) {
@@ -251,13 +262,29 @@ inline bool f32_tiled_ok(const float* x, const float* w, int64_t N, int64_t K, i
   return true;
 }
 
+// `sm_count` > 0 allows split-K when the output has too few tiles to fill the GPU (the K loop of a lone CTA is bound
+// by the latency of its loads): y is zeroed and the splits add their partial sums with atomics, so the result is
+// then no longer the serial chain, only equal to it within fp32 rounding. The record contractions pass 0.
 template <int WL>
-inline void launch_f32_tiled(const float* x, const float* w, const float* bias, const float* residual,
-                             const float* gate, float* y, int64_t M, int64_t N, int64_t K, int64_t x_inner,
-                             int64_t x_stride_outer, int64_t x_stride_m, cudaStream_t s) {
-  dim3 grid((unsigned)((N + FT_N - 1) / FT_N), (unsigned)((M + FT_M - 1) / FT_M));
+inline cudaError_t launch_f32_tiled(const float* x, const float* w, const float* bias, const float* residual,
+                                    const float* gate, float* y, int64_t M, int64_t N, int64_t K, int64_t x_inner,
+                                    int64_t x_stride_outer, int64_t x_stride_m, cudaStream_t s, int sm_count = 0) {
+  dim3 grid((unsigned)((N + FT_N - 1) / FT_N), (unsigned)((M + FT_M - 1) / FT_M), 1);
+  int64_t k_per_split = K;
+  const int64_t tiles = (int64_t)grid.x * grid.y;
+  if (sm_count > 0 && residual == nullptr && gate == nullptr && tiles < sm_count && K >= 8 * FT_K) {
+    int64_t splits = (2 * (int64_t)sm_count + tiles - 1) / tiles;
+    if (splits > 16) splits = 16;
+    k_per_split = ((K + splits - 1) / splits + FT_K - 1) / FT_K * FT_K;
+    grid.z = (unsigned)((K + k_per_split - 1) / k_per_split);
+    if (grid.z > 1) {
+      cudaError_t e = cudaMemsetAsync(y, 0, (size_t)(M * N) * sizeof(float), s);
+      if (e != cudaSuccess) return e;
+    }
+  }
   gemm_f32_tiled_kernel<WL><<<grid, 256, 0, s>>>(x, w, bias, residual, gate, y, (int)M, (int)N, (int)K, x_inner,
-                                                 x_stride_outer, x_stride_m);
+                                                 x_stride_outer, x_stride_m, (int)k_per_split);
+  return cudaSuccess;
 }
 
 // fp32 contraction of the Loop-IR kernel records (one LoopOp of the reference = one launch here):
@@ -414,8 +441,8 @@ extern "C" int emk_loop_linear_f32(emk_handle_t h, const float* x, const float* 
   if (residual != nullptr && gate != nullptr) return EMK_ERR_ARG;
   if (M <= 0x7fffffffLL && N <= 0x7fffffffLL && K <= 0x7fffffffLL && (M + FT_M - 1) / FT_M <= 65535 &&
       f32_tiled_ok(x, w, N, K, EMK_W_NK, x_inner, x_stride_outer, x_stride_m)) {
-    launch_f32_tiled<0>(x, w, nullptr, residual, gate, y, M, N, K, x_inner, x_stride_outer, x_stride_m,
-                        (cudaStream_t)stream);
+    EMK_CUDA_TRY(h, launch_f32_tiled<0>(x, w, nullptr, residual, gate, y, M, N, K, x_inner, x_stride_outer,
+                                        x_stride_m, (cudaStream_t)stream));
     EMK_LAUNCH_CHECK(h);
     return EMK_OK;
   }
@@ -475,9 +502,11 @@ extern "C" int emk_linear_f32_simt(emk_handle_t h, const float* x, const float* 
   if (M <= 0x7fffffffLL && N <= 0x7fffffffLL && K <= 0x7fffffffLL && (M + FT_M - 1) / FT_M <= 65535 &&
       f32_tiled_ok(x, w, N, K, wlayout, K, 0, K)) {
     if (wlayout == EMK_W_NK)
-      launch_f32_tiled<0>(x, w, bias, nullptr, nullptr, y, M, N, K, K, 0, K, (cudaStream_t)stream);
+      EMK_CUDA_TRY(h, launch_f32_tiled<0>(x, w, bias, nullptr, nullptr, y, M, N, K, K, 0, K, (cudaStream_t)stream,
+                                          h->sm_count));
     else
-      launch_f32_tiled<1>(x, w, bias, nullptr, nullptr, y, M, N, K, K, 0, K, (cudaStream_t)stream);
+      EMK_CUDA_TRY(h, launch_f32_tiled<1>(x, w, bias, nullptr, nullptr, y, M, N, K, K, 0, K, (cudaStream_t)stream,
+                                          h->sm_count));
     EMK_LAUNCH_CHECK(h);
     return EMK_OK;
   }

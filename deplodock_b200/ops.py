@@ -251,20 +251,53 @@ def linear_residual_rmsnorm_noalloc(x, w, residual, norm_weight, eps: float = 1e
     return hid, nrm
 
 
-def linear_f32(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, w_is_kn: bool = False) -> torch.Tensor:
-    """fp32 LinearOp / MatmulOp on CUDA cores (fp32 graphs have no tensor-core path)."""
-    _check_cuda_contig(x, w, bias)
-    if x.dtype != torch.float32 or w.dtype != torch.float32:
+#: fp32 problems with at least this many rows go to the tensor cores (split operands); below it the split of the
+#: weight costs more than the CUDA-core kernel's whole product
+F32_TC_MIN_ROWS = 256
+_F32_SCRATCH: dict[int, torch.Tensor] = {}
+
+
+def _f32_scratch(device: torch.device, nbytes: int) -> torch.Tensor:
+    """One grow-only scratch buffer per device for the split operands of :func:`linear_f32`; it holds nothing between
+    calls (calls on different streams must not overlap)."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    buf = _F32_SCRATCH.get(idx)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _F32_SCRATCH[idx] = buf
+    return buf
+
+
+def linear_f32(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, w_is_kn: bool = False,
+               route: str = "auto", out: torch.Tensor | None = None) -> torch.Tensor:
+    """fp32 LinearOp / MatmulOp. ``route``: ``"tc"`` — tensor cores on exactly split bf16 operands
+    (``emk_linear_f32_tc``; K and N multiples of 8), ``"simt"`` — the register-tiled CUDA-core kernel, ``"auto"`` —
+    tensor cores from ``F32_TC_MIN_ROWS`` rows on when the shape allows."""
+    _check_cuda_contig(x, w, bias, out)
+    if x.dtype != torch.float32 or w.dtype != torch.float32 or (bias is not None and bias.dtype != torch.float32):
         raise TypeError("linear_f32 expects float32 operands")
     K = x.shape[-1]
     M = x.numel() // K
     N = w.shape[1] if w_is_kn else w.shape[0]
     if (w.shape[0] if w_is_kn else w.shape[1]) != K:
         raise ValueError("weight does not match x")
-    y = torch.empty(*x.shape[:-1], N, dtype=torch.float32, device=x.device)
+    if route not in ("auto", "tc", "simt"):
+        raise ValueError("route must be 'auto', 'tc' or 'simt'")
+    _check_buffer("out", out, M * N, torch.float32)
+    _check_buffer("bias", bias, N, torch.float32)
+    y = torch.empty(*x.shape[:-1], N, dtype=torch.float32, device=x.device) if out is None else out
     h = handle()
-    h.check(h.lib.emk_linear_f32_simt(h.ptr, _ptr(x), _ptr(w), _ptr(bias), _ptr(y), M, N, K,
-                                      cabi.EMK_W_KN if w_is_kn else cabi.EMK_W_NK, _stream()), "emk_linear_f32_simt")
+    wl = cabi.EMK_W_KN if w_is_kn else cabi.EMK_W_NK
+    tc_ok = K % 8 == 0 and N % 8 == 0
+    if route == "tc" and not tc_ok:
+        raise ValueError("the tensor-core route needs K and N to be multiples of 8")
+    if route == "tc" or (route == "auto" and tc_ok and M >= F32_TC_MIN_ROWS):
+        ws = _f32_scratch(x.device, int(h.lib.emk_linear_f32_tc_workspace_bytes(M, N, K)))
+        h.check(h.lib.emk_linear_f32_tc(h.ptr, _ptr(x), _ptr(w), _ptr(bias), _ptr(y), M, N, K, wl, _ptr(ws),
+                                        ws.numel(), _stream()), "emk_linear_f32_tc")
+        return y
+    h.check(h.lib.emk_linear_f32_simt(h.ptr, _ptr(x), _ptr(w), _ptr(bias), _ptr(y), M, N, K, wl, _stream()),
+            "emk_linear_f32_simt")
     return y
 
 

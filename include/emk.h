@@ -181,6 +181,19 @@ int emk_linear_residual_rmsnorm_bf16_noalloc(emk_handle_t h, const void* x, cons
                                              const void* norm_weight, void* y_hidden, void* y_norm, int64_t M,
                                              int64_t N, int64_t K, float eps, emk_stream_t stream);
 
+/* fp32 LinearOp / MatmulOp on the tensor cores: y[M,N] (fp32) = x[M,K] · W (+ bias[N]), all fp32 in memory. Each
+ * operand is split exactly into three bf16 terms, the six partial products that matter are summed by ONE bf16 tcgen05
+ * GEMM with a 6K-long reduction axis and fp32 accumulation, and the accumulator is stored unrounded. The tensor core
+ * accumulates with truncation, so the result sits about 1e-6 (K = 1024) to 3e-6 (K = 3072) of the output scale
+ * below a correctly rounded sum — inside the 5e-5 the reference's tests allow for fp32 matmul. Replaces the reference's scalar-tier k_matmul_* / k_linear_*
+ * kernels for fp32 graphs (the shapes its perf suite drives, tests/perf/cases.py:60-74). K and N multiples of 8.
+ * `workspace` (device, 16-byte aligned, emk_linear_f32_tc_workspace_bytes(M, N, K) bytes = 12 (M + N) K) receives
+ * the split operands and holds nothing between calls. */
+int64_t emk_linear_f32_tc_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int emk_linear_f32_tc(emk_handle_t h, const float* x, const float* w, const float* bias, float* y, int64_t M,
+                      int64_t N, int64_t K, int wlayout, void* workspace, int64_t workspace_bytes,
+                      emk_stream_t stream);
+
 /* Embedding row gather: out[t,:] = table[ids[t],:] (bf16 rows of `hidden` elements, hidden*2 a multiple of 16).
  * Replaces the GatherOp kernel of the traced trunk (emmy/compiler/trace/huggingface.py:17-186). ids are int64. */
 int emk_embed_gather(emk_handle_t h, const void* table, const int64_t* ids, void* out, int64_t tokens,

@@ -611,7 +611,7 @@ def test_linear_f32_tiled_and_fallback(ops, M, K, N, kn):
     w = torch.randn(N, K, generator=g)
     bias = torch.randn(N, generator=g)
     wd = _dev(w.t().contiguous() if kn else w)
-    got = ops.linear_f32(_dev(x), wd, _dev(bias), kn).cpu()
+    got = ops.linear_f32(_dev(x), wd, _dev(bias), kn, route="simt").cpu()
     ops.device_status()
     want = x.double() @ w.double().t() + bias.double()
     scale = want.abs().max().item()
@@ -623,3 +623,31 @@ def test_linear_f32_tiled_and_fallback(ops, M, K, N, kn):
             acc = np.asarray(np.float64(xn[:, k:k + 1]) * np.float64(wn[None, :, k]) + np.float64(acc), dtype=np.float32)
         ref = acc + bias.numpy()[None, :]
         assert np.array_equal(got.numpy(), ref), "not the serial fmaf chain"
+
+
+@pytest.mark.parametrize("M,K,N", [(512, 1024, 2048), (256, 64, 8), (300, 136, 264), (1000, 3072, 1024), (40, 64, 96)])
+@pytest.mark.parametrize("kn", [False, True])
+def test_linear_f32_on_tensor_cores(ops, M, K, N, kn):
+    """fp32 in, fp32 out, through one bf16 tcgen05 GEMM over exactly split operands: against a float64 product at the
+    tolerance of an fp32 reduction, and against the CUDA-core kernel."""
+    g = torch.Generator().manual_seed(M + 7 * K + N)
+    x = torch.randn(M, K, generator=g) * torch.rand(M, 1, generator=g) * 4   # rows of different magnitude
+    w = torch.randn(N, K, generator=g)
+    w[::7] *= 1e-3
+    bias = torch.randn(N, generator=g)
+    wd = _dev(w.t().contiguous() if kn else w)
+    got = ops.linear_f32(_dev(x), wd, _dev(bias), kn, route="tc").cpu()
+    alt = ops.linear_f32(_dev(x), wd, _dev(bias), kn, route="simt").cpu()
+    ops.device_status()
+    want = x.double() @ w.double().t() + bias.double()
+    # per output against the sum of |products| (what any fp32 accumulation order is held to): the CUDA-core kernel
+    # rounds every step, the tensor core truncates its accumulator (see emk_linear_f32_tc) and lands within 2e-5;
+    # element-wise the reference's own bound for fp32 matmul (rtol 5e-5, atol 2e-6 of the scale) holds with room
+    mag = (x.double().abs() @ w.double().abs().t() + bias.double().abs())
+    scale = want.abs().max().item()
+    assert ((alt.double() - want).abs() <= 1e-5 * mag.clamp_min(1e-30)).all()
+    assert ((got.double() - want).abs() <= 2e-5 * mag.clamp_min(1e-30)).all()
+    assert ((got.double() - want).abs() <= 5e-5 * want.abs() + 2e-6 * scale).all()
+    print(f"fp32 tc M{M} K{K} N{N}: max err / scale = {(got.double() - want).abs().max().item() / scale:.2e}")
+    with pytest.raises(ValueError):
+        ops.linear_f32(_dev(x[:, :4].contiguous()), _dev(w[:, :4].contiguous()), None, False, route="tc")
