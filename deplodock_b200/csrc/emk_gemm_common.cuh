@@ -208,13 +208,40 @@ __device__ __forceinline__ void epilogue_prefetch(const GemmArgs& g, int row, in
 // One head (128 accumulator columns of this thread's row) of the fused QKV projection: round to bf16 as the GEMM
 // output would be, then for query/key heads the per-head RMSNorm and the rotate-half RoPE on packed bf16 pairs with
 // the rounding steps of the eager bf16 module (normalised -> bf16, * weight -> bf16, each RoPE product -> bf16,
-// sum -> bf16); value heads are stored as they are. Thread-local: the row's 128 columns live in this thread.
+// sum -> bf16); value heads are stored as they are. Thread-local: the row's 128 columns live in this thread's TMEM lane.
+//
+// The accumulator is read TWICE: a first sweep forms the row's sum of squares (four independent partial sums) and
+// keeps nothing; a second sweep takes 16 columns and their rotate-half partners (+64) at a time, normalises, rotates
+// and stores them. Holding all 64 packed pairs in registers instead (one sweep) left no room to issue the rotary-table
+// loads ahead of their use within the kernel's 168 registers, and the epilogue of a K = 1024 tile — about 10 000
+// cycles for one head per warp, against 8 192 of tensor-core work — set the pace of the whole projection.
 __device__ __forceinline__ void epilogue_head_qknorm_rope(const GemmArgs& g, uint32_t taddr, int row, int col0,
                                                           float rs) {
-  // 32 columns at a time are packed to bf16 pairs as they arrive (the next load is in flight meanwhile), so the live
-  // state is the 64 packed pairs plus two 32-register load buffers.
-  uint32_t n[64];
-  float ss = 0.f;
+  const int head = col0 >> 7;
+  const bool rotate = head < g.qk_Hq + g.qk_Hkv;   // uniform over the warp (all lanes share the column range)
+  const bool valid = row < g.M && col0 < g.N;
+  __nv_bfloat16* out = g.y + (int64_t)row * g.ldy + col0;
+  if (!rotate) {
+    // value head: bf16 of the (row-scaled) accumulator, 32 columns at a time
+    uint32_t v[2][32];
+    tmem_ld_x32(taddr, v[0]);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      tmem_ld_wait_regs(v[c & 1]);
+      if (c + 1 < 4) tmem_ld_x32(taddr + (uint32_t)((c + 1) * 32), v[(c + 1) & 1]);
+      uint32_t o[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i)
+        o[i] = pack_bf16x2(__uint_as_float(v[c & 1][2 * i]) * rs, __uint_as_float(v[c & 1][2 * i + 1]) * rs);
+      if (valid) {
+        st_global_v8(out + c * 32, o);
+        st_global_v8(out + c * 32 + 16, o + 8);
+      }
+    }
+    return;
+  }
+  // ---- sweep 1: sum of squares of the bf16-rounded row ----
+  float ss0 = 0.f, ss1 = 0.f, ss2 = 0.f, ss3 = 0.f;
   {
     uint32_t v[2][32];
     tmem_ld_x32(taddr, v[0]);
@@ -223,62 +250,67 @@ __device__ __forceinline__ void epilogue_head_qknorm_rope(const GemmArgs& g, uin
       tmem_ld_wait_regs(v[c & 1]);
       if (c + 1 < 4) tmem_ld_x32(taddr + (uint32_t)((c + 1) * 32), v[(c + 1) & 1]);
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const uint32_t pk = pack_bf16x2(__uint_as_float(v[c & 1][2 * i]) * rs, __uint_as_float(v[c & 1][2 * i + 1]) * rs);
-        const float f0 = bf16_lo(pk), f1 = bf16_hi(pk);
-        ss = fmaf(f0, f0, ss);
-        ss = fmaf(f1, f1, ss);
-        n[c * 16 + i] = pk;
+      for (int i = 0; i < 16; i += 2) {
+        const uint32_t pa = pack_bf16x2(__uint_as_float(v[c & 1][2 * i]) * rs, __uint_as_float(v[c & 1][2 * i + 1]) * rs);
+        const uint32_t pb = pack_bf16x2(__uint_as_float(v[c & 1][2 * i + 2]) * rs, __uint_as_float(v[c & 1][2 * i + 3]) * rs);
+        const float a0 = bf16_lo(pa), a1 = bf16_hi(pa), b0 = bf16_lo(pb), b1 = bf16_hi(pb);
+        ss0 = fmaf(a0, a0, ss0);
+        ss1 = fmaf(a1, a1, ss1);
+        ss2 = fmaf(b0, b0, ss2);
+        ss3 = fmaf(b1, b1, ss3);
       }
     }
   }
-  if (row >= g.M || col0 >= g.N) return;
-  const int head = col0 >> 7;
-  __nv_bfloat16* out = g.y + (int64_t)row * g.ldy + col0;
-  if (head < g.qk_Hq + g.qk_Hkv) {
-    const float r = 1.0f / sqrtf(ss * (1.0f / 128.0f) + g.qk_eps);
-    const __nv_bfloat16* wp = head < g.qk_Hq ? g.qk_qw : g.qk_kw;
+  const float r = 1.0f / sqrtf(((ss0 + ss1) + (ss2 + ss3)) * (1.0f / 128.0f) + g.qk_eps);
+  const __nv_bfloat16* wp = head < g.qk_Hq ? g.qk_qw : g.qk_kw;
+  // The table is chunk-major: chunk q of position s is 32 bytes (8 cos then 8 sin values of elements 8q..8q+7;
+  // cos[i] == cos[i + 64] so the first 64 elements suffice). The lanes of a warp are consecutive rows, hence
+  // consecutive positions, so each of these loads is one contiguous kilobyte per warp.
+  const __nv_bfloat16* tp = g.qk_rope + (int64_t)(valid ? rope_position(g, row) : 0) * 16;
+  // ---- sweep 2: 16 columns [16t, 16t+16) and their partners [64+16t, 64+16t+16) per step ----
+  uint32_t lo[2][16], hi[2][16];
+  tmem_ld_x16(taddr, lo[0]);
+  tmem_ld_x16(taddr + 64u, hi[0]);
 #pragma unroll
-    for (int q = 0; q < 16; ++q) {
-      const uint4 wv = __ldg(reinterpret_cast<const uint4*>(wp + q * 8));
-      const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int e = q * 4 + j;
-        const __nv_bfloat162 xn = __floats2bfloat162_rn(bf16_lo(n[e]) * r, bf16_hi(n[e]) * r);
-        const __nv_bfloat162 res = __hmul2_rn(*reinterpret_cast<const __nv_bfloat162*>(&ww[j]), xn);
-        n[e] = *reinterpret_cast<const uint32_t*>(&res);
-      }
+  for (int t = 0; t < 4; ++t) {
+    uint32_t cs[2][8];
+    ld_global_nc_v8(tp + (int64_t)(2 * t) * g.qk_S * 16, cs[0]);
+    ld_global_nc_v8(tp + (int64_t)(2 * t + 1) * g.qk_S * 16, cs[1]);
+    const uint4 wl0 = __ldg(reinterpret_cast<const uint4*>(wp + 16 * t));
+    const uint4 wl1 = __ldg(reinterpret_cast<const uint4*>(wp + 16 * t + 8));
+    const uint4 wh0 = __ldg(reinterpret_cast<const uint4*>(wp + 64 + 16 * t));
+    const uint4 wh1 = __ldg(reinterpret_cast<const uint4*>(wp + 64 + 16 * t + 8));
+    const uint32_t wlo[8] = {wl0.x, wl0.y, wl0.z, wl0.w, wl1.x, wl1.y, wl1.z, wl1.w};
+    const uint32_t whi[8] = {wh0.x, wh0.y, wh0.z, wh0.w, wh1.x, wh1.y, wh1.z, wh1.w};
+    tmem_ld_wait_regs16x2(lo[t & 1], hi[t & 1]);
+    if (t + 1 < 4) {
+      tmem_ld_x16(taddr + (uint32_t)((t + 1) * 16), lo[(t + 1) & 1]);
+      tmem_ld_x16(taddr + 64u + (uint32_t)((t + 1) * 16), hi[(t + 1) & 1]);
     }
-    // The table is chunk-major: chunk q of position s is 32 bytes (8 cos then 8 sin values of elements 8q..8q+7;
-    // cos[i] == cos[i + 64] so the first 64 elements suffice). The lanes of a warp are consecutive rows, hence
-    // consecutive positions, so each of these loads is one contiguous kilobyte per warp.
-    const int s = rope_position(g, row);
-    const __nv_bfloat16* tp = g.qk_rope + (int64_t)s * 16;
+    uint32_t olo[8], ohi[8];
 #pragma unroll
-    for (int q = 0; q < 8; ++q) {
-      uint32_t cs[8];
-      ld_global_nc_v8(tp + (int64_t)q * g.qk_S * 16, cs);
-      const uint32_t* cc = cs;
-      const uint32_t* sn = cs + 4;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int e = q * 4 + j;  // pair e holds elements 2e, 2e+1; its rotate-half partner is pair e + 32
-        const __nv_bfloat162 c2 = *reinterpret_cast<const __nv_bfloat162*>(&cc[j]);
-        const __nv_bfloat162 s2 = *reinterpret_cast<const __nv_bfloat162*>(&sn[j]);
-        const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&n[e]);
-        const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&n[e + 32]);
-        const uint32_t neg_hi_bits = n[e + 32] ^ 0x80008000u;
-        const __nv_bfloat162 neg_hi = *reinterpret_cast<const __nv_bfloat162*>(&neg_hi_bits);
-        const __nv_bfloat162 olo = __hadd2_rn(__hmul2_rn(lo, c2), __hmul2_rn(neg_hi, s2));
-        const __nv_bfloat162 ohi = __hadd2_rn(__hmul2_rn(hi, c2), __hmul2_rn(lo, s2));
-        n[e] = *reinterpret_cast<const uint32_t*>(&olo);
-        n[e + 32] = *reinterpret_cast<const uint32_t*>(&ohi);
-      }
+    for (int j = 0; j < 8; ++j) {   // pair j of this step: elements 16t + 2j, 16t + 2j + 1 and their partners
+      const uint32_t pl = pack_bf16x2(__uint_as_float(lo[t & 1][2 * j]) * rs, __uint_as_float(lo[t & 1][2 * j + 1]) * rs);
+      const uint32_t ph = pack_bf16x2(__uint_as_float(hi[t & 1][2 * j]) * rs, __uint_as_float(hi[t & 1][2 * j + 1]) * rs);
+      const __nv_bfloat162 nl = __floats2bfloat162_rn(bf16_lo(pl) * r, bf16_hi(pl) * r);
+      const __nv_bfloat162 nh = __floats2bfloat162_rn(bf16_lo(ph) * r, bf16_hi(ph) * r);
+      const __nv_bfloat162 xl = __hmul2_rn(*reinterpret_cast<const __nv_bfloat162*>(&wlo[j]), nl);
+      const __nv_bfloat162 xh = __hmul2_rn(*reinterpret_cast<const __nv_bfloat162*>(&whi[j]), nh);
+      const uint32_t* cc = cs[j >> 2];          // cos of elements 8q..8q+7 in words 0..3, sin in words 4..7
+      const __nv_bfloat162 c2 = *reinterpret_cast<const __nv_bfloat162*>(&cc[j & 3]);
+      const __nv_bfloat162 s2 = *reinterpret_cast<const __nv_bfloat162*>(&cc[4 + (j & 3)]);
+      const uint32_t xh_bits = *reinterpret_cast<const uint32_t*>(&xh) ^ 0x80008000u;
+      const __nv_bfloat162 neg_xh = *reinterpret_cast<const __nv_bfloat162*>(&xh_bits);
+      const __nv_bfloat162 yl = __hadd2_rn(__hmul2_rn(xl, c2), __hmul2_rn(neg_xh, s2));
+      const __nv_bfloat162 yh = __hadd2_rn(__hmul2_rn(xh, c2), __hmul2_rn(xl, s2));
+      olo[j] = *reinterpret_cast<const uint32_t*>(&yl);
+      ohi[j] = *reinterpret_cast<const uint32_t*>(&yh);
+    }
+    if (valid) {
+      st_global_v8(out + 16 * t, olo);
+      st_global_v8(out + 64 + 16 * t, ohi);
     }
   }
-#pragma unroll
-  for (int q = 0; q < 8; ++q) st_global_v8(out + q * 16, n + q * 8);
 }
 
 // Drains one accumulator (NCHUNK x 32 columns of this thread's row) from tensor memory through the epilogue. The load
