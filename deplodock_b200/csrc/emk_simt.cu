@@ -142,11 +142,11 @@ __global__ void __launch_bounds__(256) gemm_f32_simt_kernel(const float* __restr
 // and its emitted kernel for them is a 2x4-outputs-per-thread tile loop fed by TMA; this one keeps 4x4 outputs per
 // thread in registers over a 64x64 CTA tile, stages 16-deep K slices of both operands through double-buffered
 // shared memory (128-bit global loads, the activation slice stored transposed so a thread's four rows come back as
-// one 128-bit shared load) and prefetches the next slice into registers under the FMAs of the current one. Every
+// one 128-bit shared load) and keeps the next two slices in flight into registers under the FMAs. Every
 // output is still one fmaf chain over k in ascending order, i.e. bit-for-bit the serial reduce loop of the records.
 // x[m,k] may live at (k / x_inner) * x_stride_outer + m * x_stride_m + k % x_inner (the blocked activation layout of
 // the o_proj record); plain row-major is x_inner = K.
-constexpr int FT_M = 64, FT_N = 64, FT_K = 16, FT_LD = 68;
+constexpr int FT_M = 64, FT_N = 64, FT_K = 16, FT_LD = 68, FT_PF = 2;
 
 template <int WL>
 __global__ void __launch_bounds__(256) gemm_f32_tiled_kernel(const float* __restrict__ x, const float* __restrict__ w,
@@ -165,6 +165,7 @@ __global__ void __launch_bounds__(256) gemm_f32_tiled_kernel(const float* __rest
   const int lrow = tid >> 2, lkq = (tid & 3) * 4;
   const int bk = tid >> 4, bnq = (tid & 15) * 4;
   const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  const int xin = (int)x_inner;
   // split-K (gridDim.z > 1, few output tiles): this CTA sums k in [k_begin, k_lim) and adds its partial result to y,
   // which the host zeroed; with one split the result is stored and every output is one fmaf chain over all of k
   const int k_begin = (int)blockIdx.z * k_per_split;
@@ -173,7 +174,8 @@ __global__ void __launch_bounds__(256) gemm_f32_tiled_kernel(const float* __rest
   auto load_a = [&](int k0) -> float4 {
     const int m = m0 + lrow, k = k0 + lkq;
     if (m >= M || k >= k_lim) return zero4;
-    const int64_t off = (int64_t)(k / x_inner) * x_stride_outer + (int64_t)m * x_stride_m + (k % x_inner);
+    const int kq = k / xin;   // 32-bit division: the 64-bit one cost as much as the slice's FMAs
+    const int64_t off = (int64_t)kq * x_stride_outer + (int64_t)m * x_stride_m + (k - kq * xin);
     return __ldg(reinterpret_cast<const float4*>(x + off));
   };
   auto load_b = [&](int k0) -> float4 {
@@ -203,28 +205,38 @@ __global__ void __launch_bounds__(256) gemm_f32_tiled_kernel(const float* __rest
 
   const int nk = (k_lim - k_begin + FT_K - 1) / FT_K;
   if (nk <= 0) return;
-  float4 ra = load_a(k_begin), rb = load_b(k_begin);
-  store_tiles(0, ra, rb);
-  __syncthreads();
-  for (int kt = 0; kt < nk; ++kt) {
-    const int buf = kt & 1;
-    if (kt + 1 < nk) {
-      ra = load_a(k_begin + (kt + 1) * FT_K);
-      rb = load_b(k_begin + (kt + 1) * FT_K);
+  // FT_PF K slices are on their way from global memory into registers at any time (a lone CTA per SM otherwise
+  // spends most of each slice waiting for its loads: a 64-CTA problem ran at 9 TFLOP/s with one slice in flight);
+  // a slice is written to the shared buffer of its parity right before it is used, one barrier per slice
+  float4 ra[FT_PF], rb[FT_PF];
+#pragma unroll
+  for (int p = 0; p < FT_PF; ++p) {
+    ra[p] = load_a(k_begin + p * FT_K);   // slices past the range read zeros
+    rb[p] = load_b(k_begin + p * FT_K);
+  }
+  for (int kt = 0; kt < nk; kt += FT_PF) {
+#pragma unroll
+    for (int p = 0; p < FT_PF; ++p) {
+      const int tile = kt + p;
+      if (tile < nk) {   // uniform over the CTA
+        const int buf = tile & 1;
+        store_tiles(buf, ra[p], rb[p]);
+        __syncthreads();
+        ra[p] = load_a(k_begin + (tile + FT_PF) * FT_K);
+        rb[p] = load_b(k_begin + (tile + FT_PF) * FT_K);
+#pragma unroll
+        for (int k = 0; k < FT_K; ++k) {
+          const float4 a = *reinterpret_cast<const float4*>(&As[buf][k][ty * 4]);
+          const float4 b = *reinterpret_cast<const float4*>(&Bs[buf][k][tx * 4]);
+          const float av[4] = {a.x, a.y, a.z, a.w};
+          const float bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+        }
+      }
     }
-#pragma unroll
-    for (int k = 0; k < FT_K; ++k) {
-      const float4 a = *reinterpret_cast<const float4*>(&As[buf][k][ty * 4]);
-      const float4 b = *reinterpret_cast<const float4*>(&Bs[buf][k][tx * 4]);
-      const float av[4] = {a.x, a.y, a.z, a.w};
-      const float bv[4] = {b.x, b.y, b.z, b.w};
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
-    }
-    if (kt + 1 < nk) store_tiles(buf ^ 1, ra, rb);
-    __syncthreads();
   }
 
 #pragma unroll
@@ -237,7 +249,7 @@ __global__ void __launch_bounds__(256) gemm_f32_tiled_kernel(const float* __rest
       if (n >= N) continue;
       const int64_t idx = (int64_t)m * N + n;
       float v = acc[i][j];
-      if (gridDim.z > 1) {   // partial sum of one K range (no residual / gate epilogue on this path)
+      if (gridDim.z > 1) {   // partial sum of one K range; y was initialised by the host (zeros, or the residual)
         if (blockIdx.z == 0 && bias != nullptr) v = v + bias[n];
         atomicAdd(y + idx, v);
         continue;
@@ -264,7 +276,8 @@ inline bool f32_tiled_ok(const float* x, const float* w, int64_t N, int64_t K, i
 
 // `sm_count` > 0 allows split-K when the output has too few tiles to fill the GPU (the K loop of a lone CTA is bound
 // by the latency of its loads): y is zeroed and the splits add their partial sums with atomics, so the result is
-// then no longer the serial chain, only equal to it within fp32 rounding. The record contractions pass 0.
+// then no longer the serial chain, only equal to it within fp32 rounding. With a residual, y starts as a copy of it;
+// a contraction with the multiplicative gate epilogue is never split.
 template <int WL>
 inline cudaError_t launch_f32_tiled(const float* x, const float* w, const float* bias, const float* residual,
                                     const float* gate, float* y, int64_t M, int64_t N, int64_t K, int64_t x_inner,
@@ -272,14 +285,18 @@ inline cudaError_t launch_f32_tiled(const float* x, const float* w, const float*
   dim3 grid((unsigned)((N + FT_N - 1) / FT_N), (unsigned)((M + FT_M - 1) / FT_M), 1);
   int64_t k_per_split = K;
   const int64_t tiles = (int64_t)grid.x * grid.y;
-  if (sm_count > 0 && residual == nullptr && gate == nullptr && tiles < sm_count && K >= 8 * FT_K) {
-    int64_t splits = (2 * (int64_t)sm_count + tiles - 1) / tiles;
+  if (sm_count > 0 && gate == nullptr && residual != y && tiles < 3 * (int64_t)sm_count && K >= 8 * FT_K) {
+    int64_t splits = (4 * (int64_t)sm_count + tiles - 1) / tiles;   // about four 8-warp CTAs per SM hide the load latency
     if (splits > 16) splits = 16;
     k_per_split = ((K + splits - 1) / splits + FT_K - 1) / FT_K * FT_K;
     grid.z = (unsigned)((K + k_per_split - 1) / k_per_split);
     if (grid.z > 1) {
-      cudaError_t e = cudaMemsetAsync(y, 0, (size_t)(M * N) * sizeof(float), s);
+      // the splits add into y: it starts as zeros, or as the residual (which the sum is then added to)
+      cudaError_t e = residual != nullptr
+                          ? cudaMemcpyAsync(y, residual, (size_t)(M * N) * sizeof(float), cudaMemcpyDeviceToDevice, s)
+                          : cudaMemsetAsync(y, 0, (size_t)(M * N) * sizeof(float), s);
       if (e != cudaSuccess) return e;
+      residual = nullptr;
     }
   }
   gemm_f32_tiled_kernel<WL><<<grid, 256, 0, s>>>(x, w, bias, residual, gate, y, (int)M, (int)N, (int)K, x_inner,
@@ -442,7 +459,7 @@ extern "C" int emk_loop_linear_f32(emk_handle_t h, const float* x, const float* 
   if (M <= 0x7fffffffLL && N <= 0x7fffffffLL && K <= 0x7fffffffLL && (M + FT_M - 1) / FT_M <= 65535 &&
       f32_tiled_ok(x, w, N, K, EMK_W_NK, x_inner, x_stride_outer, x_stride_m)) {
     EMK_CUDA_TRY(h, launch_f32_tiled<0>(x, w, nullptr, residual, gate, y, M, N, K, x_inner, x_stride_outer,
-                                        x_stride_m, (cudaStream_t)stream));
+                                        x_stride_m, (cudaStream_t)stream, h->sm_count));
     EMK_LAUNCH_CHECK(h);
     return EMK_OK;
   }

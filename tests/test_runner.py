@@ -177,3 +177,61 @@ def test_limits(small_runner):
     # out-of-vocabulary ids of a dummy run are clamped, not read out of bounds
     out = runner.forward_packed(torch.full((9,), 10 ** 9, dtype=torch.int64, device="cuda"), list(range(9)))
     assert torch.isfinite(out.float()).all()
+
+
+# ------------------------------------------------------------------------------------------------------------
+# The vLLM model class (built against a stand-in for vLLM's config objects; vLLM itself is not imported)
+# ------------------------------------------------------------------------------------------------------------
+def _fake_vllm_config(cfg, dtype=torch.bfloat16, max_model_len=384, max_num_seqs=4, max_tokens=1024):
+    from types import SimpleNamespace
+
+    hf = SimpleNamespace(vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size, intermediate_size=cfg.intermediate_size,
+                         num_hidden_layers=cfg.num_hidden_layers, num_attention_heads=cfg.num_attention_heads,
+                         num_key_value_heads=cfg.num_key_value_heads, head_dim=cfg.head_dim,
+                         rms_norm_eps=cfg.rms_norm_eps, rope_theta=cfg.rope_theta)
+    mc = SimpleNamespace(dtype=dtype, max_model_len=max_model_len, hf_config=hf, pooler_config=None,
+                         get_vocab_size=lambda: cfg.vocab_size, model="unused")
+    return SimpleNamespace(model_config=mc, scheduler_config=SimpleNamespace(max_num_seqs=max_num_seqs,
+                                                                             max_num_batched_tokens=max_tokens))
+
+
+def test_vllm_model_class_surface(monkeypatch):
+    """Class attributes and constructor of the reference's ``EmmyEmbedModel`` (``emmy/serving/vllm_model.py:48-69``)."""
+    from deplodock_b200 import serving
+
+    monkeypatch.setattr(serving.B200EmbedModel, "_make_pooler", staticmethod(lambda mc: None))
+    cfg = inputs.EmbedModelConfig().small(layers=2, vocab=500)
+    m = serving.B200EmbedModel(vllm_config=_fake_vllm_config(cfg), prefix="")
+    assert m.is_pooling_model and m.default_seq_pooling_type == "LAST" and m.attn_type == "encoder_only"
+    assert m.cfg.num_hidden_layers == 2 and m.cfg.head_dim == 128 and m.vocab_size == 500 and m.runner is None
+    assert list(m.parameters()) == []      # weights live with the kernels, not in nn.Parameters
+    assert tuple(m.embed_input_ids(torch.zeros(7, dtype=torch.int64)).shape) == (7, 0)
+    with pytest.raises(RuntimeError, match="load_weights"):
+        m.forward(torch.zeros(4, dtype=torch.int64), torch.arange(4))
+    with pytest.raises(KeyError, match="lacks"):
+        m.load_weights(iter([("model.norm.weight", torch.ones(1024))]))
+
+
+@pytest.mark.gpu
+def test_vllm_model_class_forward(libemk, monkeypatch):
+    """``load_weights`` from a checkpoint-style stream (``model.`` prefixes, an LM head to skip), then a packed step
+    with vLLM's padding: hidden states per request against the eager CPU trunk, zero rows past the last request."""
+    from deplodock_b200 import serving
+
+    monkeypatch.setattr(serving.B200EmbedModel, "_make_pooler", staticmethod(lambda mc: None))
+    cfg = inputs.EmbedModelConfig().small(layers=2, vocab=500)
+    sd = inputs.perturb_norm_weights(inputs.embed_model_weights(cfg))
+    m = serving.B200EmbedModel(vllm_config=_fake_vllm_config(cfg, dtype=torch.float16))
+    stream = [("model." + k, v) for k, v in sd.items()] + [("lm_head.weight", torch.zeros(4, 4))]
+    taken = m.load_weights(iter(stream))
+    assert "lm_head.weight" not in taken and len(taken) == len(sd)
+    lens = [150, 1, 260]
+    seqs = [inputs.token_ids(1, n, cfg.vocab_size, seed=90 + i)[0] for i, n in enumerate(lens)]
+    ids = torch.cat(seqs + [torch.zeros(5, dtype=torch.int64)]).cuda()
+    pos = torch.cat([torch.arange(n) for n in lens] + [torch.arange(5)]).cuda()
+    out = m(ids, pos)
+    assert out.dtype == torch.float16 and tuple(out.shape) == (sum(lens) + 5, cfg.hidden_size)
+    off = 0
+    for s, n in zip(seqs, lens):
+        _assert_hidden(out[off:off + n], cpu_ref.trunk_hidden_states(s[None], cfg, sd)[0], f"request of {n} tokens")
+        off += n
