@@ -13,7 +13,13 @@ import threading
 from ctypes import c_char_p, c_float, c_int, c_int64, c_void_p
 from pathlib import Path
 
-LIB_PATH = Path(__file__).resolve().parent / "libemk.so"
+import os
+
+#: ``EMK_BOUNDS_CHECK=1`` selects the bounds-check build of the library (``python -m deplodock_b200.build
+#: --bounds-check``): out-of-range token ids, rotary positions and cu_seqlens entries are then reported by
+#: ``device_status`` as ``IndexError`` (status ``EMK_ERR_BOUNDS``) instead of being clamped silently
+BOUNDS_CHECK = os.environ.get("EMK_BOUNDS_CHECK", "0") not in ("", "0")
+LIB_PATH = Path(__file__).resolve().parent / ("libemk_check.so" if BOUNDS_CHECK else "libemk.so")
 
 EMK_OK = 0
 EMK_ERR_SHAPE = 1
@@ -24,6 +30,7 @@ EMK_ERR_CUDA = 5
 EMK_ERR_TIMEOUT = 6
 EMK_ERR_ARG = 7
 EMK_ERR_LIMIT = 8
+EMK_ERR_BOUNDS = 9
 
 EMK_F32, EMK_BF16, EMK_F16 = 0, 1, 2
 EMK_EW_ADD, EMK_EW_MUL, EMK_EW_SILU, EMK_EW_SILU_MUL = 0, 1, 2, 3
@@ -57,6 +64,7 @@ class EmkLibraryMissing(RuntimeError):
 # name -> (argtypes); every function returns int unless listed in _RESTYPES
 _SIGNATURES: dict[str, list] = {
     "emk_version": [],
+    "emk_bounds_check_enabled": [],
     "emk_status_string": [c_int],
     "emk_create": [c_int, ctypes.POINTER(c_void_p)],
     "emk_destroy": [c_void_p],
@@ -125,7 +133,8 @@ def load_library() -> ctypes.CDLL:
             return _lib
         if not LIB_PATH.exists():
             raise EmkLibraryMissing(
-                f"{LIB_PATH} not found: build it with `python -m deplodock_b200.build` (needs nvcc). "
+                f"{LIB_PATH} not found: build it with `python -m deplodock_b200.build"
+                f"{' --bounds-check' if BOUNDS_CHECK else ''}` (needs nvcc). "
                 "There is no CPU or PyTorch fallback for the kernels."
             )
         lib = ctypes.CDLL(str(LIB_PATH))
@@ -167,6 +176,8 @@ class Handle:
             raise TypeError(msg)
         if rc == EMK_ERR_TIMEOUT:
             raise HungKernelError(msg)
+        if rc == EMK_ERR_BOUNDS:
+            raise IndexError(msg)
         raise RuntimeError(msg)
 
     def device_status(self, stream: int = 0) -> None:

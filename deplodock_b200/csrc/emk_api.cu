@@ -8,6 +8,14 @@
 
 extern "C" int emk_version(void) { return EMK_VERSION; }
 
+extern "C" int emk_bounds_check_enabled(void) {
+#ifdef EMK_BOUNDS_CHECK
+  return 1;
+#else
+  return 0;
+#endif
+}
+
 extern "C" const char* emk_status_string(int s) {
   switch (s) {
     case EMK_OK: return "ok";
@@ -19,6 +27,7 @@ extern "C" const char* emk_status_string(int s) {
     case EMK_ERR_TIMEOUT: return "device-side wait expired";
     case EMK_ERR_ARG: return "invalid argument";
     case EMK_ERR_LIMIT: return "size beyond the entry point's fixed maximum";
+    case EMK_ERR_BOUNDS: return "a data-dependent index was out of range (bounds-check build)";
     default: return "unknown status";
   }
 }
@@ -102,6 +111,13 @@ extern "C" int emk_device_status(emk_handle_t h, emk_stream_t stream) {
   int code = *(volatile int*)h->status_host;
   if (code != 0) {
     *(volatile int*)h->status_host = 0;
+    if (code >= EMK_DEV_BOUNDS_TOKEN_ID) {
+      EMK_SET_ERR(h, "out-of-range %s (code %d); the access was clamped or dropped",
+                  code == EMK_DEV_BOUNDS_TOKEN_ID ? "token id in the embedding gather"
+                  : code == EMK_DEV_BOUNDS_POSITION ? "rotary position"
+                  : "sequence in cu_seqlens", code);
+      return EMK_ERR_BOUNDS;
+    }
     EMK_SET_ERR(h, "device-side wait expired (role code %d)", code);
     return EMK_ERR_TIMEOUT;
   }

@@ -78,8 +78,26 @@ enum {
   EMK_DEV_TIMEOUT_EPILOGUE = 103,
   EMK_DEV_TIMEOUT_SOFTMAX = 104,
   EMK_DEV_TIMEOUT_SELFTEST = 105,
-  EMK_DEV_TIMEOUT_CONVERT = 106
+  EMK_DEV_TIMEOUT_CONVERT = 106,
+  // bounds-check build (-DEMK_BOUNDS_CHECK) only: a data-dependent index was outside its range
+  EMK_DEV_BOUNDS_TOKEN_ID = 201,   // embedding gather: id outside [0, vocab)
+  EMK_DEV_BOUNDS_POSITION = 202,   // rotary position outside the table
+  EMK_DEV_BOUNDS_CU_SEQLENS = 203  // packed attention: a sequence outside the token rows or longer than max_seqlen
 };
+
+// The bounds-check build of the library (python -m deplodock_b200.build --bounds-check -> libemk_check.so) stands in
+// for a memory checker on machines where none may be run: indices that come from DATA (token ids, rotary positions,
+// cu_seqlens) — the only ones the host cannot validate before a launch — are checked where they are used. Both builds
+// make the access safe (clamp or drop); the checked build also records which kind of index was bad in the handle's
+// status word, so the next emk_device_status returns EMK_ERR_BOUNDS. The normal build compiles the recording away.
+__device__ __forceinline__ void emk_record_bounds(int* status, int code) {
+#ifdef EMK_BOUNDS_CHECK
+  if (status != nullptr) *(volatile int*)status = code;
+#else
+  (void)status;
+  (void)code;
+#endif
+}
 
 // Encodes a 2-D row-major tensor map: `inner` contiguous elements per row, `outer` rows, row pitch in bytes.
 int emk_make_tmap_2d(emk_handle_t h, CUtensorMap* out, CUtensorMapDataType dt, int elem_bytes, const void* base,

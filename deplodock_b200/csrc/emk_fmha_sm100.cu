@@ -608,8 +608,19 @@ fmha_causal_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
 // sequence order within a level. table[0].x receives the number of entries; entries start at table[1].
 constexpr int VL_MAX_LEVELS = 1024;
 
+// A sequence whose rows do not lie inside [0, total) or that is longer than max_seqlen is cut to the part that does
+// (the attention kernel's row stores must never leave the output); the bounds-check build also reports it.
+__device__ __forceinline__ void varlen_sequence(const int* __restrict__ cu_seqlens, int b, int total, int max_seqlen,
+                                                int* status, int& r0, int& len) {
+  const int a = cu_seqlens[b], e = cu_seqlens[b + 1];
+  r0 = min(max(a, 0), total);
+  len = min(min(max(e - r0, 0), total - r0), max_seqlen);
+  if (a < 0 || e < a || e > total || e - a > max_seqlen) emk_record_bounds(status, EMK_DEV_BOUNDS_CU_SEQLENS);
+}
+
 __global__ void __launch_bounds__(VL_MAX_LEVELS) varlen_items_kernel(const int* __restrict__ cu_seqlens, int B,
-                                                                     int levels, int4* __restrict__ table) {
+                                                                     int levels, int4* __restrict__ table, int total,
+                                                                     int max_seqlen, int* status) {
   __shared__ int count[VL_MAX_LEVELS];
   __shared__ int offset[VL_MAX_LEVELS];
   const int l = (int)threadIdx.x;
@@ -618,7 +629,8 @@ __global__ void __launch_bounds__(VL_MAX_LEVELS) varlen_items_kernel(const int* 
   int c = 0;
   if (l < levels) {
     for (int b = 0; b < B; ++b) {
-      const int len = cu_seqlens[b + 1] - cu_seqlens[b];
+      int r0, len;
+      varlen_sequence(cu_seqlens, b, total, max_seqlen, l == 0 ? status : nullptr, r0, len);
       c += (len > l * FM) ? 1 : 0;
     }
   }
@@ -636,8 +648,8 @@ __global__ void __launch_bounds__(VL_MAX_LEVELS) varlen_items_kernel(const int* 
   if (l < levels && c > 0) {
     int4* out = table + 1 + offset[l];
     for (int b = 0; b < B; ++b) {
-      const int r0 = cu_seqlens[b];
-      const int len = cu_seqlens[b + 1] - r0;
+      int r0, len;
+      varlen_sequence(cu_seqlens, b, total, max_seqlen, nullptr, r0, len);
       if (len > l * FM) *out++ = make_int4(r0, l * FM, len, 0);
     }
   }
@@ -777,7 +789,7 @@ int fmha_launch(emk_handle_t h, const void* q, const void* k, const void* v, voi
     a.q_rb = a.kv_rb = a.o_rb = 0;
     EMK_CUDA_TRY(h, launch_after_prologue(varlen_items_kernel, 1u, (unsigned)VL_MAX_LEVELS, 0, s,
                                           h->overlap_launch != 0, vl->cu_seqlens, (int)B, (int)((S + FM - 1) / FM),
-                                          table));
+                                          table, (int)vl->total, (int)S, h->status_dev));
   }
   EMK_CUDA_TRY(h, launch_after_prologue(fmha_causal_kernel, (unsigned)grid, FMHA_THREADS, FMHA_SMEM, s,
                                         h->overlap_launch != 0, tq, tk, tv, to, a));

@@ -181,7 +181,11 @@ __device__ __forceinline__ float epilogue_store32(const GemmArgs& g, const uint3
 // Rotary position of output row `row`: given per row for packed sequences (clamped to the table), else the row's
 // offset within its fixed-length sequence.
 __device__ __forceinline__ int rope_position(const GemmArgs& g, int row) {
-  if (g.qk_pos != nullptr) return min(max(__ldg(g.qk_pos + row), 0), g.qk_S - 1);
+  if (g.qk_pos != nullptr) {
+    const int p = __ldg(g.qk_pos + row);
+    if (p < 0 || p >= g.qk_S) emk_record_bounds(g.status, EMK_DEV_BOUNDS_POSITION);
+    return min(max(p, 0), g.qk_S - 1);
+  }
   return row % g.qk_S;
 }
 

@@ -19,14 +19,17 @@ using namespace emk;
 __global__ void __launch_bounds__(256) embed_gather_kernel(const uint4* __restrict__ table,
                                                            const int64_t* __restrict__ ids, uint4* __restrict__ out,
                                                            float* __restrict__ row_sumsq, int64_t tokens,
-                                                           int vec_per_row, int64_t vocab) {
+                                                           int vec_per_row, int64_t vocab, int* status) {
   const int lane = threadIdx.x & 31;
   const int64_t warp = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
   grid_dependency_wait();
   grid_launch_dependents();
   if (warp >= tokens) return;
   int64_t id = ids[warp];
-  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);  // clamp instead of reading out of bounds
+  if (id < 0 || id >= vocab) {
+    if (lane == 0) emk_record_bounds(status, EMK_DEV_BOUNDS_TOKEN_ID);
+    id = id < 0 ? 0 : vocab - 1;  // clamp instead of reading out of bounds
+  }
   const uint4* src = table + id * vec_per_row;
   uint4* dst = out + warp * vec_per_row;
   float ss = 0.f;
@@ -239,7 +242,7 @@ extern "C" int emk_embed_gather_sumsq(emk_handle_t h, const void* table, const i
   const int64_t grid = (tokens + 7) / 8;
   EMK_CUDA_TRY(h, launch_after_prologue(embed_gather_kernel, (unsigned)grid, 256u, 0, (cudaStream_t)stream,
                                         h->overlap_launch != 0, (const uint4*)table, ids, (uint4*)out, row_sumsq, tokens,
-                                        (int)(hidden / 8), vocab));
+                                        (int)(hidden / 8), vocab, h->status_dev));
   EMK_LAUNCH_CHECK(h);
   return EMK_OK;
 }

@@ -35,7 +35,9 @@ typedef enum {
   EMK_ERR_CUDA = 5,      /* a CUDA runtime/driver call failed; see emk_last_error               */
   EMK_ERR_TIMEOUT = 6,   /* a bounded device-side wait ran out (read back by emk_device_status) */
   EMK_ERR_ARG = 7,       /* null pointer / bad enum                                             */
-  EMK_ERR_LIMIT = 8      /* size beyond a stated fixed maximum of the entry point               */
+  EMK_ERR_LIMIT = 8,     /* size beyond a stated fixed maximum of the entry point               */
+  EMK_ERR_BOUNDS = 9     /* bounds-check build only: a token id, rotary position or cu_seqlens entry was out of
+                            range (the access was clamped or dropped); read back by emk_device_status */
 } emk_status_t;
 
 /* dtype tokens: same names as the reference's graph dtypes (emmy/compiler/dtype.py:61-69). */
@@ -65,6 +67,11 @@ typedef void* emk_stream_t; /* a cudaStream_t */
 /* Library identity and error text. Replaces nothing in the reference (bookkeeping for the binding). */
 int emk_version(void);
 const char* emk_status_string(int status);
+/* 1 in the bounds-check build of the library (compiled with -DEMK_BOUNDS_CHECK: indices that come from data — token
+ * ids, rotary positions, cu_seqlens — are checked on the device and a violation is reported by emk_device_status as
+ * EMK_ERR_BOUNDS), 0 in the normal build (same clamping, nothing recorded). The reference has no counterpart: its
+ * generated kernels are checked with compute-sanitizer in its own test runs. */
+int emk_bounds_check_enabled(void);
 
 /* Per-device handle: holds the device id, SM count, the driver entry point used to encode TMA tensor maps
  * (the reference calls cuTensorMapEncodeTiled through ctypes, emmy/compiler/backend/cuda/_tma.py:91-170) and a
