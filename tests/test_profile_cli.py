@@ -59,6 +59,22 @@ def test_csv_reduction_sides_and_roofline_columns():
     assert "dur (nsecond)" in lines[1] and "tensor%" in lines[1] and "hbm" in lines[1]
 
 
+def test_own_kernel_list_matches_the_sources():
+    import re
+
+    found = set()
+    for path in (Path(__file__).resolve().parent.parent / "deplodock_b200" / "csrc").glob("*.cu*"):
+        for m in re.finditer(r"__global__\s+void\s+(?:__cluster_dims__\([^)]*\)\s*)?(?:__launch_bounds__\([^)]*\)\s*)?"
+                             r"([A-Za-z_][A-Za-z_0-9]*)\s*\(", path.read_text(), flags=re.S):
+            found.add(m.group(1))
+    assert found == set(profile.OWN_KERNELS)
+    # PyTorch's own anonymous-namespace kernels are printed the same way by ncu and must stay on the ref side
+    assert not profile.is_own_kernel("void <unnamed>::softmax_warp_forward<float, float, float, 11, 0, 0>(T2 *, const T1 *)")
+    assert profile.is_own_kernel("void <unnamed>::split6_bf16_kernel<1, 1>(const float *, __nv_bfloat16 *, long, long)")
+    assert profile.is_own_kernel("k_rms_norm_239c6c") and not profile.is_own_kernel("void at::native::elementwise_kernel<128>()")
+    assert profile.kernel_base_name("<unnamed>::fmha_causal_kernel(CUtensorMap_st, FmhaArgs)") == "fmha_causal_kernel"
+
+
 def _args(argv):
     return build_parser().parse_args(argv)
 
