@@ -33,52 +33,58 @@ from deplodock_b200.graph import Graph, Node
 
 
 # ------------------------------------------------------------------------------------------------------------
-# Result types (same fields as emmy/compiler/backend/base.py:45-91)
+# Result types and the abstract base (emmy/compiler/backend/base.py:45-205)
 # ------------------------------------------------------------------------------------------------------------
-@dataclass
-class RunResult:
-    outputs: dict[str, Any]
-    time_ms: float | None = None
-
-
-@dataclass
-class LaunchTime:
-    idx: int
-    kernel_name: str
-    time_ms: float
-    samples: tuple[float, ...] | None = None
-
-
-@dataclass
-class BenchmarkResult:
-    time_ms: float
-    min_ms: float | None = None
-    max_ms: float | None = None
-    num_launches: int = 0
-    per_launch: list[LaunchTime] | None = None
-    captured: bool = False
-    e2e_ms: float | None = None
-    e2e_min_ms: float | None = None
-
-
 class LoweringError(RuntimeError):
     """No hand-written kernel covers a node (the reference raises ``LoweringError`` from its pipeline)."""
 
 
-class Backend(ABC):
-    """Abstract backend: Graph -> compiled artifact -> run (``emmy/compiler/backend/base.py:94-205``)."""
+try:
+    # Inside the reference's process the reference's own types are used, so that its callers' isinstance checks and
+    # dataclass handling see exactly what CudaBackend would hand them.
+    from emmy.compiler.backend.base import Backend, BenchmarkResult, LaunchTime, RunResult
 
-    name: str = "stub"
-    bench_compile_timeout_s: float = 30.0
-    bench_run_timeout_s: float = 10.0
-    bench_wall_timeout_s: float | None = None
+    USES_REFERENCE_TYPES = True
+except Exception:  # noqa: BLE001 - the reference package is absent (the usual case): same fields, defined here
+    USES_REFERENCE_TYPES = False
 
-    @abstractmethod
-    def compile(self, graph: Any) -> Any: ...
+    @dataclass
+    class RunResult:
+        outputs: dict[str, Any]
+        time_ms: float | None = None
 
-    @abstractmethod
-    def run(self, compiled: Any, *, input_data: dict[str, np.ndarray] | None = None,
-            pre_run: Callable[[], Any] | None = None) -> tuple[RunResult, Any]: ...
+    @dataclass
+    class LaunchTime:
+        idx: int
+        kernel_name: str
+        time_ms: float
+        samples: tuple[float, ...] | None = None
+
+    @dataclass
+    class BenchmarkResult:
+        time_ms: float
+        min_ms: float | None = None
+        max_ms: float | None = None
+        num_launches: int = 0
+        per_launch: list[LaunchTime] | None = None
+        captured: bool = False
+        e2e_ms: float | None = None
+        e2e_min_ms: float | None = None
+
+    class Backend(ABC):
+        """Abstract backend: Graph -> compiled artifact -> run (``emmy/compiler/backend/base.py:94-205``)."""
+
+        name: str = "stub"
+        bench_compile_timeout_s: float = 30.0
+        bench_run_timeout_s: float = 10.0
+        bench_wall_timeout_s: float | None = None
+
+        @abstractmethod
+        def compile(self, graph: Any) -> Any: ...
+
+        @abstractmethod
+        def run(self, compiled: Any, *, input_data: dict[str, np.ndarray] | None = None,
+                pre_run: Callable[[], Any] | None = None) -> tuple[RunResult, Any]: ...
 
 
 # ------------------------------------------------------------------------------------------------------------

@@ -419,3 +419,32 @@ def test_dynamic_spec_grammar_and_tracing():
     assert tr.graph.nodes["rms_norm"].output.shape == (2, "seq_len", 256)
     with pytest.raises(ValueError, match="no input named"):
         trace_inline_code("nn.RMSNorm(256)(torch.randn(2, 5, 256))", [("s", "nope", 1)])
+
+
+def test_backend_subclasses_the_reference_base_when_it_is_importable():
+    """Inside the reference's process ``B200Backend`` must BE a reference ``Backend`` (its callers check with
+    isinstance) and hand back the reference's own result dataclasses. Needs the reference checkout: skipped without."""
+    import subprocess
+
+    from oracle import build_ref_kernels
+
+    ref = build_ref_kernels.find_reference()
+    if ref is None:
+        pytest.skip("reference checkout not present")
+    code = (
+        "import sys; sys.path.insert(0, %r)\n"
+        "from deplodock_b200 import backend\n"
+        "from emmy.compiler.backend.base import Backend, RunResult, BenchmarkResult, LaunchTime\n"
+        "b = backend.B200Backend(device_id=0)\n"
+        "assert backend.USES_REFERENCE_TYPES and isinstance(b, Backend)\n"
+        "assert backend.RunResult is RunResult and backend.BenchmarkResult is BenchmarkResult\n"
+        "assert backend.LaunchTime is LaunchTime\n"
+        "print('OK', len(b.compile(%r).steps))\n") % (str(ROOT), str(GOLDEN / "graphs" / "cfg1_rmsnorm.json"))
+    res = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300,
+                         env=dict(os.environ, PYTHONPATH=ref))
+    assert res.returncode == 0 and "OK 1" in res.stdout, res.stderr[-2000:]
+    from deplodock_b200 import backend
+
+    assert not backend.USES_REFERENCE_TYPES   # and stand-alone it defines the same types itself
+    assert [f for f in backend.BenchmarkResult.__dataclass_fields__] == [
+        "time_ms", "min_ms", "max_ms", "num_launches", "per_launch", "captured", "e2e_ms", "e2e_min_ms"]
