@@ -202,7 +202,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       epilogue_drain<G2_BN / 64>(g, taddr, row, n0);
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&bars->tmem_empty[acc]), 0));
+      if (lane == 0) mbar_arrive_cluster_relaxed(mapa_u32(smem_u32(&bars->tmem_empty[acc]), 0));
     }
   }
 

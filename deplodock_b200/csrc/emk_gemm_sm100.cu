@@ -165,7 +165,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 epilogue_drain<BN / 32>(g, taddr, row, n0);
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->tmem_empty[acc]);
+      if (lane == 0) mbar_arrive_relaxed(&bars->tmem_empty[acc]);
     }
   }
 

@@ -205,7 +205,7 @@ gemm_w8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 epilogue_drain<W8_BN / 32>(g, taddr, row, n0);
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->tmem_empty[acc]);
+      if (lane == 0) mbar_arrive_relaxed(&bars->tmem_empty[acc]);
     }
   }
 
