@@ -496,8 +496,8 @@ def gemm_event_pass(model, passes: int = 8, heat=None, gpu_index: int = 0) -> di
 
     from deplodock_b200 import ops
 
-    names = ["embed_gather", "rmsnorm", "linear", "linear_qknorm_rope", "gemm_fused", "sdpa_causal_gqa_tok",
-             "pool_norm_l2"]
+    names = ["embed_gather", "rmsnorm", "linear", "linear_qknorm_rope", "gemm_fused", "gemm_chain",
+             "sdpa_causal_gqa_tok", "pool_norm_l2"]
     originals = {n: getattr(ops, n) for n in names}
     events = []
 
@@ -508,7 +508,14 @@ def gemm_event_pass(model, passes: int = 8, heat=None, gpu_index: int = 0) -> di
             r = fn(*args, **kw)
             e.record()
             fam, key, fl = name, name, 0
-            if name in ("linear", "linear_qknorm_rope", "gemm_fused"):
+            if name == "gemm_chain":   # several projections in one persistent launch: flops summed over its phases
+                phases = args[0]
+                M = phases[0]["x"].numel() // phases[0]["x"].shape[-1]
+                fl = sum(2 * M * ph["x"].shape[-1] * ph["w"].shape[0] for ph in phases)
+                key = f"chain[{M} rows: " + " -> ".join(f"{ph['w'].shape[0]}x{ph['x'].shape[-1]}+{ph['epilogue']}"
+                                                       for ph in phases) + "]"
+                fam = "linear"
+            elif name in ("linear", "linear_qknorm_rope", "gemm_fused"):
                 x, w = args[0], args[1]
                 M = x.numel() // x.shape[-1]
                 fl = 2 * M * x.shape[-1] * w.shape[0]
@@ -690,7 +697,10 @@ def main() -> None:
         peak = peaks["bf16_tflops_sustained"]
         cap = GEMM_TRAFFIC_CAPTURE
         roofline = {
-            "bound": "tensor", "kernel": "gemm2_bf16_kernel (tcgen05 cta_group::2, all four projections of every layer)",
+            "bound": "tensor",
+            "kernel": ("gemm2_chain_kernel + gemm2_bf16_kernel (tcgen05 cta_group::2; o_proj, gate/up, down and the "
+                       "next layer's QKV of every layer as one persistent launch)" if model.chain else
+                       "gemm2_bf16_kernel (tcgen05 cta_group::2, all four projections of every layer)"),
             "achieved": round(gemm_tflops, 1), "peak": peak, "peak_source": f"{peak_src} (sustained cuBLAS bf16)",
             "unit": "TFLOP/s", "frac": round(gemm_tflops / peak, 4),
             "frac_of_burst_peak": round(gemm_tflops / peaks["bf16_tflops"], 4),
@@ -716,7 +726,7 @@ def main() -> None:
                                    "last-token pool + L2; random-init N(0,0.02) bf16 weights",
                        "global_batch": BATCH, "seq_len": SEQ, "parallelism": f"batch-shard x{world}, weights replicated",
                        "l2_policy": "inputs larger than L2 (1.2 GB of weights + activations per step)",
-                       "cuda_graph": True, "chunk_seqs": model.chunk_seqs},
+                       "cuda_graph": True, "chunk_seqs": model.chunk_seqs, "gemm_chain": model.chain},
             "step_tflops": round(step_flops / (ms_per_step * 1e-3) / 1e12, 1),
             "seqs_per_s_per_sm_mhz": None if not clocks or not clocks.get("sm_mhz") else round(
                 value / clocks["sm_mhz"], 4),

@@ -502,7 +502,7 @@ class B200Backend(Backend):
                           rms_norm_eps=m.rms_norm_eps, rope_theta=0.0)
         sd = {name: vals[nid] for name, nid in m.state_dict_names().items()}
         ex = EmbedForward(cfg, sd, batch=m.batch, seq=m.seq, device=dev, hidden_states=True, pool=False,
-                          rope=(vals[m.cos], vals[m.sin]))
+                          rope=(vals[m.cos], vals[m.sin]), chain=False)   # one launch per listed kernel
         ex.launches = ex.launch_list(ex.ids, ex.out)
         return ex
 

@@ -85,6 +85,8 @@ _SIGNATURES: dict[str, list] = {
     "emk_linear_bf16_qknorm_rope": [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p,
                                     c_void_p, c_void_p, c_int64, c_int64, c_int64, c_float, c_void_p],
     "emk_gemm_bf16_fused": [c_void_p, c_void_p, c_void_p],
+    "emk_gemm_bf16_chain_workspace_bytes": [c_int64],
+    "emk_gemm_bf16_chain": [c_void_p, c_void_p, c_int, c_void_p, c_int64, c_void_p],
     "emk_linear_residual_rmsnorm_bf16_noalloc": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                  c_int64, c_int64, c_int64, c_float, c_void_p],
     "emk_linear_bf16_w8": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64,
@@ -116,7 +118,7 @@ _SIGNATURES: dict[str, list] = {
 }
 _RESTYPES = {"emk_status_string": c_char_p, "emk_last_error": c_char_p,
              "emk_linear_bf16_w8_workspace_bytes": c_int64, "emk_sdpa_varlen_workspace_bytes": c_int64,
-             "emk_linear_f32_tc_workspace_bytes": c_int64}
+             "emk_linear_f32_tc_workspace_bytes": c_int64, "emk_gemm_bf16_chain_workspace_bytes": c_int64}
 
 #: every symbol ``include/emk.h`` declares; ``tests/test_cabi_symbols.py`` checks the header against this list
 EXPORTED_SYMBOLS = tuple(_SIGNATURES)

@@ -53,6 +53,8 @@ extern "C" int emk_create(int device, emk_handle_t* out) {
   h->gemm_impl = impl ? atoi(impl) : 0;
   const char* ovl = getenv("EMK_OVERLAP_LAUNCH");
   h->overlap_launch = (ovl && atoi(ovl) == 0) ? 0 : 1;
+  const char* cgm = getenv("EMK_CHAIN_GROUP_M");
+  h->chain_group_m = (cgm && atoi(cgm) > 0) ? atoi(cgm) : 4;
   cudaError_t e = cudaSetDevice(device);
   if (e != cudaSuccess) {
     free(h);

@@ -44,6 +44,7 @@ struct emk_handle_s {
   int gemm_impl;        // 0 = choose by shape, 1 = single-CTA tiles, 2 = CTA-pair tiles (env EMK_GEMM_IMPL)
   int overlap_launch;   // 1 = kernels of the model path start their prologue under the previous kernel's tail
                         // (programmatic dependent launch; env EMK_OVERLAP_LAUNCH=0 turns it off)
+  int chain_group_m;    // GEMM chain: 256-row blocks per raster group (env EMK_CHAIN_GROUP_M)
   char last_error[512];
 };
 
@@ -79,6 +80,7 @@ enum {
   EMK_DEV_TIMEOUT_SOFTMAX = 104,
   EMK_DEV_TIMEOUT_SELFTEST = 105,
   EMK_DEV_TIMEOUT_CONVERT = 106,
+  EMK_DEV_TIMEOUT_DEPENDENCY = 107,  // GEMM chain: an earlier phase's rows never became final
   // bounds-check build (-DEMK_BOUNDS_CHECK) only: a data-dependent index was outside its range
   EMK_DEV_BOUNDS_TOKEN_ID = 201,   // embedding gather: id outside [0, vocab)
   EMK_DEV_BOUNDS_POSITION = 202,   // rotary position outside the table
@@ -145,6 +147,10 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 __device__ __forceinline__ void fence_barrier_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
+// Orders this thread's earlier generic-proxy accesses (all state spaces) before its later async-proxy ones (TMA).
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+// The same for global memory only.
+__device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
@@ -503,6 +509,13 @@ __device__ __forceinline__ void ld_global_nc_v8(const void* p, uint32_t* v) {
   asm volatile("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
                : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
                : "l"(p));
+}
+// 256-bit load that bypasses L1 (cache-global): for data another SM may have written earlier in the SAME launch.
+__device__ __forceinline__ void ld_global_cg_v8(const void* p, uint32_t* v) {
+  asm volatile("ld.global.cg.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+               : "l"(p)
+               : "memory");
 }
 __device__ __forceinline__ void ld_global_v8(const void* p, uint32_t* v) {
   asm volatile("ld.global.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"

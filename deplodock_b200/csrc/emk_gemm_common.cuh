@@ -38,6 +38,9 @@ struct GemmArgs {
   int ss_in_segs;
   float ss_inv_dim, ss_eps;
   float* ss_out;
+  // set by the GEMM chain: residual and ss_in may have been written by another SM earlier in the same launch, so
+  // they are read past L1 and never prefetched into it
+  int coherent;
   int* status;
   unsigned long long limit_ns;
 };
@@ -123,13 +126,18 @@ __device__ __forceinline__ float epilogue_store32(const GemmArgs& g, const uint3
     const __nv_bfloat16* res = g.residual + (int64_t)row * g.ldy + col0;
     uint32_t rr[16];
     if (full) {
-      ld_global_v8(res, rr);
-      ld_global_v8(res + 16, rr + 8);
+      if (g.coherent) {
+        ld_global_cg_v8(res, rr);
+        ld_global_cg_v8(res + 16, rr + 8);
+      } else {
+        ld_global_v8(res, rr);
+        ld_global_v8(res + 16, rr + 8);
+      }
     } else {
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
         uint4 t = make_uint4(0, 0, 0, 0);
-        if (col0 + q * 8 < g.N) t = *reinterpret_cast<const uint4*>(res + q * 8);
+        if (col0 + q * 8 < g.N) t = __ldcg(reinterpret_cast<const uint4*>(res + q * 8));
         rr[q * 4 + 0] = t.x; rr[q * 4 + 1] = t.y; rr[q * 4 + 2] = t.z; rr[q * 4 + 3] = t.w;
       }
     }
@@ -194,7 +202,7 @@ __device__ __forceinline__ int rope_position(const GemmArgs& g, int row) {
 // epilogue (two warps per scheduler, little latency hiding of its own) finds it in L1 / L2.
 __device__ __forceinline__ void epilogue_prefetch(const GemmArgs& g, int row, int n0, int ncols) {
   if (row >= g.M || n0 >= g.N) return;
-  if (g.ss_in != nullptr) {
+  if (g.ss_in != nullptr && !g.coherent) {
     asm volatile("prefetch.global.L1 [%0];" ::"l"(g.ss_in + (int64_t)row * g.ss_in_segs));
   }
   if (g.epi == EMK_EPI_QKNORM_ROPE_INTERNAL) {
@@ -328,11 +336,12 @@ __device__ __forceinline__ void epilogue_drain(const GemmArgs& g, uint32_t taddr
     float tot = 0.f;
     if (g.ss_in_segs == 8) {
       uint32_t u[8];
-      ld_global_nc_v8(pr, u);
+      if (g.coherent) ld_global_cg_v8(pr, u);
+      else ld_global_nc_v8(pr, u);
       tot = ((__uint_as_float(u[0]) + __uint_as_float(u[1])) + (__uint_as_float(u[2]) + __uint_as_float(u[3]))) +
             ((__uint_as_float(u[4]) + __uint_as_float(u[5])) + (__uint_as_float(u[6]) + __uint_as_float(u[7])));
     } else {
-      for (int sg = 0; sg < g.ss_in_segs; ++sg) tot += __ldg(pr + sg);
+      for (int sg = 0; sg < g.ss_in_segs; ++sg) tot += g.coherent ? __ldcg(pr + sg) : __ldg(pr + sg);
     }
     rs = 1.0f / sqrtf(tot * g.ss_inv_dim + g.ss_eps);
   }

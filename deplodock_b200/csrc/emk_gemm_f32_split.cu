@@ -27,9 +27,16 @@ namespace {
 
 using namespace emk;
 
-// Which of the three terms goes into each of the six blocks.
-__constant__ int c_pat_a[6] = {0, 1, 2, 0, 1, 0};
-__constant__ int c_pat_w[6] = {2, 1, 0, 1, 0, 0};
+// Which of the three terms goes into each of the six blocks: A' = [x1 x2 x3 x1 x2 x1], W' = [w3 w2 w1 w2 w1 w1].
+// A compile-time function of the unrolled block index, so the terms stay in registers.
+template <bool IS_W>
+__device__ __forceinline__ constexpr int split_term(int b) {
+  return IS_W ? (b == 0 ? 2 : (b == 1 || b == 3) ? 1 : 0) : ((b == 0 || b == 3 || b == 5) ? 0 : (b == 2) ? 2 : 1);
+}
+static_assert(split_term<false>(0) == 0 && split_term<false>(1) == 1 && split_term<false>(2) == 2 &&
+              split_term<false>(3) == 0 && split_term<false>(4) == 1 && split_term<false>(5) == 0, "A' pattern");
+static_assert(split_term<true>(0) == 2 && split_term<true>(1) == 1 && split_term<true>(2) == 0 &&
+              split_term<true>(3) == 1 && split_term<true>(4) == 0 && split_term<true>(5) == 0, "W' pattern");
 
 // in [R, C] fp32 row-major. STACKED = false: out [R, 6C] bf16, block b of row r at columns [bC, bC + C) (the A'
 // layout, and W' for W [N,K]); STACKED = true: out [6R, C], block b at rows [bR, bR + R) (W' for W [K,N]).
@@ -62,7 +69,7 @@ __global__ void __launch_bounds__(256) split6_bf16_kernel(const float* __restric
   }
 #pragma unroll
   for (int b = 0; b < 6; ++b) {
-    const int term = IS_W ? c_pat_w[b] : c_pat_a[b];
+    const int term = split_term<IS_W>(b);
     __nv_bfloat16* dst = STACKED ? out + ((int64_t)b * R + r) * C + c : out + r * (6 * C) + (int64_t)b * C + c;
     *reinterpret_cast<uint4*>(dst) = make_uint4(t[term][0], t[term][1], t[term][2], t[term][3]);
   }

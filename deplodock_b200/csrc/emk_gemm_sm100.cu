@@ -212,7 +212,8 @@ struct RowStatArgs {
 int gemm_dispatch(emk_handle_t h, const void* x, const void* w, const void* residual, const float* scale, void* y,
                   int64_t M, int64_t N, int64_t K, int wlayout, int epilogue, cudaStream_t s,
                   const QkRopeArgs* qk = nullptr, const RowStatArgs* rsx = nullptr, bool f32_out = false,
-                  const float* f32_bias = nullptr) {
+                  const float* f32_bias = nullptr, GemmArgs* args_only = nullptr) {
+  // args_only: validate and fill the kernel arguments (tiling left to the caller) without launching anything
   if (!h || !x || !w || !y) return EMK_ERR_ARG;
   if (M <= 0 || N <= 0 || K <= 0 || M > 0x7fffffff || N > 0x7fffffff || K > 0x7fffffff) return EMK_ERR_SHAPE;
   if (wlayout != EMK_W_NK && wlayout != EMK_W_KN) return EMK_ERR_ARG;
@@ -274,7 +275,15 @@ int gemm_dispatch(emk_handle_t h, const void* x, const void* w, const void* resi
     g.qk_Hkv = qk->Hkv;
     g.qk_eps = qk->eps;
     g.qk_pos = qk->pos;
+    if (args_only) {
+      *args_only = g;
+      return EMK_OK;
+    }
     return emk_gemm2_launch(h, x, w, g, wlayout, s);
+  }
+  if (args_only) {
+    *args_only = g;
+    return EMK_OK;
   }
   // CTA-pair tiles (256x256) when the problem has at least one full pair tile; single-CTA tiles otherwise.
   const bool pair_ok = M > BM && N > 128 && !narrow;
@@ -332,9 +341,9 @@ extern "C" int emk_linear_bf16_qknorm_rope(emk_handle_t h, const void* x, const 
   return emk_gemm_bf16_fused(h, &d, stream);
 }
 
-extern "C" int emk_gemm_bf16_fused(emk_handle_t h, const emk_gemm_desc_t* d, emk_stream_t stream) {
+namespace {
+int gemm_fused_impl(emk_handle_t h, const emk_gemm_desc_t* d, cudaStream_t s, GemmArgs* args_only) {
   if (!h || !d) return EMK_ERR_ARG;
-  cudaStream_t s = (cudaStream_t)stream;
   if (d->row_sumsq_in && (d->norm_dim <= 0 || d->norm_dim % 128 != 0)) {
     EMK_SET_ERR(h, "row_sumsq_in needs norm_dim > 0 and a multiple of 128 (one partial slot per 128 columns)");
     return EMK_ERR_ARG;
@@ -361,8 +370,19 @@ extern "C" int emk_gemm_bf16_fused(emk_handle_t h, const emk_gemm_desc_t* d, emk
     QkRopeArgs qk{d->q_norm_weight, d->k_norm_weight, d->rope_chunk_major, (int)S, (int)Hq, (int)Hkv, d->qk_eps,
                   d->positions};
     return gemm_dispatch(h, d->x, d->w, nullptr, nullptr, d->y, d->M, d->N, d->K, EMK_W_NK, EMK_EPI_NONE, s, &qk,
-                         any_rs ? &rs : nullptr);
+                         any_rs ? &rs : nullptr, false, nullptr, args_only);
   }
   return gemm_dispatch(h, d->x, d->w, d->residual, nullptr, d->y, d->M, d->N, d->K, d->wlayout, d->epilogue, s, nullptr,
-                       any_rs ? &rs : nullptr);
+                       any_rs ? &rs : nullptr, false, nullptr, args_only);
+}
+}  // namespace
+
+extern "C" int emk_gemm_bf16_fused(emk_handle_t h, const emk_gemm_desc_t* d, emk_stream_t stream) {
+  return gemm_fused_impl(h, d, (cudaStream_t)stream, nullptr);
+}
+
+// The kernel arguments emk_gemm_bf16_fused would launch with (same validation), for callers that schedule the tiles
+// themselves (the GEMM chain).
+int emk_gemm_desc_to_args(emk_handle_t h, const emk_gemm_desc_t* d, emk::GemmArgs* out) {
+  return gemm_fused_impl(h, d, nullptr, out);
 }

@@ -24,6 +24,8 @@ rows interleaved, cos/sin tables rounded to bf16 as the eager module does.
 
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass
 
 import torch
@@ -71,13 +73,25 @@ def rope_tables(seq: int, head_dim: int, theta: float, device) -> tuple[torch.Te
     return cos, sin
 
 
+#: a rank with at most this many token rows runs the projections between two attention launches as one GEMM chain
+#: (``emk_gemm_bf16_chain``): measured faster up to 16384 rows, 1-2 % slower at 32768
+CHAIN_MAX_TOKENS = 16384
+
+
 def launch_names(num_layers: int, fold_rmsnorm: bool = True, hidden_states: bool = False,
-                 pool: bool = True) -> list[tuple[str, str]]:
+                 pool: bool = True, chain: bool = False) -> list[tuple[str, str]]:
     """``(kernel name, C-ABI entry)`` of every launch of one chunk of the plan, in order — what
     :meth:`EmbedForward.launch_list` launches, computable without a device (the backend shim lists a compiled trunk
-    with it)."""
+    with it). ``chain``: o_proj, gate/up, down and the next layer's QKV projection as one launch."""
     L: list[tuple[str, str]] = []
-    if fold_rmsnorm:
+    if fold_rmsnorm and chain:
+        L.append(("k_embed_gather_sumsq", "emk_embed_gather_sumsq"))
+        L.append(("k_rmsnorm_linear_qkv_qknorm_rope_0", "emk_gemm_bf16_fused"))
+        for i in range(num_layers):
+            L.append((f"k_scaled_dot_product_attention_{i}", "emk_sdpa_causal_gqa_bf16_tok"))
+            tail = f"_qkv_{i + 1}" if i + 1 < num_layers else ""
+            L.append((f"k_linear_chain_o_proj_gate_up_down_{i}{tail}", "emk_gemm_bf16_chain"))
+    elif fold_rmsnorm:
         L.append(("k_embed_gather_sumsq", "emk_embed_gather_sumsq"))
         for i in range(num_layers):
             L += [(f"k_rmsnorm_linear_qkv_qknorm_rope_{i}", "emk_gemm_bf16_fused"),
@@ -185,12 +199,15 @@ class EmbedForward:
 
     @property
     def LAUNCHES_PER_LAYER(self) -> int:
+        if self.chain:
+            return 2
         return 5 if self.fold_rmsnorm else 7
 
     def __init__(self, cfg, state_dict: dict[str, torch.Tensor] | None = None, *, batch: int, seq: int, device=None,
                  chunk_seqs: int | None = None, fold_rmsnorm: bool = True, weights: EmbedWeights | None = None,
                  workspace: EmbedWorkspace | None = None, hidden_states: bool = False,
-                 rope: tuple[torch.Tensor, torch.Tensor] | None = None, pool: bool = True) -> None:
+                 rope: tuple[torch.Tensor, torch.Tensor] | None = None, pool: bool = True,
+                 chain: bool | None = None) -> None:
         if weights is None:
             if state_dict is None:
                 raise ValueError("give a state_dict or prepared weights")
@@ -232,6 +249,12 @@ class EmbedForward:
         self.qkv, self.attn, self.mlp = ws.qkv[:T], ws.attn[:T], ws.mlp[:T]
         self.out = ws.out[: self.batch]
         self.ss1, self.ss2 = ws.ss1[:T], ws.ss2[:T]
+        #: the GEMMs between two attention launches as one chained launch (None: by size; EMK_GEMM_CHAIN=0/1 forces)
+        if chain is None:
+            env = os.environ.get("EMK_GEMM_CHAIN")
+            chain = (env != "0") and (env == "1" or T <= CHAIN_MAX_TOKENS)
+        self.chain = bool(chain) and self.fold_rmsnorm
+        self.chain_ws = ops.gemm_chain_workspace(T, dev) if self.chain else None
         self._graph: torch.cuda.CUDAGraph | None = None
 
     # -----------------------------------------------------------------------------------------------------------
@@ -239,7 +262,7 @@ class EmbedForward:
     def num_launches(self) -> int:
         chunks = self.batch // self.chunk_seqs
         per_layer = self.LAUNCHES_PER_LAYER
-        return chunks * (per_layer * self.cfg.num_hidden_layers + self.LAUNCHES_FIXED)
+        return chunks * (per_layer * self.cfg.num_hidden_layers + self.LAUNCHES_FIXED + int(self.chain))
 
     def flops(self) -> int:
         return self.cfg.linear_flops_per_token() * self.batch * self.seq + self.cfg.attention_flops(self.batch,
@@ -258,7 +281,37 @@ class EmbedForward:
         def add(name: str, entry: str, fn) -> None:
             L.append((name, entry, fn))
 
-        if self.fold_rmsnorm:
+        def qkv_phase(lw) -> dict:
+            return dict(x=self.h, w=lw.wqkv, out=self.qkv, epilogue="qknorm_rope", row_sumsq_in=self.ss1, norm_dim=H,
+                        norm_eps=eps, q_weight=lw.qn, k_weight=lw.kn, rope_cm=self.rope_cm, S=S, Hq=nq, Hkv=nkv,
+                        qk_eps=eps)
+
+        def mlp_phases(lw) -> list[dict]:
+            return [dict(x=self.attn, w=lw.wo, out=self.h, epilogue="residual", residual=self.h,
+                         row_sumsq_out=self.ss2),
+                    dict(x=self.h, w=lw.wgu, out=self.mlp, epilogue="swiglu", row_sumsq_in=self.ss2, norm_dim=H,
+                         norm_eps=eps),
+                    dict(x=self.mlp, w=lw.wdown, out=self.h, epilogue="residual", residual=self.h,
+                         row_sumsq_out=self.ss1)]
+
+        if self.fold_rmsnorm and self.chain:
+            add("k_embed_gather_sumsq", "emk_embed_gather_sumsq",
+                lambda: ops.embed_gather(self.embed, ids, out=self.h, row_sumsq=self.ss1))
+            first = dict(qkv_phase(self.layers[0]))
+            add("k_rmsnorm_linear_qkv_qknorm_rope_0", "emk_gemm_bf16_fused",
+                lambda first=first: ops.gemm_fused(first["x"], first["w"], first["out"],
+                                                   **{k: v for k, v in first.items() if k not in ("x", "w", "out")}))
+            for i, lw in enumerate(self.layers):
+                add(f"k_scaled_dot_product_attention_{i}", "emk_sdpa_causal_gqa_bf16_tok",
+                    lambda: ops.sdpa_causal_gqa_tok(self.qkv, B, S, nq, nkv, self.attn))
+                phases = mlp_phases(lw)
+                tail = ""
+                if i + 1 < len(self.layers):
+                    phases.append(qkv_phase(self.layers[i + 1]))
+                    tail = f"_qkv_{i + 1}"
+                add(f"k_linear_chain_o_proj_gate_up_down_{i}{tail}", "emk_gemm_bf16_chain",
+                    lambda phases=phases: ops.gemm_chain(phases, self.chain_ws))
+        elif self.fold_rmsnorm:
             add("k_embed_gather_sumsq", "emk_embed_gather_sumsq",
                 lambda: ops.embed_gather(self.embed, ids, out=self.h, row_sumsq=self.ss1))
             for i, lw in enumerate(self.layers):
@@ -300,7 +353,7 @@ class EmbedForward:
             add("k_pool_norm_l2", "emk_pool_norm_l2",
                 lambda: ops.pool_norm_l2(self.h, self.final_norm, B, S, eps, out=out))
         assert [(n, e) for n, e, _ in L] == launch_names(c.num_hidden_layers, self.fold_rmsnorm, self.hidden_states,
-                                                         self.pool)
+                                                         self.pool, self.chain)
         return L
 
     def _forward_chunk(self, ids: torch.Tensor, out: torch.Tensor) -> None:
@@ -351,7 +404,8 @@ class PackedForward:
     token 0 and ignored."""
 
     def __init__(self, weights: EmbedWeights, *, tokens: int, max_seqs: int, max_seq_len: int,
-                 workspace: EmbedWorkspace | None = None, hidden_states: bool = True, pool: bool = True) -> None:
+                 workspace: EmbedWorkspace | None = None, hidden_states: bool = True, pool: bool = True,
+                 chain: bool | None = None) -> None:
         self.weights = weights
         self.cfg = c = weights.cfg
         if not weights.fold_rmsnorm:
@@ -376,11 +430,17 @@ class PackedForward:
         self.vl_ws = ops.sdpa_varlen_workspace(self.max_seqs, T, dev)
         cos, sin = rope_tables(self.max_seq_len, c.head_dim, c.rope_theta, dev)
         self.rope_cm = ops.rope_chunk_major(cos, sin)
+        if chain is None:   # as in EmbedForward
+            env = os.environ.get("EMK_GEMM_CHAIN")
+            chain = (env != "0") and (env == "1" or T <= CHAIN_MAX_TOKENS)
+        self.chain = bool(chain)
+        self.chain_ws = ops.gemm_chain_workspace(T, dev) if self.chain else None
         self._graph: torch.cuda.CUDAGraph | None = None
 
     @property
     def num_launches(self) -> int:
-        return 1 + 6 * self.cfg.num_hidden_layers + int(self.hidden_states) + int(self.pool)
+        per_layer = 3 if self.chain else 6   # the variable-length attention is two launches (item table + kernel)
+        return 1 + int(self.chain) + per_layer * self.cfg.num_hidden_layers + int(self.hidden_states) + int(self.pool)
 
     def set_batch(self, ids: torch.Tensor, positions: torch.Tensor, cu_seqlens: torch.Tensor) -> None:
         """Copy a packed batch into the static buffers: ``ids`` / ``positions`` ``(n,)`` with ``n <= tokens``,
@@ -401,16 +461,36 @@ class PackedForward:
         c = self.cfg
         nq, nkv, H, eps = c.num_attention_heads, c.num_key_value_heads, c.hidden_size, c.rms_norm_eps
         ops.embed_gather(self.weights.embed, self.ids, out=self.h, row_sumsq=self.ss1)
-        for lw in self.weights.layers:
-            ops.gemm_fused(self.h, lw.wqkv, self.qkv, epilogue="qknorm_rope", row_sumsq_in=self.ss1, norm_dim=H,
-                           norm_eps=eps, q_weight=lw.qn, k_weight=lw.kn, rope_cm=self.rope_cm, S=self.max_seq_len,
-                           Hq=nq, Hkv=nkv, qk_eps=eps, positions=self.positions)
+
+        def qkv_phase(lw) -> dict:
+            return dict(x=self.h, w=lw.wqkv, out=self.qkv, epilogue="qknorm_rope", row_sumsq_in=self.ss1, norm_dim=H,
+                        norm_eps=eps, q_weight=lw.qn, k_weight=lw.kn, rope_cm=self.rope_cm, S=self.max_seq_len,
+                        Hq=nq, Hkv=nkv, qk_eps=eps, positions=self.positions)
+
+        def run(ph: dict) -> None:
+            ops.gemm_fused(ph["x"], ph["w"], ph["out"], **{k: v for k, v in ph.items() if k not in ("x", "w", "out")})
+
+        layers = self.weights.layers
+        if self.chain:
+            run(qkv_phase(layers[0]))
+        for i, lw in enumerate(layers):
+            if not self.chain:
+                run(qkv_phase(lw))
             ops.sdpa_causal_gqa_varlen(self.qkv, self.cu_seqlens, self.max_seq_len, nq, nkv, self.attn,
                                        workspace=self.vl_ws)
-            ops.gemm_fused(self.attn, lw.wo, self.h, epilogue="residual", residual=self.h, row_sumsq_out=self.ss2)
-            ops.gemm_fused(self.h, lw.wgu, self.mlp, epilogue="swiglu", row_sumsq_in=self.ss2, norm_dim=H,
-                           norm_eps=eps)
-            ops.gemm_fused(self.mlp, lw.wdown, self.h, epilogue="residual", residual=self.h, row_sumsq_out=self.ss1)
+            phases = [dict(x=self.attn, w=lw.wo, out=self.h, epilogue="residual", residual=self.h,
+                           row_sumsq_out=self.ss2),
+                      dict(x=self.h, w=lw.wgu, out=self.mlp, epilogue="swiglu", row_sumsq_in=self.ss2, norm_dim=H,
+                           norm_eps=eps),
+                      dict(x=self.mlp, w=lw.wdown, out=self.h, epilogue="residual", residual=self.h,
+                           row_sumsq_out=self.ss1)]
+            if self.chain:
+                if i + 1 < len(layers):
+                    phases.append(qkv_phase(layers[i + 1]))
+                ops.gemm_chain(phases, self.chain_ws)
+            else:
+                for ph in phases:
+                    run(ph)
         if self.hidden_states:
             ops.rmsnorm(self.h, self.weights.final_norm, eps, out=self.hs)
         if self.pool:

@@ -181,15 +181,11 @@ def linear_qknorm_rope(x, w_qkv, q_weight, k_weight, rope_cm, S: int, Hq: int, H
     return y
 
 
-def gemm_fused(x, w, out, *, epilogue: str = "none", residual=None, w_is_kn: bool = False, row_sumsq_in=None,
+def _gemm_desc(x, w, out, *, epilogue: str = "none", residual=None, w_is_kn: bool = False, row_sumsq_in=None,
                norm_dim: int = 0, norm_eps: float = 1e-6, row_sumsq_out=None, q_weight=None,
                k_weight=None, rope_cm=None, S: int = 0, Hq: int = 0, Hkv: int = 0, qk_eps: float = 1e-6,
-               positions=None):
-    """``emk_gemm_bf16_fused``: the tcgen05 GEMM with an epilogue (``none | residual | bias | swiglu | qknorm_rope``)
-    and an RMSNorm folded around it through per-row partial sum-of-squares buffers ``[M, dim/128]`` fp32 (see
-    ``emk_gemm_desc_t``)."""
-    import ctypes as _ct
-
+               positions=None) -> "cabi.GemmDesc":
+    """Checks the tensors of one fused GEMM and fills its ``emk_gemm_desc_t``."""
     _check_cuda_contig(x, w, out, residual, row_sumsq_in, row_sumsq_out, q_weight, k_weight, rope_cm)
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise TypeError("gemm_fused expects bfloat16 operands")
@@ -225,9 +221,49 @@ def gemm_fused(x, w, out, *, epilogue: str = "none", residual=None, w_is_kn: boo
         _check_cuda_contig(positions)
         _check_buffer("positions", positions, M, torch.int32)
         d.positions = positions.data_ptr()
+    return d
+
+
+def gemm_fused(x, w, out, **kw):
+    """``emk_gemm_bf16_fused``: the tcgen05 GEMM with an epilogue (``none | residual | bias | swiglu | qknorm_rope``)
+    and an RMSNorm folded around it through per-row partial sum-of-squares buffers ``[M, dim/128]`` fp32 (see
+    ``emk_gemm_desc_t``). Keywords: ``epilogue, residual, w_is_kn, row_sumsq_in, norm_dim, norm_eps, row_sumsq_out,
+    q_weight, k_weight, rope_cm, S, Hq, Hkv, qk_eps, positions``."""
+    import ctypes as _ct
+
+    d = _gemm_desc(x, w, out, **kw)
     h = handle()
     h.check(h.lib.emk_gemm_bf16_fused(h.ptr, _ct.byref(d), _stream()), "emk_gemm_bf16_fused")
     return out
+
+
+def gemm_chain_workspace(M: int, device) -> torch.Tensor:
+    """Zeroed counter workspace for :func:`gemm_chain` over ``M`` rows. One workspace serves any number of chain
+    launches that follow each other on a stream (every completed launch leaves it zero)."""
+    h = handle()
+    n = int(h.lib.emk_gemm_bf16_chain_workspace_bytes(int(M)))
+    return torch.zeros((n + 3) // 4, dtype=torch.int32, device=device)
+
+
+def gemm_chain(phases: list[dict], workspace: torch.Tensor):
+    """``emk_gemm_bf16_chain``: 1 to 4 fused GEMMs, each reading the output of the one before it, as one persistent
+    launch. ``phases`` are keyword dicts of :func:`gemm_fused` with ``x``, ``w`` and ``out`` entries. Returns the last
+    phase's output."""
+    import ctypes as _ct
+
+    if not phases:
+        raise ValueError("gemm_chain needs at least one phase")
+    descs = (cabi.GemmDesc * len(phases))()
+    for i, ph in enumerate(phases):
+        kw = dict(ph)
+        descs[i] = _gemm_desc(kw.pop("x"), kw.pop("w"), kw.pop("out"), **kw)
+    _check_cuda_contig(workspace)
+    if workspace.dtype != torch.int32:
+        raise TypeError("gemm_chain workspace must be int32")
+    h = handle()
+    h.check(h.lib.emk_gemm_bf16_chain(h.ptr, descs, len(phases), workspace.data_ptr(),
+                                      workspace.numel() * 4, _stream()), "emk_gemm_bf16_chain")
+    return phases[-1]["out"]
 
 
 def linear_residual_rmsnorm_noalloc(x, w, residual, norm_weight, eps: float = 1e-6, out_hidden=None, out_norm=None):

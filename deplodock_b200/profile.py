@@ -65,7 +65,7 @@ REF_ROWS_MAX = 12
 #: by this list. ``tests/test_profile_cli.py`` checks it against the ``__global__`` definitions under ``csrc/``.
 OWN_KERNELS = frozenset({
     "elementwise_kernel", "embed_gather_kernel", "emk_wait_expiry_kernel", "expand_e4m3_bf16_kernel",
-    "fmha_causal_kernel", "gemm2_bf16_kernel", "gemm_bf16_kernel", "gemm_f32_simt_kernel", "gemm_f32_tiled_kernel",
+    "fmha_causal_kernel", "gemm2_bf16_kernel", "gemm2_chain_kernel", "gemm_bf16_kernel", "gemm_f32_simt_kernel", "gemm_f32_tiled_kernel",
     "gemm_simt_kernel", "gemm_w8_kernel", "loop_linear_f32_kernel", "loop_rope_scores_f32_kernel",
     "loop_softmax_pv_f32_kernel", "pool_norm_l2_kernel", "qknorm_rope_kernel", "rmsnorm_cta_kernel",
     "rmsnorm_from_partials_kernel", "rmsnorm_generic_kernel", "rmsnorm_warp_kernel", "sdpa_simt_kernel",

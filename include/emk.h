@@ -174,6 +174,21 @@ typedef struct {
 } emk_gemm_desc_t;
 int emk_gemm_bf16_fused(emk_handle_t h, const emk_gemm_desc_t* desc, emk_stream_t stream);
 
+/* A chain of 1 to 4 GEMMs of emk_gemm_bf16_fused, each reading as x the y of the one before it (descs[p].x ==
+ * descs[p-1].y, K == its columns), run as ONE persistent launch: the 256x256 tiles of all phases form one list that
+ * the CTA pairs walk together, a tile waiting only for the 256-row block of its input to be final (a device-side
+ * counter per phase and row block), so the launches, pipeline fills, exposed last epilogues and partial last waves of
+ * separate calls disappear — the o_proj -> gate/up -> down -> next-layer QKV sequence of a decoder layer, whose
+ * counterpart in the reference is four separately launched k_linear_* kernels. Every phase: the same M, W [N,K]
+ * (EMK_W_NK), N > 128. Besides its x, a phase may read (residual, row_sumsq_in) only what an EARLIER phase of the chain
+ * wrote or what the chain does not write; y may alias the phase's own residual.
+ * `workspace` (emk_gemm_bf16_chain_workspace_bytes(M) bytes, 16-byte aligned, device memory) holds the counters: it
+ * must be zero before the first launch, and every launch that completes leaves it zero again (after
+ * EMK_ERR_TIMEOUT the caller zeroes it). Launches that share a workspace must not overlap. */
+int64_t emk_gemm_bf16_chain_workspace_bytes(int64_t M);
+int emk_gemm_bf16_chain(emk_handle_t h, const emk_gemm_desc_t* descs, int n, void* workspace, int64_t workspace_bytes,
+                        emk_stream_t stream);
+
 /* y_hidden = bf16(bf16(x·Wᵀ) + residual) [M,N] and y_norm = RMSNorm(y_hidden; norm_weight, eps) [M,N], W [N,K], all
  * bf16 — the "projection + residual, then norm" step of a decoder layer in one call that allocates NOTHING: the
  * scratch between its two kernels (partial row sums of squares) is a fixed 4 MiB array inside the library, held by
