@@ -54,7 +54,7 @@ extern "C" int emk_create(int device, emk_handle_t* out) {
   const char* ovl = getenv("EMK_OVERLAP_LAUNCH");
   h->overlap_launch = (ovl && atoi(ovl) == 0) ? 0 : 1;
   const char* cgm = getenv("EMK_CHAIN_GROUP_M");
-  h->chain_group_m = (cgm && atoi(cgm) > 0) ? atoi(cgm) : 4;
+  h->chain_group_m = (cgm && atoi(cgm) > 0) ? atoi(cgm) : 2;
   cudaError_t e = cudaSetDevice(device);
   if (e != cudaSuccess) {
     free(h);

@@ -311,9 +311,9 @@ gemm2_chain_kernel(const __grid_constant__ ChainParams P) {
         int p, tm, tn;
         chain_locate(P, t, p, tm, tn);
         if (p + 1 < P.n) {
-          // The epilogue warps' stores were acquired through the barrier; this fence makes them visible at gpu scope
-          // before the counter moves (fences are cumulative), and it is this thread that waits for them, not they.
-          __threadfence();
+          // The epilogue warps' stores were acquired through the barrier; the releasing reduction makes them visible
+          // at gpu scope before the counter moves (release is cumulative), and it is this thread that waits for
+          // them, not they. (A separate fence in front of it cost 1-2 % and adds nothing.)
           asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(P.done + p * P.row_blocks + tm) : "memory");
         }
         mbar_arrive(&bars->sig_done[acc]);
