@@ -426,7 +426,43 @@ def kernel_cases() -> dict:
             return fn, "fma", flops, 1e12, "f32_tflops_nominal", note, 20
         return build
 
+    def layer_gemms(M, chained):
+        """The four projections between two attention launches of the model plan (o_proj + residual, gate/up SwiGLU,
+        down + residual, next layer's QKV with q/k-norm + RoPE) at one rank's rows: as one chained launch or as four."""
+        def build():
+            from deplodock_b200.model import rope_tables
+
+            g = gen()
+            r = lambda *sh, sc=1.0: (sc * torch.randn(*sh, device=dev, generator=g)).bfloat16()  # noqa: E731
+            attn, h = r(M, 2048), r(M, 1024)
+            wo, wgu, wd, wqkv = r(1024, 2048, sc=0.02), r(6144, 1024, sc=0.05), r(1024, 3072, sc=0.02), r(4096, 1024, sc=0.03)
+            mlp = torch.empty(M, 3072, device=dev, dtype=torch.bfloat16)
+            qkv = torch.empty(M, 4096, device=dev, dtype=torch.bfloat16)
+            ss2, ss3 = torch.empty(M, 8, device=dev), torch.empty(M, 8, device=dev)
+            qn = torch.ones(128, device=dev, dtype=torch.bfloat16)
+            cm = ops.rope_chunk_major(*rope_tables(512, 128, 1e6, dev))
+            phases = [dict(x=attn, w=wo, out=h, epilogue="residual", residual=h, row_sumsq_out=ss2),
+                      dict(x=h, w=wgu, out=mlp, epilogue="swiglu", row_sumsq_in=ss2, norm_dim=1024),
+                      dict(x=mlp, w=wd, out=h, epilogue="residual", residual=h, row_sumsq_out=ss3),
+                      dict(x=h, w=wqkv, out=qkv, epilogue="qknorm_rope", row_sumsq_in=ss3, norm_dim=1024, q_weight=qn,
+                           k_weight=qn, rope_cm=cm, S=512, Hq=16, Hkv=8)]
+            flops = 2 * M * (1024 * 2048 + 6144 * 1024 + 1024 * 3072 + 4096 * 1024)
+            if chained:
+                ws = ops.gemm_chain_workspace(M, dev)
+                fn = lambda: ops.gemm_chain(phases, ws)  # noqa: E731
+                note = "one persistent launch, tiles of a phase wait for their 256-row block of the phase before"
+            else:
+                def fn():
+                    for ph in phases:
+                        ops.gemm_fused(ph["x"], ph["w"], ph["out"],
+                                       **{k: v for k, v in ph.items() if k not in ("x", "w", "out")})
+                note = "four launches (the time is of all four)"
+            return fn, "tensor", flops, 1e12, "bf16_tflops", note + "; burst peak", 10
+        return build
+
     return {
+        "k_linear chain o_proj>gate_up>down>qkv 4096 rows (8-GPU shard), one launch": layer_gemms(4096, True),
+        "k_linear o_proj, gate_up, down, qkv 4096 rows (8-GPU shard), four launches": layer_gemms(4096, False),
         "k_matmul f32 512x1024x2048 (q_proj s512)": matmul_f32(512, 1024, 2048),
         "k_matmul f32 128x1024x2048 (q_proj s128)": matmul_f32(128, 1024, 2048),
         "k_matmul f32 32x1024x2048 (q_proj s32)": matmul_f32(32, 1024, 2048),

@@ -111,8 +111,13 @@ __device__ __forceinline__ float epilogue_store32(const GemmArgs& g, const uint3
   }
   const bool full = g.wide && (col0 + 32 <= g.N);
   float v[32];
+  if (g.ss_in != nullptr) {   // the row scale of a folded RMSNorm; without one rs is 1 and the multiplies are skipped
 #pragma unroll
-  for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(r[e]) * rs;
+    for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(r[e]) * rs;
+  } else {
+#pragma unroll
+    for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(r[e]);
+  }
   if (g.scale != nullptr) {
 #pragma unroll
     for (int q = 0; q < 8; ++q) {

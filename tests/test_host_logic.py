@@ -448,3 +448,16 @@ def test_backend_subclasses_the_reference_base_when_it_is_importable():
     assert not backend.USES_REFERENCE_TYPES   # and stand-alone it defines the same types itself
     assert [f for f in backend.BenchmarkResult.__dataclass_fields__] == [
         "time_ms", "min_ms", "max_ms", "num_launches", "per_launch", "captured", "e2e_ms", "e2e_min_ms"]
+
+
+def test_launch_names_of_the_chained_plan():
+    """With the GEMM chain the plan is: gather, the first layer's QKV, then attention + one chain per layer (the
+    chain of the last layer has no next QKV)."""
+    from deplodock_b200.model import launch_names
+
+    names = launch_names(3, chain=True)
+    assert [e for _, e in names] == ["emk_embed_gather_sumsq", "emk_gemm_bf16_fused"] + [
+        "emk_sdpa_causal_gqa_bf16_tok", "emk_gemm_bf16_chain"] * 3 + ["emk_pool_norm_l2"]
+    assert names[3][0] == "k_linear_chain_o_proj_gate_up_down_0_qkv_1"
+    assert names[-2][0] == "k_linear_chain_o_proj_gate_up_down_2"
+    assert len(launch_names(3, chain=False)) == 1 + 5 * 3 + 1
