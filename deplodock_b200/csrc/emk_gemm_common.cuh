@@ -257,7 +257,10 @@ __device__ __forceinline__ void epilogue_head_qknorm_rope(const GemmArgs& g, uin
     }
     return;
   }
-  // ---- sweep 1: sum of squares of the bf16-rounded row ----
+  // ---- sweep 1: sum of squares of the bf16-rounded row; the rounded pairs go back into tensor memory ----
+  // Chunk c (32 fp32 columns) becomes 16 packed bf16 pairs, written over columns [16c, 16c+16) of the head's own
+  // accumulator region: those columns were read by this or an earlier chunk, and the chunk in flight lies above them.
+  // Sweep 2 then reads the packed pairs and does not round the accumulator a second time.
   float ss0 = 0.f, ss1 = 0.f, ss2 = 0.f, ss3 = 0.f;
   {
     uint32_t v[2][32];
@@ -266,17 +269,22 @@ __device__ __forceinline__ void epilogue_head_qknorm_rope(const GemmArgs& g, uin
     for (int c = 0; c < 4; ++c) {
       tmem_ld_wait_regs(v[c & 1]);
       if (c + 1 < 4) tmem_ld_x32(taddr + (uint32_t)((c + 1) * 32), v[(c + 1) & 1]);
+      uint32_t pk[16];
 #pragma unroll
       for (int i = 0; i < 16; i += 2) {
         const uint32_t pa = pack_bf16x2(__uint_as_float(v[c & 1][2 * i]) * rs, __uint_as_float(v[c & 1][2 * i + 1]) * rs);
         const uint32_t pb = pack_bf16x2(__uint_as_float(v[c & 1][2 * i + 2]) * rs, __uint_as_float(v[c & 1][2 * i + 3]) * rs);
+        pk[i] = pa;
+        pk[i + 1] = pb;
         const float a0 = bf16_lo(pa), a1 = bf16_hi(pa), b0 = bf16_lo(pb), b1 = bf16_hi(pb);
         ss0 = fmaf(a0, a0, ss0);
         ss1 = fmaf(a1, a1, ss1);
         ss2 = fmaf(b0, b0, ss2);
         ss3 = fmaf(b1, b1, ss3);
       }
+      tmem_st_x16(taddr + (uint32_t)(c * 16), pk);
     }
+    tmem_st_wait();
   }
   const float r = 1.0f / sqrtf(((ss0 + ss1) + (ss2 + ss3)) * (1.0f / 128.0f) + g.qk_eps);
   const __nv_bfloat16* wp = head < g.qk_Hq ? g.qk_qw : g.qk_kw;
@@ -284,10 +292,11 @@ __device__ __forceinline__ void epilogue_head_qknorm_rope(const GemmArgs& g, uin
   // cos[i] == cos[i + 64] so the first 64 elements suffice). The lanes of a warp are consecutive rows, hence
   // consecutive positions, so each of these loads is one contiguous kilobyte per warp.
   const __nv_bfloat16* tp = g.qk_rope + (int64_t)(valid ? rope_position(g, row) : 0) * 16;
-  // ---- sweep 2: 16 columns [16t, 16t+16) and their partners [64+16t, 64+16t+16) per step ----
-  uint32_t lo[2][16], hi[2][16];
-  tmem_ld_x16(taddr, lo[0]);
-  tmem_ld_x16(taddr + 64u, hi[0]);
+  // ---- sweep 2: 16 elements [16t, 16t+16) and their partners [64+16t, 64+16t+16) per step, as packed pairs:
+  //      words [8t, 8t+8) and [32+8t, 32+8t+8) of the region written above ----
+  uint32_t lo[2][8], hi[2][8];
+  tmem_ld_x8(taddr, lo[0]);
+  tmem_ld_x8(taddr + 32u, hi[0]);
 #pragma unroll
   for (int t = 0; t < 4; ++t) {
     uint32_t cs[2][8];
@@ -299,16 +308,16 @@ __device__ __forceinline__ void epilogue_head_qknorm_rope(const GemmArgs& g, uin
     const uint4 wh1 = __ldg(reinterpret_cast<const uint4*>(wp + 64 + 16 * t + 8));
     const uint32_t wlo[8] = {wl0.x, wl0.y, wl0.z, wl0.w, wl1.x, wl1.y, wl1.z, wl1.w};
     const uint32_t whi[8] = {wh0.x, wh0.y, wh0.z, wh0.w, wh1.x, wh1.y, wh1.z, wh1.w};
-    tmem_ld_wait_regs16x2(lo[t & 1], hi[t & 1]);
+    tmem_ld_wait_regs8x2(lo[t & 1], hi[t & 1]);
     if (t + 1 < 4) {
-      tmem_ld_x16(taddr + (uint32_t)((t + 1) * 16), lo[(t + 1) & 1]);
-      tmem_ld_x16(taddr + 64u + (uint32_t)((t + 1) * 16), hi[(t + 1) & 1]);
+      tmem_ld_x8(taddr + (uint32_t)((t + 1) * 8), lo[(t + 1) & 1]);
+      tmem_ld_x8(taddr + 32u + (uint32_t)((t + 1) * 8), hi[(t + 1) & 1]);
     }
     uint32_t olo[8], ohi[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {   // pair j of this step: elements 16t + 2j, 16t + 2j + 1 and their partners
-      const uint32_t pl = pack_bf16x2(__uint_as_float(lo[t & 1][2 * j]) * rs, __uint_as_float(lo[t & 1][2 * j + 1]) * rs);
-      const uint32_t ph = pack_bf16x2(__uint_as_float(hi[t & 1][2 * j]) * rs, __uint_as_float(hi[t & 1][2 * j + 1]) * rs);
+      const uint32_t pl = lo[t & 1][j];
+      const uint32_t ph = hi[t & 1][j];
       const __nv_bfloat162 nl = __floats2bfloat162_rn(bf16_lo(pl) * r, bf16_hi(pl) * r);
       const __nv_bfloat162 nh = __floats2bfloat162_rn(bf16_lo(ph) * r, bf16_hi(ph) * r);
       const __nv_bfloat162 xl = __hmul2_rn(*reinterpret_cast<const __nv_bfloat162*>(&wlo[j]), nl);
