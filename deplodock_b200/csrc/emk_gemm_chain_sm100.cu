@@ -25,9 +25,13 @@
 // last CTA to leave the kernel zeroes them again, so launches (and CUDA-graph replays) can follow each other without
 // host work. No load uses cluster multicast.
 //
-// Measured on the four projections of a Qwen3-0.6B layer (o_proj, gate/up, down, next QKV): 4096 rows 129 -> 120 us,
-// 8192 rows 235 -> 208 us, 16384 rows 440 -> 425 us; at 32768 rows the separate launches are 1-2 % faster (nothing
-// left to hide, and the tracking costs a little), which is where the caller should stop chaining.
+// Measured on the four projections of a Qwen3-0.6B layer (o_proj, gate/up, down, next QKV), chains launched back to
+// back: 4096 rows 129 -> 120 us, 8192 rows 235 -> 208 us, 16384 rows 440 -> 425 us at the power-capped clock (at the
+// burst clock 109 -> 105 us at 4096 rows); at 32768 rows the separate launches are 1-2 % faster (nothing left to hide,
+// and the tracking costs a little). Inside the model, where an attention launch sits between two chains, the whole
+// forward gains 1.5 % at 8192 rows, 1.8-3.3 % at 8192-16384 rows per rank in the multi-GPU bench, and LOSES 2-3 % at
+// 4096 rows: the caller chains between 8192 and 16384 rows only. Asking every phase's weights into L2 at kernel start
+// (cp.async.bulk.prefetch) changed nothing.
 #include "emk_gemm_common.cuh"
 
 int emk_gemm_desc_to_args(emk_handle_t h, const emk_gemm_desc_t* d, emk::GemmArgs* out);

@@ -73,8 +73,10 @@ def rope_tables(seq: int, head_dim: int, theta: float, device) -> tuple[torch.Te
     return cos, sin
 
 
-#: a rank with at most this many token rows runs the projections between two attention launches as one GEMM chain
-#: (``emk_gemm_bf16_chain``): measured faster up to 16384 rows, 1-2 % slower at 32768
+#: a rank with this many token rows runs the projections between two attention launches as one GEMM chain
+#: (``emk_gemm_bf16_chain``): the whole forward measured 1.5-3 % faster at 8192 and 16384 rows, 2-3 % slower at 4096
+#: (the chain's dependency latencies outweigh the launches it saves) and 1-2 % slower at 32768 (nothing left to hide)
+CHAIN_MIN_TOKENS = 8192
 CHAIN_MAX_TOKENS = 16384
 
 
@@ -252,7 +254,7 @@ class EmbedForward:
         #: the GEMMs between two attention launches as one chained launch (None: by size; EMK_GEMM_CHAIN=0/1 forces)
         if chain is None:
             env = os.environ.get("EMK_GEMM_CHAIN")
-            chain = (env != "0") and (env == "1" or T <= CHAIN_MAX_TOKENS)
+            chain = (env != "0") and (env == "1" or CHAIN_MIN_TOKENS <= T <= CHAIN_MAX_TOKENS)
         self.chain = bool(chain) and self.fold_rmsnorm
         self.chain_ws = ops.gemm_chain_workspace(T, dev) if self.chain else None
         self._graph: torch.cuda.CUDAGraph | None = None
@@ -432,7 +434,7 @@ class PackedForward:
         self.rope_cm = ops.rope_chunk_major(cos, sin)
         if chain is None:   # as in EmbedForward
             env = os.environ.get("EMK_GEMM_CHAIN")
-            chain = (env != "0") and (env == "1" or T <= CHAIN_MAX_TOKENS)
+            chain = (env != "0") and (env == "1" or CHAIN_MIN_TOKENS <= T <= CHAIN_MAX_TOKENS)
         self.chain = bool(chain)
         self.chain_ws = ops.gemm_chain_workspace(T, dev) if self.chain else None
         self._graph: torch.cuda.CUDAGraph | None = None
