@@ -36,7 +36,8 @@ struct __align__(8) G2Barriers {
 
 // G2_BN: tile width (256 or 128 columns; each CTA loads half of them). A ring stage holds KSUB 64-wide K slices:
 // KSUB x (16 KB of A + G2_BN/2 rows of W).
-template <int G2_BN, int G2_STAGES, int WL, int KSUB>
+// EPI: the one epilogue this instantiation carries (EMK_EPI_*), or -1 for all of them chosen by the launch argument.
+template <int G2_BN, int G2_STAGES, int WL, int KSUB, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2_THREADS, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                   const GemmArgs g) {
@@ -194,12 +195,12 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       tile_coords(tile, g.tiles_m, g.tiles_n, G2_GROUP_M, tm, tn);
       const int row = tm * 2 * BM + (int)rank * BM + quarter * 32 + lane;
       const int n0 = tn * G2_BN + half * (G2_BN / 2);
-      epilogue_prefetch(g, row, n0, G2_BN / 2);
+      epilogue_prefetch<EPI>(g, row, n0, G2_BN / 2);
       if (!mbar_wait_warp(&bars->tmem_full[acc], acc_phase, wc, EMK_DEV_TIMEOUT_EPILOGUE)) break;
       tc_fence_after();
       const uint32_t taddr =
           tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * G2_BN + half * (G2_BN / 2));
-      epilogue_drain<G2_BN / 64>(g, taddr, row, n0);
+      epilogue_drain<G2_BN / 64, EPI>(g, taddr, row, n0);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster_relaxed(mapa_u32(smem_u32(&bars->tmem_empty[acc]), 0));
@@ -214,12 +215,12 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
   if (warp == 0) tmem_dealloc_pair(tmem_base, G2_TMEM_COLS);
 }
 
-template <int G2_BN, int G2_STAGES, int WL, int KSUB>
+template <int G2_BN, int G2_STAGES, int WL, int KSUB, int EPI = -1>
 int launch_gemm2(emk_handle_t h, const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, cudaStream_t s) {
   constexpr int G2_SMEM = G2_STAGES * KSUB * (A_STAGE_BYTES + (G2_BN / 2) * BK * 2) + 1024 + (int)sizeof(G2Barriers);
   static emk_device_once once;
   static int max_pairs[EMK_MAX_DEVICES] = {0};
-  auto kern = gemm2_bf16_kernel<G2_BN, G2_STAGES, WL, KSUB>;
+  auto kern = gemm2_bf16_kernel<G2_BN, G2_STAGES, WL, KSUB, EPI>;
   const int d = h->device;   // emk_create admits ordinals below EMK_MAX_DEVICES only
   std::unique_lock<std::mutex> lk(once.mu);
   if (!once.done[d]) {
@@ -271,7 +272,16 @@ int emk_gemm2_launch(emk_handle_t h, const void* x, const void* w, emk::GemmArgs
                           (uint64_t)g.K * 2, BK, (uint32_t)(bn / 2), CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != EMK_OK) return rc;
     // two 64-wide K slices per ring stage: the per-stage barrier/commit work of the MMA thread is paid half as often
-    if (bn == 256) return launch_gemm2<256, 3, 0, 2>(h, ta, tb, g, s);
+    if (bn == 256) {
+      // the epilogues of the model path each have a kernel of their own (smaller code: see epi_of)
+      switch (g.epi) {
+        case EMK_EPI_NONE: return launch_gemm2<256, 3, 0, 2, EMK_EPI_NONE>(h, ta, tb, g, s);
+        case EMK_EPI_RESIDUAL: return launch_gemm2<256, 3, 0, 2, EMK_EPI_RESIDUAL>(h, ta, tb, g, s);
+        case EMK_EPI_SWIGLU: return launch_gemm2<256, 3, 0, 2, EMK_EPI_SWIGLU>(h, ta, tb, g, s);
+        case EMK_EPI_QKNORM_ROPE_INTERNAL: return launch_gemm2<256, 3, 0, 2, EMK_EPI_QKNORM_ROPE_INTERNAL>(h, ta, tb, g, s);
+        default: return launch_gemm2<256, 3, 0, 2>(h, ta, tb, g, s);
+      }
+    }
     return launch_gemm2<128, 4, 0, 2>(h, ta, tb, g, s);
   }
   rc = emk_make_tmap_2d(h, &tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.N * 2,

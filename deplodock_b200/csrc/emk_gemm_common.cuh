@@ -61,15 +61,25 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   tn = in_group / gsize;
 }
 
+// The epilogue kind of a kernel instantiation: a compile-time constant where the kernel was built for one epilogue
+// (its code then holds only that epilogue), the launch argument where it was built for all of them (EPI < 0).
+// A GEMM kernel that carries every epilogue is large enough to push the attention kernel out of the instruction
+// cache and back at every switch between the two (measured: about 7 us per switch, two switches per decoder layer).
+template <int EPI>
+__device__ __forceinline__ int epi_of(const GemmArgs& g) {
+  return EPI < 0 ? g.epi : EPI;
+}
+
 // silu(g) = g / (1 + exp(-g)) with the approximate reciprocal (2 ulp): the result is rounded to bf16 right after, and
 // the IEEE division's slow path made the SwiGLU epilogue longer than the main loop of a K = 1024 tile.
 __device__ __forceinline__ float silu_f(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
 
 // Epilogue for 32 accumulator columns [col0, col0+32) of one output row held by this thread. `g.wide` says rows of
 // y (and of the residual) are 32-byte aligned, so full 32-column groups move as 256-bit accesses.
+template <int EPI>
 __device__ __forceinline__ float epilogue_store32(const GemmArgs& g, const uint32_t* r, int row, int col0, float rs) {
   if (row >= g.M || col0 >= g.N) return 0.f;
-  if (g.epi == EMK_EPI_SWIGLU) {
+  if (epi_of<EPI>(g) == EMK_EPI_SWIGLU) {
     // columns are (gate, up) pairs; 16 outputs = 32 bytes
     __nv_bfloat16* out = g.y + (int64_t)row * g.ldy + (col0 >> 1);
     uint32_t o[8];
@@ -93,7 +103,7 @@ __device__ __forceinline__ float epilogue_store32(const GemmArgs& g, const uint3
     }
     return 0.f;
   }
-  if (g.epi == EMK_EPI_F32_INTERNAL) {
+  if (epi_of<EPI>(g) == EMK_EPI_F32_INTERNAL) {
     float* out = reinterpret_cast<float*>(g.y) + (int64_t)row * g.ldy + col0;
 #pragma unroll
     for (int q = 0; q < 8; ++q) {
@@ -127,7 +137,7 @@ __device__ __forceinline__ float epilogue_store32(const GemmArgs& g, const uint3
       }
     }
   }
-  if (g.epi == EMK_EPI_RESIDUAL) {
+  if (epi_of<EPI>(g) == EMK_EPI_RESIDUAL) {
     const __nv_bfloat16* res = g.residual + (int64_t)row * g.ldy + col0;
     uint32_t rr[16];
     if (full) {
@@ -151,7 +161,7 @@ __device__ __forceinline__ float epilogue_store32(const GemmArgs& g, const uint3
       v[2 * e] = bf16_round(v[2 * e]) + bf16_lo(rr[e]);
       v[2 * e + 1] = bf16_round(v[2 * e + 1]) + bf16_hi(rr[e]);
     }
-  } else if (g.epi == EMK_EPI_BIAS) {
+  } else if (epi_of<EPI>(g) == EMK_EPI_BIAS) {
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       if (col0 + q * 8 < g.N) {
@@ -205,18 +215,19 @@ __device__ __forceinline__ int rope_position(const GemmArgs& g, int row) {
 // Issued by an epilogue thread BEFORE it waits for its accumulator: everything the epilogue will read from global
 // memory for this row segment is pulled towards the SM while the tensor core is still working on the tile, so the
 // epilogue (two warps per scheduler, little latency hiding of its own) finds it in L1 / L2.
+template <int EPI = -1>
 __device__ __forceinline__ void epilogue_prefetch(const GemmArgs& g, int row, int n0, int ncols) {
   if (row >= g.M || n0 >= g.N) return;
   if (g.ss_in != nullptr && !g.coherent) {
     asm volatile("prefetch.global.L1 [%0];" ::"l"(g.ss_in + (int64_t)row * g.ss_in_segs));
   }
-  if (g.epi == EMK_EPI_QKNORM_ROPE_INTERNAL) {
+  if (epi_of<EPI>(g) == EMK_EPI_QKNORM_ROPE_INTERNAL) {
     if ((n0 >> 7) < g.qk_Hq + g.qk_Hkv) {
       const __nv_bfloat16* tp = g.qk_rope + (int64_t)rope_position(g, row) * 16;
 #pragma unroll
       for (int q = 0; q < 8; ++q) asm volatile("prefetch.global.L1 [%0];" ::"l"(tp + (int64_t)q * g.qk_S * 16));
     }
-  } else if (g.epi == EMK_EPI_RESIDUAL) {
+  } else if (epi_of<EPI>(g) == EMK_EPI_RESIDUAL) {
     const __nv_bfloat16* res = g.residual + (int64_t)row * g.ldy + n0;
     for (int c = 0; c < ncols; c += 64) asm volatile("prefetch.global.L2 [%0];" ::"l"(res + c));
   }
@@ -341,7 +352,7 @@ __device__ __forceinline__ void epilogue_head_qknorm_rope(const GemmArgs& g, uin
 
 // Drains one accumulator (NCHUNK x 32 columns of this thread's row) from tensor memory through the epilogue. The load
 // of chunk c+1 is in flight while chunk c is converted and stored.
-template <int NCHUNK>
+template <int NCHUNK, int EPI = -1>
 __device__ __forceinline__ void epilogue_drain(const GemmArgs& g, uint32_t taddr, int row, int n0) {
   // row scale of a folded RMSNorm on the input side (1 when there is none)
   float rs = 1.0f;
@@ -359,7 +370,7 @@ __device__ __forceinline__ void epilogue_drain(const GemmArgs& g, uint32_t taddr
     }
     rs = 1.0f / sqrtf(tot * g.ss_inv_dim + g.ss_eps);
   }
-  if (g.epi == EMK_EPI_QKNORM_ROPE_INTERNAL) {
+  if (epi_of<EPI>(g) == EMK_EPI_QKNORM_ROPE_INTERNAL) {
 #pragma unroll 1
     for (int hd = 0; hd < NCHUNK / 4; ++hd)
       epilogue_head_qknorm_rope(g, taddr + (uint32_t)(hd * 128), row, n0 + hd * 128, rs);
@@ -372,7 +383,7 @@ __device__ __forceinline__ void epilogue_drain(const GemmArgs& g, uint32_t taddr
   for (int c = 0; c < NCHUNK; ++c) {
     tmem_ld_wait_regs(r[c & 1]);
     if (c + 1 < NCHUNK) tmem_ld_x32(taddr + (uint32_t)((c + 1) * 32), r[(c + 1) & 1]);
-    ss += epilogue_store32(g, r[c & 1], row, n0 + c * 32, rs);
+    ss += epilogue_store32<EPI>(g, r[c & 1], row, n0 + c * 32, rs);
   }
   if (g.ss_out != nullptr && row < g.M) {
     // this thread owns columns [n0, n0 + 32*NCHUNK): its total goes to the first 128-column slot it covers, zeros to
