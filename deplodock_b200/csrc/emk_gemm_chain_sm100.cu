@@ -338,11 +338,11 @@ gemm2_chain_kernel(const __grid_constant__ ChainParams P) {
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * CH_BN + half * (CH_BN / 2));
       bool ok = true;
       const GemmArgs g = P.g[p];  // a local copy: the fields the epilogue uses become registers
-      epilogue_prefetch(g, row, n0, CH_BN / 2);
+      epilogue_prefetch<EMK_EPI_SET_LAYER>(g, row, n0, CH_BN / 2);
       ok = mbar_wait_warp(&bars->tmem_full[acc], acc_phase, wc, EMK_DEV_TIMEOUT_EPILOGUE);
       if (ok) {
         tc_fence_after();
-        epilogue_drain<CH_BN / 64>(g, taddr, row, n0);
+        epilogue_drain<CH_BN / 64, EMK_EPI_SET_LAYER>(g, taddr, row, n0);
       }
       if (!ok) break;
       tc_fence_before();
@@ -430,6 +430,11 @@ extern "C" int emk_gemm_bf16_chain(emk_handle_t h, const emk_gemm_desc_t* descs,
     GemmArgs& g = P.g[p];
     int rc = emk_gemm_desc_to_args(h, &d, &g);
     if (rc != EMK_OK) return rc;
+    if (g.epi != EMK_EPI_RESIDUAL && g.epi != EMK_EPI_SWIGLU && g.epi != EMK_EPI_QKNORM_ROPE_INTERNAL) {
+      EMK_SET_ERR(h, "emk_gemm_bf16_chain: phase %d: the chain kernel carries the residual, SwiGLU and q/k-norm + RoPE "
+                  "epilogues only", p);
+      return EMK_ERR_ARG;
+    }
     g.coherent = 1;
     g.tiles_m = P.row_blocks;
     g.tiles_n = (int)((d.N + CH_BN - 1) / CH_BN);

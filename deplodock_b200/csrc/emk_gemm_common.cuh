@@ -65,8 +65,14 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
 // (its code then holds only that epilogue), the launch argument where it was built for all of them (EPI < 0).
 // A GEMM kernel that carries every epilogue is large enough to push the attention kernel out of the instruction
 // cache and back at every switch between the two (measured: about 7 us per switch, two switches per decoder layer).
+constexpr int EMK_EPI_SET_LAYER = -2;  // run-time choice among residual / SwiGLU / q-k-norm + RoPE only (GEMM chain)
 template <int EPI>
 __device__ __forceinline__ int epi_of(const GemmArgs& g) {
+  if (EPI == EMK_EPI_SET_LAYER) {
+    const int e = g.epi;   // any other value is refused by the host; the selects let the compiler drop the other paths
+    return e == EMK_EPI_SWIGLU ? (int)EMK_EPI_SWIGLU
+                               : (e == EMK_EPI_QKNORM_ROPE_INTERNAL ? EMK_EPI_QKNORM_ROPE_INTERNAL : (int)EMK_EPI_RESIDUAL);
+  }
   return EPI < 0 ? g.epi : EPI;
 }
 

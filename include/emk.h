@@ -180,7 +180,7 @@ int emk_gemm_bf16_fused(emk_handle_t h, const emk_gemm_desc_t* desc, emk_stream_
  * counter per phase and row block), so the launches, pipeline fills, exposed last epilogues and partial last waves of
  * separate calls disappear — the o_proj -> gate/up -> down -> next-layer QKV sequence of a decoder layer, whose
  * counterpart in the reference is four separately launched k_linear_* kernels. Every phase: the same M, W [N,K]
- * (EMK_W_NK), N > 128. Besides its x, a phase may read (residual, row_sumsq_in) only what an EARLIER phase of the chain
+ * (EMK_W_NK), N > 128, epilogue EMK_EPI_RESIDUAL, EMK_EPI_SWIGLU or EMK_EPI_QKNORM_ROPE. Besides its x, a phase may read (residual, row_sumsq_in) only what an EARLIER phase of the chain
  * wrote or what the chain does not write; y may alias the phase's own residual.
  * `workspace` (emk_gemm_bf16_chain_workspace_bytes(M) bytes, 16-byte aligned, device memory) holds the counters: it
  * must be zero before the first launch, and every launch that completes leaves it zero again (after
