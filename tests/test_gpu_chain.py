@@ -156,3 +156,28 @@ def test_model_plans_with_and_without_the_chain_agree(libemk):
     ya2 = a(ids.cuda()).cpu().clone()          # graph replay over the same counter workspace
     yc = c(ids.cuda()).cpu().clone()
     assert torch.equal(ya, yc) and torch.equal(ya, ya2)
+
+
+def test_packed_plan_with_and_without_the_chain_agree(libemk):
+    """The variable-length plan (per-row rotary positions, cu_seqlens-driven attention) with chained projections."""
+    from deplodock_b200.model import EmbedWeights, PackedForward
+
+    cfg = inputs.EmbedModelConfig(num_hidden_layers=2, vocab_size=1000)
+    w = EmbedWeights(cfg, inputs.embed_model_weights(cfg, seed=8))
+    lens = [130, 64, 257, 5, 200]
+    total = sum(lens)
+    g = torch.Generator().manual_seed(9)
+    ids = torch.randint(0, cfg.vocab_size, (total,), generator=g).cuda()
+    pos = torch.cat([torch.arange(n, dtype=torch.int32) for n in lens]).cuda()
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32).cuda()
+    outs = {}
+    for chain in (False, True):
+        plan = PackedForward(w, tokens=768, max_seqs=8, max_seq_len=384, chain=chain)
+        assert plan.chain is chain
+        plan.set_batch(ids, pos, cu)
+        plan.replay()
+        plan.replay()
+        torch.cuda.synchronize()
+        outs[chain] = (plan.hs[:total].clone(), plan.out[: len(lens)].clone())
+    assert torch.equal(outs[False][0], outs[True][0])
+    assert torch.equal(outs[False][1], outs[True][1])
