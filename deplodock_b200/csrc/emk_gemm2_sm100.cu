@@ -37,7 +37,8 @@ struct __align__(8) G2Barriers {
 // G2_BN: tile width (256 or 128 columns; each CTA loads half of them). A ring stage holds KSUB 64-wide K slices:
 // KSUB x (16 KB of A + G2_BN/2 rows of W).
 // EPI: the one epilogue this instantiation carries (EMK_EPI_*), or -1 for all of them chosen by the launch argument.
-template <int G2_BN, int G2_STAGES, int WL, int KSUB, int EPI>
+// FAST: whole tiles of 32-byte aligned rows only (no bounds tests, no narrow accesses in the epilogue).
+template <int G2_BN, int G2_STAGES, int WL, int KSUB, int EPI, bool FAST>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2_THREADS, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                   const GemmArgs g) {
@@ -195,12 +196,12 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       tile_coords(tile, g.tiles_m, g.tiles_n, G2_GROUP_M, tm, tn);
       const int row = tm * 2 * BM + (int)rank * BM + quarter * 32 + lane;
       const int n0 = tn * G2_BN + half * (G2_BN / 2);
-      epilogue_prefetch<EPI>(g, row, n0, G2_BN / 2);
+      epilogue_prefetch<EPI, FAST>(g, row, n0, G2_BN / 2);
       if (!mbar_wait_warp(&bars->tmem_full[acc], acc_phase, wc, EMK_DEV_TIMEOUT_EPILOGUE)) break;
       tc_fence_after();
       const uint32_t taddr =
           tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * G2_BN + half * (G2_BN / 2));
-      epilogue_drain<G2_BN / 64, EPI>(g, taddr, row, n0);
+      epilogue_drain<G2_BN / 64, EPI, FAST>(g, taddr, row, n0);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster_relaxed(mapa_u32(smem_u32(&bars->tmem_empty[acc]), 0));
@@ -215,12 +216,12 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
   if (warp == 0) tmem_dealloc_pair(tmem_base, G2_TMEM_COLS);
 }
 
-template <int G2_BN, int G2_STAGES, int WL, int KSUB, int EPI = -1>
+template <int G2_BN, int G2_STAGES, int WL, int KSUB, int EPI = -1, bool FAST = false>
 int launch_gemm2(emk_handle_t h, const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, cudaStream_t s) {
   constexpr int G2_SMEM = G2_STAGES * KSUB * (A_STAGE_BYTES + (G2_BN / 2) * BK * 2) + 1024 + (int)sizeof(G2Barriers);
   static emk_device_once once;
   static int max_pairs[EMK_MAX_DEVICES] = {0};
-  auto kern = gemm2_bf16_kernel<G2_BN, G2_STAGES, WL, KSUB, EPI>;
+  auto kern = gemm2_bf16_kernel<G2_BN, G2_STAGES, WL, KSUB, EPI, FAST>;
   const int d = h->device;   // emk_create admits ordinals below EMK_MAX_DEVICES only
   std::unique_lock<std::mutex> lk(once.mu);
   if (!once.done[d]) {
@@ -274,13 +275,19 @@ int emk_gemm2_launch(emk_handle_t h, const void* x, const void* w, emk::GemmArgs
     // two 64-wide K slices per ring stage: the per-stage barrier/commit work of the MMA thread is paid half as often
     if (bn == 256) {
       // the epilogues of the model path each have a kernel of their own (smaller code: see epi_of)
+      const bool fast = (g.M % (2 * BM)) == 0 && (g.N % 256) == 0 && g.wide;
+#define EMK_G2_CASE(E)                                                              \
+  case E:                                                                           \
+    return fast ? launch_gemm2<256, 3, 0, 2, E, true>(h, ta, tb, g, s)              \
+                : launch_gemm2<256, 3, 0, 2, E, false>(h, ta, tb, g, s);
       switch (g.epi) {
-        case EMK_EPI_NONE: return launch_gemm2<256, 3, 0, 2, EMK_EPI_NONE>(h, ta, tb, g, s);
-        case EMK_EPI_RESIDUAL: return launch_gemm2<256, 3, 0, 2, EMK_EPI_RESIDUAL>(h, ta, tb, g, s);
-        case EMK_EPI_SWIGLU: return launch_gemm2<256, 3, 0, 2, EMK_EPI_SWIGLU>(h, ta, tb, g, s);
-        case EMK_EPI_QKNORM_ROPE_INTERNAL: return launch_gemm2<256, 3, 0, 2, EMK_EPI_QKNORM_ROPE_INTERNAL>(h, ta, tb, g, s);
+        EMK_G2_CASE(EMK_EPI_NONE)
+        EMK_G2_CASE(EMK_EPI_RESIDUAL)
+        EMK_G2_CASE(EMK_EPI_SWIGLU)
+        EMK_G2_CASE(EMK_EPI_QKNORM_ROPE_INTERNAL)
         default: return launch_gemm2<256, 3, 0, 2>(h, ta, tb, g, s);
       }
+#undef EMK_G2_CASE
     }
     return launch_gemm2<128, 4, 0, 2>(h, ta, tb, g, s);
   }

@@ -82,9 +82,11 @@ __device__ __forceinline__ float silu_f(float g) { return __fdividef(g, 1.0f + _
 
 // Epilogue for 32 accumulator columns [col0, col0+32) of one output row held by this thread. `g.wide` says rows of
 // y (and of the residual) are 32-byte aligned, so full 32-column groups move as 256-bit accesses.
-template <int EPI>
+template <int EPI, bool FAST = false>
 __device__ __forceinline__ float epilogue_store32(const GemmArgs& g, const uint32_t* r, int row, int col0, float rs) {
-  if (row >= g.M || col0 >= g.N) return 0.f;
+  // FAST: the launch covers whole 256 x 256 tiles of 32-byte aligned rows, so no row / column test and no narrow
+  // access path is compiled in (less code to fetch at every kernel switch)
+  if (!FAST && (row >= g.M || col0 >= g.N)) return 0.f;
   if (epi_of<EPI>(g) == EMK_EPI_SWIGLU) {
     // columns are (gate, up) pairs; 16 outputs = 32 bytes
     __nv_bfloat16* out = g.y + (int64_t)row * g.ldy + (col0 >> 1);
@@ -101,7 +103,7 @@ __device__ __forceinline__ float epilogue_store32(const GemmArgs& g, const uint3
       }
       o[j] = pack_bf16x2(v[0], v[1]);
     }
-    if (g.wide && col0 + 32 <= g.N) {
+    if (FAST || (g.wide && col0 + 32 <= g.N)) {
       st_global_v8(out, o);
     } else {
       if (col0 < g.N) *reinterpret_cast<uint4*>(out) = make_uint4(o[0], o[1], o[2], o[3]);
@@ -125,7 +127,7 @@ __device__ __forceinline__ float epilogue_store32(const GemmArgs& g, const uint3
     }
     return 0.f;
   }
-  const bool full = g.wide && (col0 + 32 <= g.N);
+  const bool full = FAST || (g.wide && (col0 + 32 <= g.N));
   float v[32];
   if (g.ss_in != nullptr) {   // the row scale of a folded RMSNorm; without one rs is 1 and the multiplies are skipped
 #pragma unroll
@@ -137,7 +139,7 @@ __device__ __forceinline__ float epilogue_store32(const GemmArgs& g, const uint3
   if (g.scale != nullptr) {
 #pragma unroll
     for (int q = 0; q < 8; ++q) {
-      if (col0 + q * 4 < g.N) {
+      if (FAST || col0 + q * 4 < g.N) {
         const float4 s = __ldg(reinterpret_cast<const float4*>(g.scale + col0 + q * 4));
         v[q * 4 + 0] *= s.x; v[q * 4 + 1] *= s.y; v[q * 4 + 2] *= s.z; v[q * 4 + 3] *= s.w;
       }
@@ -221,9 +223,9 @@ __device__ __forceinline__ int rope_position(const GemmArgs& g, int row) {
 // Issued by an epilogue thread BEFORE it waits for its accumulator: everything the epilogue will read from global
 // memory for this row segment is pulled towards the SM while the tensor core is still working on the tile, so the
 // epilogue (two warps per scheduler, little latency hiding of its own) finds it in L1 / L2.
-template <int EPI = -1>
+template <int EPI = -1, bool FAST = false>
 __device__ __forceinline__ void epilogue_prefetch(const GemmArgs& g, int row, int n0, int ncols) {
-  if (row >= g.M || n0 >= g.N) return;
+  if (!FAST && (row >= g.M || n0 >= g.N)) return;
   if (g.ss_in != nullptr && !g.coherent) {
     asm volatile("prefetch.global.L1 [%0];" ::"l"(g.ss_in + (int64_t)row * g.ss_in_segs));
   }
@@ -249,11 +251,12 @@ __device__ __forceinline__ void epilogue_prefetch(const GemmArgs& g, int row, in
 // and stores them. Holding all 64 packed pairs in registers instead (one sweep) left no room to issue the rotary-table
 // loads ahead of their use within the kernel's 168 registers, and the epilogue of a K = 1024 tile — about 10 000
 // cycles for one head per warp, against 8 192 of tensor-core work — set the pace of the whole projection.
+template <bool FAST = false>
 __device__ __forceinline__ void epilogue_head_qknorm_rope(const GemmArgs& g, uint32_t taddr, int row, int col0,
                                                           float rs) {
   const int head = col0 >> 7;
   const bool rotate = head < g.qk_Hq + g.qk_Hkv;   // uniform over the warp (all lanes share the column range)
-  const bool valid = row < g.M && col0 < g.N;
+  const bool valid = FAST || (row < g.M && col0 < g.N);
   __nv_bfloat16* out = g.y + (int64_t)row * g.ldy + col0;
   if (!rotate) {
     // value head: bf16 of the (row-scaled) accumulator, 32 columns at a time
@@ -358,11 +361,11 @@ __device__ __forceinline__ void epilogue_head_qknorm_rope(const GemmArgs& g, uin
 
 // Drains one accumulator (NCHUNK x 32 columns of this thread's row) from tensor memory through the epilogue. The load
 // of chunk c+1 is in flight while chunk c is converted and stored.
-template <int NCHUNK, int EPI = -1>
+template <int NCHUNK, int EPI = -1, bool FAST = false>
 __device__ __forceinline__ void epilogue_drain(const GemmArgs& g, uint32_t taddr, int row, int n0) {
   // row scale of a folded RMSNorm on the input side (1 when there is none)
   float rs = 1.0f;
-  if (g.ss_in != nullptr && row < g.M) {
+  if (g.ss_in != nullptr && (FAST || row < g.M)) {
     const float* pr = g.ss_in + (int64_t)row * g.ss_in_segs;  // the row's partial sums are contiguous
     float tot = 0.f;
     if (g.ss_in_segs == 8) {
@@ -379,7 +382,7 @@ __device__ __forceinline__ void epilogue_drain(const GemmArgs& g, uint32_t taddr
   if (epi_of<EPI>(g) == EMK_EPI_QKNORM_ROPE_INTERNAL) {
 #pragma unroll 1
     for (int hd = 0; hd < NCHUNK / 4; ++hd)
-      epilogue_head_qknorm_rope(g, taddr + (uint32_t)(hd * 128), row, n0 + hd * 128, rs);
+      epilogue_head_qknorm_rope<FAST>(g, taddr + (uint32_t)(hd * 128), row, n0 + hd * 128, rs);
     return;
   }
   uint32_t r[2][32];
@@ -389,9 +392,9 @@ __device__ __forceinline__ void epilogue_drain(const GemmArgs& g, uint32_t taddr
   for (int c = 0; c < NCHUNK; ++c) {
     tmem_ld_wait_regs(r[c & 1]);
     if (c + 1 < NCHUNK) tmem_ld_x32(taddr + (uint32_t)((c + 1) * 32), r[(c + 1) & 1]);
-    ss += epilogue_store32<EPI>(g, r[c & 1], row, n0 + c * 32, rs);
+    ss += epilogue_store32<EPI, FAST>(g, r[c & 1], row, n0 + c * 32, rs);
   }
-  if (g.ss_out != nullptr && row < g.M) {
+  if (g.ss_out != nullptr && (FAST || row < g.M)) {
     // this thread owns columns [n0, n0 + 32*NCHUNK): its total goes to the first 128-column slot it covers, zeros to
     // the others
     const int slot0 = n0 >> 7;
