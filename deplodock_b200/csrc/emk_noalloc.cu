@@ -15,8 +15,8 @@
 //     keeps the last call's contents; nothing in it has to start at zero because the GEMM epilogue overwrites every
 //     slot it later reads;
 //   * the first call on a device looks the array's device address up (cudaGetSymbolAddress), and the first call of
-//     each shape class (M <= 128 or larger, N <= 128 or larger: each selects its own GEMM kernel) sets that kernel's
-//     attributes: make a warm-up call of the same shape class before any stream capture.
+//     each shape class (M <= 128 or larger, N <= 128 or larger, M and N both multiples of 256 or not: each selects
+//     its own GEMM kernel) sets that kernel's attributes: make a warm-up call of the same shape class before any stream capture.
 // No counterpart exists in the reference (its runtime allocates through cupy, emmy/compiler/backend/cuda/program.py:340-364).
 #include "emk_common.cuh"
 

@@ -196,8 +196,8 @@ int emk_gemm_bf16_chain(emk_handle_t h, const emk_gemm_desc_t* descs, int n, voi
  * heap, code under stream capture, latency-critical loops. Limit: M * ceil(N/128) <= 1048576, else EMK_ERR_LIMIT.
  * All calls on a device share the array, so calls that overlap on the GPU race; nothing in it needs zeroing. The
  * first call on a device resolves the array's address, and the first call of each shape class (M <= 128 or larger,
- * N <= 128 or larger: each selects its own GEMM kernel) sets that kernel's attributes: make a warm-up call of the
- * same shape class before any stream capture.
+ * N <= 128 or larger, M and N both multiples of 256 or not: each selects its own GEMM kernel) sets that kernel's
+ * attributes: make a warm-up call of the same shape class before any stream capture.
  * This entry point has no counterpart in the reference. */
 int emk_linear_residual_rmsnorm_bf16_noalloc(emk_handle_t h, const void* x, const void* w, const void* residual,
                                              const void* norm_weight, void* y_hidden, void* y_norm, int64_t M,
