@@ -71,6 +71,7 @@ _SIGNATURES: dict[str, list] = {
     "emk_last_error": [c_void_p],
     "emk_device_status": [c_void_p, c_void_p],
     "emk_set_wait_limit_ms": [c_void_p, c_int],
+    "emk_set_launch_overlap": [c_void_p, c_int],
     "emk_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_float, c_int, c_void_p],
     "emk_softmax_lastdim": [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p],
     "emk_linear_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int,
@@ -188,6 +189,13 @@ class Handle:
 
     def set_wait_limit_ms(self, ms: int) -> None:
         self.check(self.lib.emk_set_wait_limit_ms(self.ptr, int(ms)), "emk_set_wait_limit_ms")
+
+    def set_launch_overlap(self, on: bool) -> bool:
+        """Programmatic dependent launch for the kernels launched from now on; returns the previous setting."""
+        prev = int(self.lib.emk_set_launch_overlap(self.ptr, 1 if on else 0))
+        if prev < 0:
+            self.check(-prev, "emk_set_launch_overlap")
+        return bool(prev)
 
     def close(self) -> None:
         if getattr(self, "ptr", None) is not None and self.ptr.value:

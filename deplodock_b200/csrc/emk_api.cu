@@ -107,6 +107,13 @@ extern "C" int emk_set_wait_limit_ms(emk_handle_t h, int ms) {
   return EMK_OK;
 }
 
+extern "C" int emk_set_launch_overlap(emk_handle_t h, int on) {
+  if (!h) return -EMK_ERR_ARG;
+  const int prev = h->overlap_launch;
+  h->overlap_launch = on ? 1 : 0;
+  return prev;
+}
+
 extern "C" int emk_device_status(emk_handle_t h, emk_stream_t stream) {
   if (!h) return EMK_ERR_ARG;
   EMK_CUDA_TRY(h, cudaStreamSynchronize((cudaStream_t)stream));

@@ -476,8 +476,10 @@ extern "C" int emk_gemm_bf16_chain(emk_handle_t h, const emk_gemm_desc_t* descs,
   }
   // Every pair must be resident for the dependency waits to be safe: never more pairs than the device holds at once.
   const int pairs = tiles < max_pairs[dv] ? tiles : max_pairs[dv];
+  // Launched WITHOUT programmatic dependent launch: with it the 16 x 512 forward measured 1.5-2 % slower (the chain's
+  // CTAs that become resident early only spin until the attention kernel before them has drained).
   EMK_CUDA_TRY(h, launch_after_prologue(kern, 2u * (unsigned)pairs, CH_THREADS, CH_SMEM, (cudaStream_t)stream,
-                                        h->overlap_launch != 0, P));
+                                        false, P));
   EMK_LAUNCH_CHECK(h);
   return EMK_OK;
 }

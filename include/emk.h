@@ -88,6 +88,13 @@ int emk_device_status(emk_handle_t h, emk_stream_t stream);
 /* Limit, in milliseconds, of every device-side mbarrier wait (default 2000). */
 int emk_set_wait_limit_ms(emk_handle_t h, int ms);
 
+/* Programmatic dependent launch for the model-path kernels launched through this handle from now on: on (the
+ * default, unless EMK_OVERLAP_LAUNCH=0) a kernel may become resident and run its set-up while the kernel before it in
+ * the stream drains; off, kernels follow each other the ordinary way. Returns the previous setting (0 / 1), or a
+ * negative status. Plans that chain their projections (emk_gemm_bf16_chain) measured 1.5-2 % faster with it off,
+ * plans of separately launched GEMMs up to 3 % faster with it on. No counterpart in the reference. */
+int emk_set_launch_overlap(emk_handle_t h, int on);
+
 /* RMSNorm over the last axis: y = x * rsqrt(mean(x^2) + eps) * w, statistics in fp32.
  * Replaces the emitted k_rms_norm_<hash> kernel (RmsNormOp, emmy/compiler/ir/frontend/ir.py:296-312;
  * decomposition emmy/compiler/pipeline/passes/frontend/decomposition/080_rms_norm.py:17-60).
