@@ -639,7 +639,7 @@ def main() -> None:
     import torch.distributed as dist
 
     from deplodock_b200 import cabi, ops
-    from deplodock_b200.dist import gather_embeddings, init_process_group, shard_batch
+    from deplodock_b200.dist import PipelinedGather, gather_embeddings, init_process_group, shard_batch
     from deplodock_b200.model import EmbedConfig, EmbedForward
 
     cabi.load_library()  # fail loudly when the CUDA extension is missing
@@ -682,9 +682,21 @@ def main() -> None:
             dist.barrier()
         torch.cuda.synchronize()
 
+    # device-timed steps: the all-gather of step i runs beside the forward of step i + 1 (PipelinedGather); every
+    # gather still in flight is waited for before the closing event of the timed region
+    pipe = PipelinedGather(shard.size, BATCH, H, dev) if shard.size * world == BATCH else None
+
     def step_device():
         model.replay()
-        gather_embeddings(model.out, BATCH, out=gathered)
+        if pipe is not None:
+            pipe.submit(model.out)
+        else:
+            gather_embeddings(model.out, BATCH, out=gathered)
+
+    def finish_device():
+        if pipe is not None:
+            gathered.copy_(pipe.result())
+            pipe.flush()
 
     def step_e2e():
         model(ids_host)
@@ -692,12 +704,14 @@ def main() -> None:
         out_host.copy_(gathered, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
-    def timed(fn, steps):
+    def timed(fn, steps, finish=None):
         barrier()
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s.record()
         for _ in range(steps):
             fn()
+        if finish is not None:
+            finish()
         e.record()
         barrier()
         ms = torch.tensor([s.elapsed_time(e)], device=dev, dtype=torch.float64)
@@ -710,7 +724,7 @@ def main() -> None:
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
         sampler.start()
-    total_ms = timed(step_device, args.steps)
+    total_ms = timed(step_device, args.steps, finish_device)
     clocks = sampler.stop() if sampler else None
     for _ in range(2):
         step_e2e()

@@ -84,3 +84,52 @@ def gather_embeddings(local: torch.Tensor, total: int, out: torch.Tensor | None 
         sh = shard_batch(total, r, world)
         out[sh.start: sh.stop] = buf[r * width: r * width + sh.size]
     return out
+
+
+class PipelinedGather:
+    """All-gather of the pooled embeddings that does not stall the next forward.
+
+    A forward's last kernel writes ``[batch/world, hidden]`` embeddings; gathering them on the compute stream makes
+    every rank wait for the slowest one at every step before its next forward may start. Here the shard is copied to
+    one of ``depth`` staging buffers (compute stream, 32 KB) and gathered from there with an asynchronous NCCL
+    all-gather: the next forward starts at once, and a buffer is reused only after the gather that read it has
+    completed (a stream-level wait on a collective issued ``depth`` steps earlier, long done). :meth:`result` waits
+    for the most recent gather and returns its ``[total, hidden]`` output. Equal shards only."""
+
+    def __init__(self, shard_rows: int, total: int, hidden: int, device, dtype=torch.float32, depth: int = 2) -> None:
+        self.world = dist.get_world_size() if dist.is_initialized() else 1
+        if shard_rows * self.world != total:
+            raise ValueError("PipelinedGather needs equal shards (total = world * shard rows)")
+        self.stage = [torch.empty(shard_rows, hidden, dtype=dtype, device=device) for _ in range(depth)]
+        self.out = [torch.empty(total, hidden, dtype=dtype, device=device) for _ in range(depth)]
+        self.work: list = [None] * depth
+        self.n = 0
+
+    def submit(self, local: torch.Tensor) -> None:
+        k = self.n % len(self.stage)
+        if self.work[k] is not None:
+            self.work[k].wait()          # the gather that last used this pair of buffers (stream-level for NCCL)
+            self.work[k] = None
+        self.stage[k].copy_(local)
+        if self.world > 1:
+            self.work[k] = dist.all_gather_into_tensor(self.out[k], self.stage[k], async_op=True)
+        else:
+            self.out[k].copy_(self.stage[k])
+        self.n += 1
+
+    def result(self) -> torch.Tensor:
+        """The gathered embeddings of the most recent :meth:`submit` (the current stream waits for that gather)."""
+        if self.n == 0:
+            raise RuntimeError("nothing has been submitted")
+        k = (self.n - 1) % len(self.stage)
+        if self.work[k] is not None:
+            self.work[k].wait()
+            self.work[k] = None
+        return self.out[k]
+
+    def flush(self) -> None:
+        """Make the current stream wait for every gather still in flight."""
+        for k, w in enumerate(self.work):
+            if w is not None:
+                w.wait()
+                self.work[k] = None

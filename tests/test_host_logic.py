@@ -461,3 +461,62 @@ def test_launch_names_of_the_chained_plan():
     assert names[3][0] == "k_linear_chain_o_proj_gate_up_down_0_qkv_1"
     assert names[-2][0] == "k_linear_chain_o_proj_gate_up_down_2"
     assert len(launch_names(3, chain=False)) == 1 + 5 * 3 + 1
+
+
+def _pipelined_gather_worker(rank: int, world: int, port: int, q) -> None:
+    sys.path.insert(0, str(ROOT))
+    os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port))
+    import torch.distributed as dist
+
+    from deplodock_b200.dist import PipelinedGather, init_process_group, shard_batch
+
+    r, _, w = init_process_group("gloo")
+    total, hidden = 8, 4
+    sh = shard_batch(total, r, w)
+    pipe = PipelinedGather(sh.size, total, hidden, "cpu")
+    ok = True
+    local = torch.empty(sh.size, hidden)
+    for step in range(5):   # more steps than buffers: every staging / output pair is reused
+        full = torch.arange(total * hidden, dtype=torch.float32).reshape(total, hidden) + 100 * step
+        local.copy_(full[sh.start:sh.stop])      # the same tensor object every step, as a plan's output buffer is
+        pipe.submit(local)
+        if step % 2 == 1:
+            ok = ok and torch.equal(pipe.result(), full)
+    pipe.flush()
+    ok = ok and torch.equal(pipe.result(), full)
+    try:
+        PipelinedGather(sh.size + 1, total, hidden, "cpu")
+        ok = False
+    except ValueError:
+        pass
+    q.put((rank, ok))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_pipelined_gather_two_gloo_ranks():
+    """The gather that runs beside the next forward: staged copies, asynchronous collectives, buffers reused only
+    after their gather completed; results in shard order at every step."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_pipelined_gather_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = sorted(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert results == [(0, True), (1, True)]
+
+
+def test_pipelined_gather_single_process():
+    from deplodock_b200.dist import PipelinedGather
+
+    pipe = PipelinedGather(3, 3, 2, "cpu")
+    x = torch.arange(6, dtype=torch.float32).reshape(3, 2)
+    pipe.submit(x)
+    assert torch.equal(pipe.result(), x)
+    with pytest.raises(RuntimeError):
+        PipelinedGather(3, 3, 2, "cpu").result()
