@@ -3,12 +3,12 @@
 // The reference has no fp8 path (nothing under emmy/ mentions fp8 or e4m3); the contraction itself is the LinearOp of
 // emmy/compiler/ir/frontend/ir.py:202-217. tcgen05 kind::f16 needs both operands as 16-bit types, so the weight tile
 // is dequantised inside the main loop: TMA lands the raw e4m3 tile (half the bytes of a bf16 tile) in shared memory,
-// four converter warps expand it to bf16 (exact: every e4m3 value is representable in bf16) directly into the
+// eight converter warps expand it to bf16 (exact: every e4m3 value is representable in bf16) directly into the
 // 128-byte-swizzled K-major layout the tensor core reads, and the per-output-channel scale is applied once per
 // output element in the epilogue (it commutes with the sum over k).
 //
 //   warps 0..3  epilogue (as in the bf16 kernel)      warp 4  TMA producer      warp 5  MMA issuer
-//   warps 6..9  e4m3 -> bf16 converters
+//   warps 6..13 e4m3 -> bf16 converters
 #include "emk_gemm_common.cuh"
 
 #include <cuda_fp8.h>
@@ -19,7 +19,8 @@ using namespace emk;
 
 constexpr int W8_BN = 256;
 constexpr int W8_STAGES = 3;
-constexpr int W8_THREADS = 320;
+constexpr int W8_THREADS = 448;  // warps 0-3 epilogue, 4 TMA, 5 MMA, 6-13 converters
+constexpr int W8_CVT_THREADS = 256;
 constexpr int W8_RAW_BYTES = W8_BN * BK;       // e4m3 tile: 256 rows x 64 bytes
 constexpr int W8_B_BYTES = W8_BN * BK * 2;     // bf16 tile
 constexpr uint32_t W8_TX = A_STAGE_BYTES + W8_RAW_BYTES;
@@ -46,6 +47,11 @@ __device__ __forceinline__ void cvt_e4m3x4_bf16(uint32_t w, uint32_t& lo, uint32
   hi = pack_bf16x2(f23.x, f23.y);
 }
 
+// Eight converter warps, not four: the conversion (one operation of the quarter-rate conversion pipe per element) is
+// what paces the main loop, and two converter warps per scheduler hide its latency where one could not (4096 x 2048 x
+// 6144: 158 -> 124 us; twelve warps: 130 us). Two routes around the conversion pipe were measured and dropped: the
+// e4m3 bits shifted into a bf16's fields and scaled by a packed bf16 multiply (232 us), and cvt to f16 followed by the
+// same shift-and-scale (184 us) — both exact, both slower than the plain conversions.
 constexpr int W8_EXPAND_MIN_M = 256;  // above this many rows the weight is expanded once instead of per row tile
 
 __global__ void __launch_bounds__(W8_THREADS, 1)
@@ -65,7 +71,7 @@ gemm_w8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   if (threadIdx.x == 0) {
     for (int i = 0; i < W8_STAGES; ++i) {
       mbar_init(&bars->full_raw[i], 1);
-      mbar_init(&bars->full_cvt[i], 128);
+      mbar_init(&bars->full_cvt[i], W8_CVT_THREADS);
       mbar_init(&bars->empty[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
@@ -155,7 +161,7 @@ gemm_w8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     // ---------------- converters: e4m3 tile -> bf16 tile in the UMMA swizzled layout ----------------
     const int tid = threadIdx.x - 192;
     const int c = tid & 3;     // 16-byte chunk of the 64-byte e4m3 row -> bf16 chunks 2c, 2c+1
-    const int r0 = tid >> 2;   // 0..31
+    const int r0 = tid >> 2;   // 0..63
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
@@ -168,8 +174,8 @@ gemm_w8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         const uint8_t* raw = sW + stage * W8_RAW_BYTES;
         uint8_t* dst = sB + stage * W8_B_BYTES;
 #pragma unroll
-        for (int i = 0; i < W8_BN / 32; ++i) {
-          const int r = r0 + 32 * i;
+        for (int i = 0; i < W8_BN / (W8_CVT_THREADS / 4); ++i) {
+          const int r = r0 + (W8_CVT_THREADS / 4) * i;
           const uint4 v = *reinterpret_cast<const uint4*>(raw + r * 64 + c * 16);
           uint4 o0, o1;
           cvt_e4m3x4_bf16(v.x, o0.x, o0.y);
@@ -202,7 +208,7 @@ gemm_w8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       const int n0 = tn * W8_BN;
       const int row = m0 + warp * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(acc * W8_BN);
-epilogue_drain<W8_BN / 32>(g, taddr, row, n0);
+      epilogue_drain<W8_BN / 32, EMK_EPI_NONE>(g, taddr, row, n0);   // the only epilogue of this kernel (+ channel scale)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_relaxed(&bars->tmem_empty[acc]);

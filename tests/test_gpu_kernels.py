@@ -215,6 +215,24 @@ def test_linear_w8_exact_dequant_incl_subnormals(ops):
     assert torch.equal(got, wq.float().t().contiguous())
 
 
+def test_linear_w8_nan_codes_stay_nan(ops):
+    """The two e4m3 NaN codes take the converter's slow path: a channel that holds one is NaN, the others are exact."""
+    K = N = 256
+    codes = torch.arange(256, dtype=torch.uint8)
+    codes = codes[(codes & 0x7F) != 0x7F]
+    bits = codes.repeat((N * K + len(codes) - 1) // len(codes))[: N * K].reshape(N, K).clone()
+    bits[5, 7] = 0x7F
+    bits[130, 200] = 0xFF
+    wq = bits.view(torch.float8_e4m3fn)
+    x = torch.eye(K).bfloat16()
+    got = ops.linear_w8(_dev(x), _dev(wq), _dev(torch.ones(N)), workspace=None).cpu().float()
+    ops.device_status()
+    assert torch.isnan(got[:, 5]).all() and torch.isnan(got[:, 130]).all()
+    keep = torch.ones(N, dtype=torch.bool)
+    keep[[5, 130]] = False
+    assert torch.equal(got[:, keep], wq.float().t().contiguous()[:, keep])
+
+
 @pytest.mark.parametrize("M,K,N", [(512, 1024, 1024), (1000, 144, 264)])
 def test_linear_w8_routes_agree(ops, M, K, N):
     """In-loop conversion and expand-once-then-multiply do the same arithmetic (exact e4m3 -> bf16, fp32
