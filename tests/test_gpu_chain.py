@@ -181,3 +181,20 @@ def test_packed_plan_with_and_without_the_chain_agree(libemk):
         outs[chain] = (plan.hs[:total].clone(), plan.out[: len(lens)].clone())
     assert torch.equal(outs[False][0], outs[True][0])
     assert torch.equal(outs[False][1], outs[True][1])
+
+
+def test_launch_overlap_setting_round_trip(ops):
+    """``emk_set_launch_overlap`` returns the previous setting; a chained plan leaves the handle as it found it."""
+    import os
+
+    from deplodock_b200.model import EmbedForward
+
+    h = ops.handle()
+    default = os.environ.get("EMK_OVERLAP_LAUNCH", "1") != "0"
+    assert h.set_launch_overlap(False) is default
+    assert h.set_launch_overlap(True) is False
+    assert h.set_launch_overlap(default) is True
+    cfg = inputs.EmbedModelConfig(num_hidden_layers=1, vocab_size=500)
+    plan = EmbedForward(cfg, inputs.embed_model_weights(cfg, seed=2), batch=2, seq=64, chain=True)
+    plan(inputs.token_ids(2, 64, cfg.vocab_size, seed=3).cuda())
+    assert h.set_launch_overlap(default) is default   # the plan restored it after capturing
